@@ -1,0 +1,139 @@
+/* C ABI of the B200 (sm_100a) Mixture-of-Experts feed-forward block.
+ *
+ * Drop-in replacement for the MoE block of TMT (tmt-cuda/src/moe.cu): the functions
+ * below take over what moe_keep_alloc / moe_ws_alloc / moe_forward / moe_aux_from /
+ * moe_backward do there. Conventions follow the reference's existing C ABI
+ * (tmt-cuda/src/capi.h, capi.cu:9-24): opaque handle, 0 on success and -1 on failure,
+ * the message of the last failure of the calling thread from tmt_moe_last_error(),
+ * C++ exceptions never cross, the library never calls exit().
+ *
+ * All tensor arguments are DEVICE pointers unless a function name ends in _host.
+ * bf16 tensors are raw 16-bit patterns. Weight layout is the reference's [out,in]
+ * row-major (tmt-cuda/src/linalg.cu:3-4).
+ *
+ * Two expert modes:
+ *   hidden == 0  "reference mode": one dim x dim matrix per expert, SiLU applied in
+ *                combine (moe.cu:142-158). Wup[e] is that matrix, Wdown is NULL.
+ *   hidden  > 0  two-matrix FFN: h = silu(x Wup[e]^T), y = gate * (h Wdown[e]^T).
+ *                Wup[e] is hidden x dim, Wdown[e] is dim x hidden.
+ */
+#ifndef TMT_MOE_H
+#define TMT_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tmt_moe tmt_moe;
+
+enum { TMT_MOE_BF16 = 0, TMT_MOE_F32 = 1 };
+enum { TMT_MOE_GEMM_TCGEN05 = 0, TMT_MOE_GEMM_SIMT = 1 };
+
+/* Replaces the (N,E,K,D) arguments of moe_keep_alloc / moe_ws_alloc (moe.cu:330-362) and
+ * the config knobs experts=, topk= (tmt-cuda/src/config.h:12). */
+typedef struct tmt_moe_desc {
+    int tokens;        /* capacity: most rows (batch*seqlen) one call may carry            */
+    int dim;           /* model width D, multiple of 8                                     */
+    int hidden;        /* expert hidden width H (multiple of 8); 0 = reference mode        */
+    int experts;       /* E >= 1 (no upper bound of 16 as in config.h:51-52; E <= 256)      */
+    int topk;          /* 1 <= K <= min(E, 8)                                               */
+    int router_dtype;  /* TMT_MOE_BF16 (the reference's work copy, model.cu:513) or _F32    */
+    int training;      /* 1: keep what backward needs; 0: forward only                     */
+    int gemm_impl;     /* TMT_MOE_GEMM_TCGEN05 (product) or _SIMT (slow cross-check kernel) */
+    int device;        /* CUDA device ordinal                                              */
+    int host_io;       /* 1: also allocate staging for the *_host entry points             */
+    void* stream;      /* cudaStream_t all work is queued on; NULL = legacy default stream  */
+    int ep_world;      /* expert-parallel ranks (1 = all experts local)                    */
+    int ep_rank;       /* this rank; it owns experts [rank*E/world, (rank+1)*E/world)        */
+} tmt_moe_desc;
+
+/* moe_keep_alloc + moe_ws_alloc (moe.cu:330-362): every buffer is allocated here, none later. */
+int tmt_moe_create(const tmt_moe_desc* desc, tmt_moe** out);
+/* moe_keep_free + moe_ws_free (moe.cu:342-348, 363-370). Never frees caller memory. */
+void tmt_moe_destroy(tmt_moe* h);
+/* capi.cu:24 tmt_last_error. */
+const char* tmt_moe_last_error(void);
+
+/* Optional per-expert additive bias on the router logits (host pointer, E floats, copied;
+ * NULL removes it). The reference has no such term; the skewed-routing benchmark uses it. */
+int tmt_moe_set_router_bias(tmt_moe* h, const float* bias_host);
+
+/* moe_forward (moe.cu:374-466). X (tokens,D) bf16; Wrouter (E,D) in router_dtype; Wup / Wdown
+ * HOST arrays of E device pointers (the reference's bf16** Wexp, model.cu:500); Y (tokens,D)
+ * bf16, in/out when beta != 0 (Y = beta*Y + moe(X), the fused residual of model.cu:513-515).
+ * tokens <= desc.tokens. Statistics stay on the device until tmt_moe_stats. */
+int tmt_moe_forward(tmt_moe* h, const void* X, const void* Wrouter, const void* const* Wup,
+                    const void* const* Wdown, void* Y, float beta, int tokens);
+
+/* moe_aux_from + the hcnt read (moe.cu:470-475, capi.cu:131-136). Synchronises the stream.
+ * stat[0..E) = sum over tokens of the router probabilities, stat[E] = mean lse^2 (z-loss);
+ * counts[e] = tokens routed to expert e (global over expert-parallel ranks);
+ * *aux = E * sum_e (stat[e]/N) * (counts[e]/(N*K)). Any pointer may be NULL. */
+int tmt_moe_stats(tmt_moe* h, float* stat, int64_t* counts, float* aux);
+
+/* moe_backward (moe.cu:479-545); must follow the forward call on the same handle.
+ * dY (tokens,D) bf16. Outputs: dX (tokens,D) bf16 (written, not accumulated), dWrouter (E,D)
+ * fp32 (written), dWup[e] / dWdown[e] fp32 with the shape of the weight (written; zero for an
+ * expert that received no token). aux and zcoef are the loss coefficients already divided by
+ * the layer count (model.cu:676-677). */
+int tmt_moe_backward(tmt_moe* h, const void* dY, const void* Wrouter, const void* const* Wup,
+                     const void* const* Wdown, float* dWrouter, float* const* dWup,
+                     float* const* dWdown, void* dX, float aux, float zcoef);
+
+/* Host-buffer step used for end-to-end timing: copies X (and dY) from host memory, runs
+ * forward (and backward when dY_host != NULL), copies Y (and dX) and the E+1 statistics back
+ * and synchronises. Needs desc.host_io = 1. Weight and gradient pointers are device memory. */
+int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter,
+                      const void* const* Wup, const void* const* Wdown, float* dWrouter,
+                      float* const* dWup, float* const* dWdown, void* Y_host, void* dX_host,
+                      float* stat_host, float beta, float aux, float zcoef, int tokens);
+
+/* Copies saved routing state to HOST memory (synchronises). The reference exposes the same
+ * tensors as MoeKeep fields (moe.cu:294-315). name is one of
+ *   "logits" "probs" (tokens*E f32)  "idx" "slot_of" (tokens*K i32)  "w" (tokens*K f32)
+ *   "counts" (E i32)  "poff" (E+1 i32, 128-row padded group starts)  "lse" (tokens f32)
+ *   "dlogits" (tokens*E f32, after backward)  "s_j" (tokens*K f32, after backward)
+ * Returns the number of bytes written, or -1. */
+long long tmt_moe_read(tmt_moe* h, const char* name, void* dst_host, size_t dst_bytes);
+
+/* Number of kernel launches the handle has queued since creation (the reference counts
+ * nothing; used by the benchmark to report its launch count). */
+long long tmt_moe_launch_count(const tmt_moe* h);
+/* Device-side status word: 0 when no kernel reported a bounds violation or a wait that ran
+ * out; otherwise the first code recorded. Synchronises. */
+int tmt_moe_device_status(tmt_moe* h);
+
+/* ---- NVFP4 expert weights for sampling (no counterpart in the reference) ---------------
+ * e2m1 values, one e4m3 scale per 16 consecutive input elements, one fp32 scale per tensor. */
+typedef struct tmt_nvfp4_weight {
+    const void* packed;   /* rows*cols/2 bytes, element 2i in the low nibble            */
+    const void* scales;   /* rows*cols/16 e4m3 bytes, row-major                         */
+    float tensor_scale;
+    int rows, cols;
+} tmt_nvfp4_weight;
+
+/* Quantises a bf16 (rows,cols) device matrix, cols % 16 == 0. packed/scales are device
+ * buffers of the sizes above; the per-tensor scale is returned through a HOST pointer. */
+int tmt_moe_quantize_nvfp4(const void* W_bf16, int rows, int cols, void* packed, void* scales,
+                           float* tensor_scale_host, void* stream);
+
+/* Forward with NVFP4 expert weights (hidden > 0 only, training = 0). Wup / Wdown are HOST
+ * arrays of E descriptors. Router as in tmt_moe_forward. */
+int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter,
+                          const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, void* Y,
+                          float beta, int tokens);
+
+/* ---- expert parallelism over NCCL (no counterpart in the reference) -------------------
+ * One process per GPU. Rank 0 creates an id, the host program ships the 128 bytes to all
+ * ranks, every rank calls tmt_moe_ep_init. Dispatch and combine then run as all-to-all
+ * exchanges of grouped rows; Wup/Wdown hold only the E/world local experts. */
+int tmt_moe_ep_unique_id(void* id128);
+int tmt_moe_ep_init(tmt_moe* h, const void* id128);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TMT_MOE_H */

@@ -1,0 +1,84 @@
+// Slow cross-check GEMM: one thread per output row and 32-column chunk, plain loads, the
+// same epilogues as the tensor-core kernel. Exists so that the tcgen05 kernel can be
+// compared against an independent CUDA implementation on the GPU; never the default.
+#include "gemm.cuh"
+
+namespace tmt {
+namespace {
+
+template <int EPI>
+__global__ void gemm_simt_kernel(const GemmParams p, int max_m_tiles) {
+    const int chunks = (p.N + kChunk - 1) / kChunk;
+    const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long r_all = gid / chunks;
+    const int col0 = (int)(gid % chunks) * kChunk;
+    float v[kChunk];
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+    float sw = 0.0f;
+    if (p.mode == kRowsRagged) {
+        const int m_tiles = *p.num_m_tiles;
+        if (r_all >= (long)m_tiles * kBM || r_all >= (long)max_m_tiles * kBM) return;
+        const int e = p.tile_expert[r_all / kBM];
+        if (e < 0 || e >= p.experts) { report(p.status, kErrSlotRange); return; }
+        const uint16_t* W = p.Bexp[e];
+        for (int k = 0; k < p.K; ++k) {
+            const float a = bf2f(p.A[r_all * p.lda + k]);
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+                const int n = col0 + i;
+                if (n < p.N) v[i] += a * bf2f(p.b_mn ? W[(long)k * p.ldb + n] : W[(long)n * p.ldb + k]);
+            }
+        }
+        // the tensor-core kernel writes one partial per 256-column tile; emulate with atomics-free
+        // accumulation: only chunk 0 of each 256-tile owns the partial, so sum its 8 chunks here
+        if constexpr (EPI == kEpiDh) {
+            // handled below by recomputation per 256-column tile
+        }
+        epilogue_chunk<EPI>(p, e, r_all, col0, v, sw);
+        if constexpr (EPI == kEpiDh) atomicAdd(&p.sw_part[r_all * p.sw_ld + col0 / kBN], sw);
+    } else {
+        const long per = p.M;
+        const int e = (int)(r_all / per);
+        const long m = r_all % per;
+        if (e >= p.experts) return;
+        for (int r = p.poff[e]; r < p.poff[e + 1]; ++r) {
+            const float a = bf2f(p.A[(long)r * p.lda + m]);
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+                const int n = col0 + i;
+                if (n < p.N) v[i] += a * bf2f(p.B[(long)r * p.ldb + n]);
+            }
+        }
+        epilogue_chunk<EPI>(p, e, m, col0, v, sw);
+    }
+}
+
+template <int EPI>
+cudaError_t launch_one(const GemmParams& p, int max_m_tiles, cudaStream_t stream) {
+    const int chunks = (p.N + kChunk - 1) / kChunk;
+    const long rows = p.mode == kRowsRagged ? (long)max_m_tiles * kBM : (long)p.experts * p.M;
+    const long threads = rows * chunks;
+    if (threads == 0) return cudaSuccess;
+    if (EPI == kEpiDh) {
+        cudaError_t e = cudaMemsetAsync(p.sw_part, 0, (size_t)max_m_tiles * kBM * p.sw_ld * sizeof(float), stream);
+        if (e != cudaSuccess) return e;
+    }
+    gemm_simt_kernel<EPI><<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>(p, max_m_tiles);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_simt(const GemmParams& p, int max_m_tiles, cudaStream_t stream) {
+    switch (p.epi) {
+        case kEpiBf16: return launch_one<kEpiBf16>(p, max_m_tiles, stream);
+        case kEpiUp: return launch_one<kEpiUp>(p, max_m_tiles, stream);
+        case kEpiDown: return launch_one<kEpiDown>(p, max_m_tiles, stream);
+        case kEpiDh: return launch_one<kEpiDh>(p, max_m_tiles, stream);
+        case kEpiF32: return launch_one<kEpiF32>(p, max_m_tiles, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace tmt

@@ -1,0 +1,320 @@
+// Grouped expert GEMM on the 5th-generation tensor cores (sm_100a): tcgen05.mma with the
+// accumulator in tensor memory, operands staged in shared memory by TMA (no multicast),
+// persistent over 128x256 tiles.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM allocator and
+// MMA issuer (one lane), warps 2..5 = epilogue (each owns the 32 TMEM lanes warp_id % 4).
+// Two 256-column accumulators in TMEM let the epilogue of tile i run under the MMAs of tile
+// i+1. Every wait is bounded: when one runs out the kernel records kErrWaitTimeout, all
+// roles leave their loops, the producer waits (bounded) for copies still in flight, TMEM is
+// freed and the kernel returns.
+#include "gemm.cuh"
+
+namespace tmt {
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kATile = kBM * kBK * 2;   // 16 KB
+constexpr int kBTile = kBN * kBK * 2;   // 32 KB
+constexpr int kStageBytes = kATile + kBTile;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;     // two fp32 accumulators of 256 columns
+constexpr long long kWaitCycles = 4000000000LL;   // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait. Returns false when the kernel is aborting (this wait or another ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            report(status, kErrWaitTimeout);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tensormap_acquire(const CUtensorMap* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (descriptor version 1).
+// K-major: rows of 64 bf16 (128 B) packed 128 B apart; 8-row groups 1024 B apart (stride
+// offset); the leading offset is not used. MN-major: 64 elements of the MN extent are
+// contiguous (128 B), the 8 k-rows of a swizzle atom are 128 B apart, atoms 1024 B apart
+// along k (stride offset), and 64-element MN blocks `mn_block_bytes` apart (leading offset).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, bool mn_major, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+    d |= (uint64_t)(((mn_major ? mn_block_bytes : 16u) >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((1024u >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;   // version
+    d |= 2ull << 61;   // SWIZZLE_128B
+    return d;
+}
+
+struct TileInfo {
+    int expert, row0, col0, kb0, nkb;   // row0: output row (kRowsRagged) or m offset; kb0/nkb in 64-wide k blocks
+};
+
+__device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int m_tiles, int n_tiles, TileInfo& ti) {
+    if (p.mode == kRowsRagged) {
+        if (t >= m_tiles * n_tiles) return false;
+        int mt = t / n_tiles, nt = t - mt * n_tiles;
+        ti.expert = p.tile_expert[mt];
+        ti.row0 = mt * kBM;
+        ti.col0 = nt * kBN;
+        ti.kb0 = 0;
+        ti.nkb = (p.K + kBK - 1) / kBK;
+        return ti.expert >= 0 && ti.expert < p.experts;
+    }
+    int per = m_tiles * n_tiles;
+    if (t >= per * p.experts) return false;
+    int e = t / per, r = t - e * per;
+    int mt = r / n_tiles, nt = r - mt * n_tiles;
+    ti.expert = e;
+    ti.row0 = mt * kBM;
+    ti.col0 = nt * kBN;
+    ti.kb0 = p.poff[e] / kBK;
+    ti.nkb = (p.poff[e + 1] - p.poff[e]) / kBK;
+    return true;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tfull_bar[2], tempty_bar[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // tiles start on a 1024-byte boundary of the shared window (128-byte swizzle atoms)
+    const uint32_t tiles_s = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    volatile int* abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    int m_tiles, n_tiles = (p.N + kBN - 1) / kBN;
+    if (p.mode == kRowsRagged) m_tiles = *p.num_m_tiles; else m_tiles = (p.M + kBM - 1) / kBM;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer ----------------
+            int s = 0; uint32_t ph = 0;
+            uint32_t issued = 0;           // bit s set once stage s has received a load
+            uint32_t last_parity = 0;      // parity of the last load issued into stage s
+            bool ok = true;
+            for (int t = blockIdx.x; ok; t += gridDim.x) {
+                TileInfo ti;
+                if (!get_tile(p, t, m_tiles, n_tiles, ti)) {
+                    if (p.mode == kRowsRagged && t < m_tiles * n_tiles) report(p.status, kErrSlotRange);
+                    break;
+                }
+                const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
+                const CUtensorMap* mb = p.mapB + (size_t)ti.expert * p.b_stride;
+                tensormap_acquire(ma);
+                tensormap_acquire(mb);
+                for (int kb = 0; kb < ti.nkb; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+                    const uint32_t fb = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(fb, p.tx_bytes);
+                    const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
+                    const int k0 = (ti.kb0 + kb) * kBK;
+                    if (p.a_mn) {       // A[k rows][m contiguous]: boxes of 64 m x 64 k
+                        for (int j = 0; j < p.a_boxes; ++j) tma_load_2d(sa + j * 8192, ma, fb, ti.row0 + j * p.a_box_step, k0);
+                    } else {            // A[rows][k contiguous]: one box of 64 k x 128 rows
+                        tma_load_2d(sa, ma, fb, k0, ti.row0);
+                    }
+                    if (p.b_mn) {
+                        for (int j = 0; j < p.b_boxes; ++j) tma_load_2d(sb + j * 8192, mb, fb, ti.col0 + j * p.b_box_step, k0);
+                    } else {
+                        tma_load_2d(sb, mb, fb, k0, ti.col0);
+                    }
+                    issued |= 1u << s;
+                    last_parity = (last_parity & ~(1u << s)) | (ph << s);
+                    if (++s == kStages) { s = 0; ph ^= 1; }
+                }
+            }
+            if (!ok) {
+                // aborting: wait (bounded, no abort short-cut) until the copies already issued have landed
+                for (int q = 0; q < kStages; ++q) {
+                    if (!(issued >> q & 1)) continue;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
+                                   ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor units of 16 B per k = 16
+            const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok; t += gridDim.x) {
+                TileInfo ti;
+                if (!get_tile(p, t, m_tiles, n_tiles, ti)) break;
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+                for (int kb = 0; kb < ti.nkb; ++kb) {
+                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, p.status)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
+                    const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        tc_mma(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                    tc_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs have read it
+                    if (++s == kStages) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                if (ti.nkb > 0) tc_commit(smem_u32(&tfull_bar[acc]));   // accumulator complete
+                else mbar_arrive(smem_u32(&tfull_bar[acc]));            // empty group: nothing to wait for
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
+        int acc = 0; uint32_t acc_ph = 0;
+        for (int t = blockIdx.x;; t += gridDim.x) {
+            TileInfo ti;
+            if (!get_tile(p, t, m_tiles, n_tiles, ti)) break;
+            bool ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int r_in_tile = quarter * 32 + lane;
+            const long row = (long)ti.row0 + r_in_tile;
+            const bool row_ok = (p.mode == kRowsRagged) || (row < p.M);
+            float sw = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < kBN / kChunk; ++c) {
+                const int col0 = ti.col0 + c * kChunk;
+                if (col0 >= p.N) break;
+                float v[kChunk];
+                if (ti.nkb > 0) {
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kBN + c * kChunk), v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+                }
+                if (row_ok) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
+            }
+            if (EPI == kEpiDh && row_ok) p.sw_part[row * p.sw_ld + ti.col0 / kBN] = sw;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+template <int EPI>
+cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
+    const size_t smem = gemm_tcgen05_smem_bytes();
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    gemm_tcgen05_kernel<EPI><<<grid, kThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t gemm_tcgen05_smem_bytes() { return (size_t)kStages * kStageBytes + 1024; }
+
+cudaError_t launch_gemm_tcgen05(const GemmParams& p, int num_sms, cudaStream_t stream) {
+    // persistent: one CTA per SM (the shared-memory footprint allows no second one)
+    switch (p.epi) {
+        case kEpiBf16: return launch_one<kEpiBf16>(p, num_sms, stream);
+        case kEpiUp: return launch_one<kEpiUp>(p, num_sms, stream);
+        case kEpiDown: return launch_one<kEpiDown>(p, num_sms, stream);
+        case kEpiDh: return launch_one<kEpiDh>(p, num_sms, stream);
+        case kEpiF32: return launch_one<kEpiF32>(p, num_sms, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace tmt

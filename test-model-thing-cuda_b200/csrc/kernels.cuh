@@ -1,0 +1,63 @@
+// Launchers of the routing / permutation kernels (routing.cu, permute.cu).
+#pragma once
+#include "common.cuh"
+
+namespace tmt {
+
+struct RouteBufs {
+    // shapes: T tokens, E experts, K top-k, NB = ceil(T / kTokBlock) router blocks
+    float* logits;        // T*E
+    float* probs;         // T*E
+    float* lse;           // T
+    int* idx;             // T*K   selected experts, best first
+    float* w;             // T*K   renormalised gate weights
+    int* rank;            // T*K   position of the assignment among its block's assignments to the same expert
+    int* block_counts;    // NB*E
+    float* block_sump;    // NB*E
+    float* block_z;       // NB
+    int* block_base;      // NB*E  assignments to expert e in earlier blocks
+    int* counts;          // E
+    int* off;             // E+1   true group starts (moe.cu:413)
+    int* poff;            // E+1   group starts padded to kPad rows (moe.cu:416-419)
+    int* tile_expert;     // cap/kPad expert of each 128-row tile, -1 past the end
+    int* num_m_tiles;     // 1
+    float* stat;          // E+1   sum_p[0..E), mean lse^2
+    int* slot_of;         // T*K   row of the assignment in the grouped buffers
+    float* slotw;         // cap   gate weight of each grouped row (0 on pad rows)
+    int* tok_of_slot;     // cap   token of each grouped row (-1 on pad rows)
+    int* status;
+};
+
+struct RouteDims {
+    int T, D, E, K;
+    int cap;              // rows of the grouped buffers
+    int max_tiles;        // cap / kPad
+    int router_f32;
+};
+
+cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
+                          const float* bias, cudaStream_t s);
+cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, cudaStream_t s);
+// Xg[slot] = X[token]; pad rows zeroed; fills slot_of / slotw / tok_of_slot (moe.cu:103-140).
+cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s);
+// Y = beta*Y + sum_j Yg[slot_j]                       (two-matrix mode, gate applied by the GEMM)
+// Y = beta*Y + sum_j w_j * silu(Yg[slot_j])           (reference mode, moe.cu:144-158)
+cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
+                           int silu_in_combine, cudaStream_t s);
+// two-matrix mode: dYg[slot] = bf16(w * dY[token]), pad rows zero.
+// reference mode:  dYg[slot] = silu_bwd(Yg[slot], w * dY[token]); s_j = <dY, silu(Yg[slot])> (moe.cu:162-197).
+cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
+                                 uint16_t* dYg, float* s_j, int reference_mode, cudaStream_t s);
+// moe.cu:200-234. sw_part (may be NULL): per-row partial sums of w * dL/dw from the dH GEMM.
+cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
+                              float* dlogits, float aux, float zcoef, cudaStream_t s);
+// dWr[e, :] = sum_t bf16(dlogits[t, e]) * X[t, :] with X[t] read from Xg[slot_of[t, 0]] (moe.cu:519-521).
+cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float* dlogits, const uint16_t* Xg,
+                             float* partial, int chunks, float* dWr, cudaStream_t s);
+// dX[t] = sum_e bf16(dlogits[t, e]) * Wr[e] + sum_j dXg[slot_j]   (moe.cu:525-529, 238-249)
+cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
+                           const uint16_t* dXg, uint16_t* dX, cudaStream_t s);
+
+constexpr int kRouterDwChunks = 32;
+
+}  // namespace tmt

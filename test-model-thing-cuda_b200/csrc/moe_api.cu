@@ -1,0 +1,534 @@
+// Host side of the MoE block behind the C ABI of include/tmt_moe.h: owns every buffer,
+// builds the TMA tensor maps, queues the kernels of one forward / backward on the handle's
+// stream. Mirrors moe_keep_alloc / moe_ws_alloc / moe_forward / moe_aux_from / moe_backward
+// of tmt-cuda/src/moe.cu:330-545; no allocation and no host synchronisation inside a step.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/tmt_moe.h"
+#include "gemm.cuh"
+#include "kernels.cuh"
+#include "moe_internal.h"
+
+namespace tmt {
+
+thread_local std::string g_error;
+
+void set_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+}
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || !p)
+            throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor, `inner` contiguous elements per row, 128-byte swizzle, zero fill.
+void make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows) {
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled failed (%d) for %llux%llu box %ux%u", (int)r,
+                 (unsigned long long)inner, (unsigned long long)rows, box_inner, box_rows);
+        throw std::runtime_error(msg);
+    }
+}
+
+#define CK(call)                                                                              \
+    do {                                                                                      \
+        cudaError_t e__ = (call);                                                             \
+        if (e__ != cudaSuccess) {                                                             \
+            char m__[256];                                                                    \
+            snprintf(m__, sizeof m__, "%s failed: %s", #call, cudaGetErrorString(e__));       \
+            throw std::runtime_error(m__);                                                    \
+        }                                                                                     \
+    } while (0)
+
+template <class T>
+T* dalloc(tmt_moe* h, size_t n) {
+    void* p = nullptr;
+    CK(cudaMalloc(&p, std::max<size_t>(n, 1) * sizeof(T)));
+    h->allocs.push_back(p);
+    h->bytes += n * sizeof(T);
+    return reinterpret_cast<T*>(p);
+}
+
+enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kNumActMaps };
+enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };
+
+void build_act_maps(tmt_moe* h) {
+    const uint64_t D = h->d.dim, H = h->d.hidden, cap = h->dims.cap;
+    std::vector<CUtensorMap> m(kNumActMaps);
+    memset(m.data(), 0, m.size() * sizeof(CUtensorMap));
+    make_map(&m[kXgK], h->Xg, D, cap, 64, 128);
+    make_map(&m[kDYgK], h->dYg, D, cap, 64, 128);
+    make_map(&m[kDYgMN], h->dYg, D, cap, 64, 64);
+    make_map(&m[kXgMN], h->Xg, D, cap, 64, 64);
+    if (H > 0) {
+        make_map(&m[kHactK], h->Hact, H, cap, 64, 128);
+        make_map(&m[kDPK], h->dP, H, cap, 64, 128);
+        make_map(&m[kHactMN], h->Hact, H, cap, 64, 64);
+        make_map(&m[kDPMN], h->dP, H, cap, 64, 64);
+    }
+    CK(cudaMemcpyAsync(h->act_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+}
+
+// Rebuilds the per-expert weight maps and pointer tables when the caller's pointers changed.
+void refresh_weights(tmt_moe* h, const void* const* Wup, const void* const* Wdown) {
+    const int E = h->local_experts;
+    const uint64_t D = h->d.dim, H = h->d.hidden;
+    bool same = (int)h->up_seen.size() == E;
+    for (int e = 0; same && e < E; ++e)
+        same = h->up_seen[e] == Wup[e] && (H == 0 || h->down_seen[e] == Wdown[e]);
+    if (same) return;
+    h->up_seen.assign(Wup, Wup + E);
+    if (H > 0) h->down_seen.assign(Wdown, Wdown + E);
+    for (int e = 0; e < E; ++e)
+        if (!Wup[e] || (H > 0 && !Wdown[e])) throw std::runtime_error("null expert weight pointer");
+    if (h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05) {
+        std::vector<CUtensorMap> m((size_t)kNumWMaps * E);
+        memset(m.data(), 0, m.size() * sizeof(CUtensorMap));
+        for (int e = 0; e < E; ++e) {
+            if (H > 0) {
+                make_map(&m[kUpK * E + e], Wup[e], D, H, 64, (uint32_t)std::min<uint64_t>(256, H));       // [H][D], k = D
+                make_map(&m[kDownK * E + e], Wdown[e], H, D, 64, (uint32_t)std::min<uint64_t>(256, D));   // [D][H], k = H
+                make_map(&m[kDownMN * E + e], Wdown[e], H, D, 64, 64);    // dH: k = rows (D), n = H contiguous
+                make_map(&m[kUpMN * E + e], Wup[e], D, H, 64, 64);        // dXg: k = rows (H), n = D contiguous
+            } else {
+                make_map(&m[kUpK * E + e], Wup[e], D, D, 64, (uint32_t)std::min<uint64_t>(256, D));
+                make_map(&m[kUpMN * E + e], Wup[e], D, D, 64, 64);
+            }
+        }
+        CK(cudaMemcpyAsync(h->w_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+    }
+    CK(cudaMemcpyAsync(h->up_ptrs, Wup, E * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
+    if (H > 0) CK(cudaMemcpyAsync(h->down_ptrs, Wdown, E * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
+}
+
+void refresh_grads(tmt_moe* h, float* const* dWup, float* const* dWdown) {
+    const int E = h->local_experts;
+    const bool two = h->d.hidden > 0;
+    bool same = (int)h->gup_seen.size() == E;
+    for (int e = 0; same && e < E; ++e) same = h->gup_seen[e] == dWup[e] && (!two || h->gdown_seen[e] == dWdown[e]);
+    if (same) return;
+    for (int e = 0; e < E; ++e)
+        if (!dWup[e] || (two && !dWdown[e])) throw std::runtime_error("null expert gradient pointer");
+    h->gup_seen.assign(dWup, dWup + E);
+    CK(cudaMemcpyAsync(h->gup_ptrs, dWup, E * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
+    if (two) {
+        h->gdown_seen.assign(dWdown, dWdown + E);
+        CK(cudaMemcpyAsync(h->gdown_ptrs, dWdown, E * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
+    }
+}
+
+GemmParams base_params(tmt_moe* h) {
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.experts = h->local_experts;
+    p.tile_expert = h->rb.tile_expert;
+    p.num_m_tiles = h->rb.num_m_tiles;
+    p.poff = h->rb.poff;
+    p.status = h->rb.status;
+    p.a_boxes = 1; p.b_boxes = 1; p.a_box_step = 64; p.b_box_step = 64;
+    return p;
+}
+
+// C[rows, N] = A[rows, K] * W_e (k-major W_e[N][K] or mn-major W_e[K][N])
+GemmParams rows_gemm(tmt_moe* h, ActMap a, const uint16_t* A, WMap w, const uint16_t* const* Wptrs, bool w_mn, int N, int K,
+                     int epi) {
+    GemmParams p = base_params(h);
+    p.mode = kRowsRagged;
+    p.mapA = h->act_maps + a; p.a_stride = 0;
+    p.mapB = h->w_maps + (size_t)w * h->local_experts; p.b_stride = 1;
+    p.A = A; p.lda = K; p.Bexp = Wptrs; p.ldb = w_mn ? N : K;
+    p.a_mn = 0; p.b_mn = w_mn;
+    p.N = N; p.K = K; p.epi = epi; p.ldc = N;
+    if (w_mn) { p.b_boxes = kBN / 64; p.tx_bytes = kBM * kBK * 2 + p.b_boxes * 8192; }
+    else p.tx_bytes = kBM * kBK * 2 + (uint32_t)std::min(kBN, N) * kBK * 2;
+    return p;
+}
+
+// C_e[M, N] = sum over the group's rows of A[r, M] * B[r, N]
+GemmParams red_gemm(tmt_moe* h, ActMap a, const uint16_t* A, int M, ActMap b, const uint16_t* B, int N, float* const* out) {
+    GemmParams p = base_params(h);
+    p.mode = kRedRagged;
+    p.mapA = h->act_maps + a; p.a_stride = 0;
+    p.mapB = h->act_maps + b; p.b_stride = 0;
+    p.A = A; p.lda = M; p.B = B; p.ldb = N;
+    p.a_mn = 1; p.b_mn = 1;
+    p.a_boxes = kBM / 64; p.b_boxes = kBN / 64;
+    p.tx_bytes = (p.a_boxes + p.b_boxes) * 8192;
+    p.M = M; p.N = N; p.epi = kEpiF32; p.outF = out; p.ldc = N;
+    return p;
+}
+
+void run_gemm(tmt_moe* h, const GemmParams& p) {
+    if (h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05) CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+    else CK(launch_gemm_simt(p, h->dims.max_tiles, h->stream));
+    h->launches += 1;
+}
+
+void check_tokens(tmt_moe* h, int tokens) {
+    if (tokens < 1 || tokens > h->d.tokens) throw std::runtime_error("tokens outside [1, desc.tokens]");
+}
+
+}  // namespace
+
+void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
+                  float beta, int tokens) {
+    check_tokens(h, tokens);
+    if (!X || !Wr || !Wup || !Y || (h->d.hidden > 0 && !Wdown)) throw std::runtime_error("null argument");
+    CK(cudaSetDevice(h->d.device));
+    const int D = h->d.dim, H = h->d.hidden;
+    h->dims.T = tokens;
+    h->last_tokens = tokens;
+    refresh_weights(h, Wup, Wdown);
+    const uint16_t* Xb = static_cast<const uint16_t*>(X);
+    CK(launch_router(h->dims, h->rb, Xb, Wr, h->has_bias ? h->bias : nullptr, h->stream));
+    CK(launch_scan(h->dims, h->rb, h->stream));
+    CK(launch_dispatch(h->dims, h->rb, Xb, h->Xg, h->stream));
+    h->launches += 3;
+    if (H > 0) {
+        GemmParams up = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, H, D, kEpiUp);
+        up.out0 = h->d.training ? h->P : nullptr;
+        up.out1 = h->Hact;
+        if (h->q_expert_scales) up.expert_scale = h->q_scales;
+        run_gemm(h, up);
+        GemmParams down = rows_gemm(h, kHactK, h->Hact, kDownK, h->down_ptrs, false, D, H, kEpiDown);
+        down.out0 = h->Yg;
+        down.row_scale = h->rb.slotw;
+        if (h->q_expert_scales) down.expert_scale = h->q_scales + h->d.experts;
+        run_gemm(h, down);
+    } else {
+        GemmParams g = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, D, D, kEpiBf16);
+        g.out0 = h->Yg;
+        run_gemm(h, g);
+    }
+    CK(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, H == 0, h->stream));
+    h->launches += 1;
+    h->have_forward = true;
+}
+
+void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
+                   float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef) {
+    if (!h->d.training) throw std::runtime_error("handle was created with training = 0");
+    if (!h->have_forward) throw std::runtime_error("backward without a preceding forward");
+    if (!dY || !Wr || !Wup || !dWr || !dWup || !dX || (h->d.hidden > 0 && (!Wdown || !dWdown)))
+        throw std::runtime_error("null argument");
+    CK(cudaSetDevice(h->d.device));
+    const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
+    refresh_weights(h, Wup, Wdown);
+    refresh_grads(h, dWup, dWdown);
+    const uint16_t* dYb = static_cast<const uint16_t*>(dY);
+    CK(launch_grad_dispatch(h->dims, h->rb, dYb, h->Yg, h->dYg, h->s_j, H == 0, h->stream));
+    h->launches += 1;
+    if (H > 0) {
+        GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
+        dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
+        run_gemm(h, dh);
+        run_gemm(h, red_gemm(h, kDYgMN, h->dYg, D, kHactMN, h->Hact, H, h->gdown_ptrs));
+        run_gemm(h, red_gemm(h, kDPMN, h->dP, H, kXgMN, h->Xg, D, h->gup_ptrs));
+        GemmParams dx = rows_gemm(h, kDPK, h->dP, kUpMN, h->up_ptrs, true, D, H, kEpiBf16);
+        dx.out0 = h->dXg;
+        run_gemm(h, dx);
+    } else {
+        run_gemm(h, red_gemm(h, kDYgMN, h->dYg, D, kXgMN, h->Xg, D, h->gup_ptrs));
+        GemmParams dx = rows_gemm(h, kDYgK, h->dYg, kUpMN, h->up_ptrs, true, D, D, kEpiBf16);
+        dx.out0 = h->dXg;
+        run_gemm(h, dx);
+    }
+    if (E > 1) {
+        CK(launch_router_bwd(h->dims, h->rb, H > 0 ? h->sw_part : nullptr, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, h->stream));
+        CK(launch_router_dw(h->dims, h->rb, h->dlogits, h->Xg, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
+        h->launches += 3;
+    } else {
+        CK(cudaMemsetAsync(dWr, 0, (size_t)E * D * sizeof(float), h->stream));
+    }
+    CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, h->dXg, static_cast<uint16_t*>(dX), h->stream));
+    h->launches += 1;
+}
+
+tmt_moe* create_impl(const tmt_moe_desc* dsc) {
+    const tmt_moe_desc& d = *dsc;
+    if (d.tokens < 1 || d.dim < 64 || d.dim % 64 || d.hidden < 0 || d.hidden % 64)
+        throw std::runtime_error("need tokens >= 1, dim and hidden multiples of 64");
+    if (d.experts < 1 || d.experts > 256 || d.topk < 1 || d.topk > d.experts || d.topk > 8)
+        throw std::runtime_error("require 1 <= topk <= experts <= 256 and topk <= 8");
+    if (d.ep_world < 1 || d.ep_rank < 0 || d.ep_rank >= d.ep_world || d.experts % d.ep_world)
+        throw std::runtime_error("invalid expert-parallel layout (experts must divide by ep_world)");
+    if ((long)d.tokens * d.topk + 128L * d.experts > 0x7fffff00L)
+        throw std::runtime_error("tokens * topk exceeds the supported index range");
+    CK(cudaSetDevice(d.device));
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, d.device));
+    if (prop.major != 10) throw std::runtime_error("this library is built for sm_100a (B200) only");
+    std::unique_ptr<tmt_moe, void (*)(tmt_moe*)> hold(new tmt_moe(), [](tmt_moe* p) { tmt_moe_destroy(p); });
+    tmt_moe* h = hold.get();
+    h->d = d;
+    h->stream = static_cast<cudaStream_t>(d.stream);
+    h->num_sms = prop.multiProcessorCount;
+    h->local_experts = d.experts / d.ep_world;
+    const int T = d.tokens, E = d.experts, K = d.topk, D = d.dim, H = d.hidden;
+    // rows of the grouped buffers: every assignment plus up to kPad-1 pad rows per expert (moe.cu:331)
+    const long cap = ((long)T * K + kPad - 1) / kPad * kPad + (long)kPad * E;
+    h->dims = RouteDims{T, D, E, K, (int)cap, (int)(cap / kPad), d.router_dtype == TMT_MOE_F32};
+    const int NB = (T + kTokBlock - 1) / kTokBlock;
+    RouteBufs& b = h->rb;
+    b.logits = dalloc<float>(h, (size_t)T * E);
+    b.probs = dalloc<float>(h, (size_t)T * E);
+    b.lse = dalloc<float>(h, T);
+    b.idx = dalloc<int>(h, (size_t)T * K);
+    b.w = dalloc<float>(h, (size_t)T * K);
+    b.rank = dalloc<int>(h, (size_t)NB * kTokBlock * K);
+    b.block_counts = dalloc<int>(h, (size_t)NB * E);
+    b.block_sump = dalloc<float>(h, (size_t)NB * E);
+    b.block_z = dalloc<float>(h, NB);
+    b.block_base = dalloc<int>(h, (size_t)NB * E);
+    b.counts = dalloc<int>(h, E);
+    b.off = dalloc<int>(h, E + 1);
+    b.poff = dalloc<int>(h, E + 1);
+    b.tile_expert = dalloc<int>(h, cap / kPad);
+    b.num_m_tiles = dalloc<int>(h, 1);
+    b.stat = dalloc<float>(h, E + 1);
+    b.slot_of = dalloc<int>(h, (size_t)T * K);
+    b.slotw = dalloc<float>(h, cap);
+    b.tok_of_slot = dalloc<int>(h, cap);
+    b.status = dalloc<int>(h, 1);
+    CK(cudaMemsetAsync(b.status, 0, sizeof(int), h->stream));
+    h->bias = dalloc<float>(h, E);
+    h->Xg = dalloc<uint16_t>(h, (size_t)cap * D);
+    h->Yg = dalloc<uint16_t>(h, (size_t)cap * D);
+    if (H > 0) h->Hact = dalloc<uint16_t>(h, (size_t)cap * H);
+    if (d.training) {
+        h->dYg = dalloc<uint16_t>(h, (size_t)cap * D);
+        h->dXg = dalloc<uint16_t>(h, (size_t)cap * D);
+        h->s_j = dalloc<float>(h, (size_t)T * K);
+        h->dlogits = dalloc<float>(h, (size_t)T * E);
+        h->dwr_partial = dalloc<float>(h, (size_t)kRouterDwChunks * E * D);
+        if (H > 0) {
+            h->P = dalloc<uint16_t>(h, (size_t)cap * H);
+            h->dP = dalloc<uint16_t>(h, (size_t)cap * H);
+            h->sw_ld = (H + kBN - 1) / kBN;
+            h->sw_part = dalloc<float>(h, (size_t)cap * h->sw_ld);
+        }
+    } else {
+        // forward-only handles still need valid map bases for the unused gradient maps
+        h->dYg = h->Xg; h->dP = h->Hact;
+    }
+    h->act_maps = dalloc<CUtensorMap>(h, kNumActMaps);
+    h->w_maps = dalloc<CUtensorMap>(h, (size_t)kNumWMaps * h->local_experts);
+    h->up_ptrs = dalloc<const uint16_t*>(h, h->local_experts);
+    h->down_ptrs = dalloc<const uint16_t*>(h, h->local_experts);
+    h->gup_ptrs = dalloc<float*>(h, h->local_experts);
+    h->gdown_ptrs = dalloc<float*>(h, h->local_experts);
+    if (d.gemm_impl == TMT_MOE_GEMM_TCGEN05) build_act_maps(h);
+    if (d.host_io) {
+        h->Xs = dalloc<uint16_t>(h, (size_t)T * D);
+        h->Ys = dalloc<uint16_t>(h, (size_t)T * D);
+        if (d.training) {
+            h->dYs = dalloc<uint16_t>(h, (size_t)T * D);
+            h->dXs = dalloc<uint16_t>(h, (size_t)T * D);
+        }
+    }
+    CK(cudaStreamSynchronize(h->stream));
+    return hold.release();
+}
+
+}  // namespace tmt
+
+using namespace tmt;
+
+#define GUARD(...)                                                     \
+    try { __VA_ARGS__; return 0; }                                     \
+    catch (const std::exception& e) { set_error("%s", e.what()); return -1; } \
+    catch (...) { set_error("unknown error"); return -1; }
+
+extern "C" {
+
+const char* tmt_moe_last_error(void) { return g_error.c_str(); }
+
+int tmt_moe_create(const tmt_moe_desc* desc, tmt_moe** out) {
+    if (!desc || !out) { set_error("null argument"); return -1; }
+    *out = nullptr;
+    GUARD(*out = create_impl(desc))
+}
+
+void tmt_moe_destroy(tmt_moe* h) {
+    if (!h) return;
+    cudaSetDevice(h->d.device);
+    cudaStreamSynchronize(h->stream);
+    ep_teardown(h);
+    for (void* p : h->allocs) cudaFree(p);
+    delete h;
+}
+
+int tmt_moe_set_router_bias(tmt_moe* h, const float* bias_host) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        CK(cudaSetDevice(h->d.device));
+        h->has_bias = bias_host != nullptr;
+        if (bias_host) {
+            CK(cudaMemcpyAsync(h->bias, bias_host, h->d.experts * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+            CK(cudaStreamSynchronize(h->stream));
+        }
+    })
+}
+
+int tmt_moe_forward(tmt_moe* h, const void* X, const void* Wrouter, const void* const* Wup, const void* const* Wdown,
+                    void* Y, float beta, int tokens) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        if (h->d.ep_world > 1) ep_forward(h, X, Wrouter, Wup, Wdown, Y, beta, tokens);
+        else forward_impl(h, X, Wrouter, Wup, Wdown, Y, beta, tokens);
+    })
+}
+
+int tmt_moe_backward(tmt_moe* h, const void* dY, const void* Wrouter, const void* const* Wup, const void* const* Wdown,
+                     float* dWrouter, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        if (h->d.ep_world > 1) ep_backward(h, dY, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, dX, aux, zcoef);
+        else backward_impl(h, dY, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, dX, aux, zcoef);
+    })
+}
+
+int tmt_moe_stats(tmt_moe* h, float* stat, int64_t* counts, float* aux) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        CK(cudaSetDevice(h->d.device));
+        const int E = h->d.experts, K = h->d.topk;
+        std::vector<float> st(E + 1);
+        std::vector<int> cn(E);
+        CK(cudaMemcpyAsync(st.data(), h->rb.stat, (E + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaMemcpyAsync(cn.data(), h->ep_world_counts ? h->ep_world_counts : h->rb.counts, E * sizeof(int),
+                           cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaStreamSynchronize(h->stream));
+        const double N = (double)h->last_tokens * h->d.ep_world;
+        if (stat) memcpy(stat, st.data(), (E + 1) * sizeof(float));
+        if (counts) for (int e = 0; e < E; ++e) counts[e] = cn[e];
+        if (aux) {
+            // moe_aux_from, moe.cu:470-475
+            float a = 0;
+            for (int e = 0; e < E; ++e) a += (st[e] / (float)N) * (cn[e] / (float)(N * K));
+            *aux = E == 1 ? 0.0f : E * a;
+        }
+    })
+}
+
+int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter, const void* const* Wup,
+                      const void* const* Wdown, float* dWrouter, float* const* dWup, float* const* dWdown, void* Y_host,
+                      void* dX_host, float* stat_host, float beta, float aux, float zcoef, int tokens) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        if (!h->Xs) throw std::runtime_error("handle was created with host_io = 0");
+        if (!X_host || !Y_host) throw std::runtime_error("null argument");
+        if (h->d.ep_world > 1) throw std::runtime_error("host step is single-GPU");
+        check_tokens(h, tokens);
+        CK(cudaSetDevice(h->d.device));
+        const size_t bytes = (size_t)tokens * h->d.dim * 2;
+        CK(cudaMemcpyAsync(h->Xs, X_host, bytes, cudaMemcpyHostToDevice, h->stream));
+        if (beta != 0.0f) CK(cudaMemcpyAsync(h->Ys, Y_host, bytes, cudaMemcpyHostToDevice, h->stream));
+        forward_impl(h, h->Xs, Wrouter, Wup, Wdown, h->Ys, beta, tokens);
+        CK(cudaMemcpyAsync(Y_host, h->Ys, bytes, cudaMemcpyDeviceToHost, h->stream));
+        if (dY_host) {
+            if (!dX_host || !h->dYs) throw std::runtime_error("backward needs dX_host and training = 1");
+            CK(cudaMemcpyAsync(h->dYs, dY_host, bytes, cudaMemcpyHostToDevice, h->stream));
+            backward_impl(h, h->dYs, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, h->dXs, aux, zcoef);
+            CK(cudaMemcpyAsync(dX_host, h->dXs, bytes, cudaMemcpyDeviceToHost, h->stream));
+        }
+        if (stat_host)
+            CK(cudaMemcpyAsync(stat_host, h->rb.stat, (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaStreamSynchronize(h->stream));
+    })
+}
+
+long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes) {
+    if (!h || !name || !dst) { set_error("null argument"); return -1; }
+    try {
+        CK(cudaSetDevice(h->d.device));
+        const size_t T = h->last_tokens, E = h->d.experts, K = h->d.topk;
+        const void* src = nullptr;
+        size_t n = 0;
+        const std::string s(name);
+        if (s == "logits") { src = h->rb.logits; n = T * E * 4; }
+        else if (s == "probs") { src = h->rb.probs; n = T * E * 4; }
+        else if (s == "idx") { src = h->rb.idx; n = T * K * 4; }
+        else if (s == "slot_of") { src = h->rb.slot_of; n = T * K * 4; }
+        else if (s == "w") { src = h->rb.w; n = T * K * 4; }
+        else if (s == "lse") { src = h->rb.lse; n = T * 4; }
+        else if (s == "counts") { src = h->rb.counts; n = E * 4; }
+        else if (s == "poff") { src = h->rb.poff; n = (E + 1) * 4; }
+        else if (s == "dlogits") { src = h->dlogits; n = T * E * 4; }
+        else if (s == "s_j") { src = h->s_j; n = T * K * 4; }
+        else if (s == "cap") { n = 4; int cap = h->dims.cap; if (dst_bytes < 4) throw std::runtime_error("destination too small"); memcpy(dst, &cap, 4); return 4; }
+        else if (s == "slotw") { src = h->rb.slotw; n = (size_t)h->dims.cap * 4; }
+        else if (s == "tok_of_slot") { src = h->rb.tok_of_slot; n = (size_t)h->dims.cap * 4; }
+        else if (s == "tile_expert") { src = h->rb.tile_expert; n = (size_t)h->dims.max_tiles * 4; }
+        else if (s == "num_m_tiles") { src = h->rb.num_m_tiles; n = 4; }
+        // grouped activations, all cap rows (debugging / cross-checks; cap comes from "cap")
+        else if (s == "Xg") { src = h->Xg; n = (size_t)h->dims.cap * h->d.dim * 2; }
+        else if (s == "Yg") { src = h->Yg; n = (size_t)h->dims.cap * h->d.dim * 2; }
+        else if (s == "dYg") { src = h->d.training ? h->dYg : nullptr; n = (size_t)h->dims.cap * h->d.dim * 2; }
+        else if (s == "dXg") { src = h->dXg; n = (size_t)h->dims.cap * h->d.dim * 2; }
+        else if (s == "P") { src = h->P; n = (size_t)h->dims.cap * h->d.hidden * 2; }
+        else if (s == "Hact") { src = h->Hact; n = (size_t)h->dims.cap * h->d.hidden * 2; }
+        else if (s == "dP") { src = h->d.training ? h->dP : nullptr; n = (size_t)h->dims.cap * h->d.hidden * 2; }
+        else if (s == "sw_part") { src = h->sw_part; n = (size_t)h->dims.cap * h->sw_ld * 4; }
+        else throw std::runtime_error("unknown tensor name: " + s);
+        if (!src) throw std::runtime_error("tensor not kept by this handle: " + s);
+        if (n > dst_bytes) throw std::runtime_error("destination too small for " + s);
+        CK(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaStreamSynchronize(h->stream));
+        return (long long)n;
+    } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
+}
+
+long long tmt_moe_launch_count(const tmt_moe* h) { return h ? h->launches : -1; }
+
+int tmt_moe_device_status(tmt_moe* h) {
+    if (!h) { set_error("null handle"); return -1; }
+    int v = -1;
+    cudaSetDevice(h->d.device);
+    if (cudaMemcpyAsync(&v, h->rb.status, sizeof v, cudaMemcpyDeviceToHost, h->stream) != cudaSuccess ||
+        cudaStreamSynchronize(h->stream) != cudaSuccess) {
+        set_error("reading the device status failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return -1;
+    }
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Internal definition of the opaque handle and of the entry points shared between the
+// translation units of the library.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/tmt_moe.h"
+#include "kernels.cuh"
+
+struct tmt_ep_state;
+
+struct tmt_moe {
+    tmt_moe_desc d{};
+    cudaStream_t stream = nullptr;
+    int num_sms = 0;
+    int local_experts = 0;
+    tmt::RouteDims dims{};
+    tmt::RouteBufs rb{};
+    float* bias = nullptr;
+    bool has_bias = false;
+    // grouped activations (cap rows): input copies, up-projection pre-activation, SiLU output,
+    // down-projection output (reference mode: pre-activation) and their gradients
+    uint16_t *Xg = nullptr, *P = nullptr, *Hact = nullptr, *Yg = nullptr;
+    uint16_t *dYg = nullptr, *dP = nullptr, *dXg = nullptr;
+    float* sw_part = nullptr; int sw_ld = 0;
+    float *s_j = nullptr, *dlogits = nullptr, *dwr_partial = nullptr;
+    CUtensorMap* act_maps = nullptr;
+    CUtensorMap* w_maps = nullptr;
+    const uint16_t** up_ptrs = nullptr; const uint16_t** down_ptrs = nullptr;
+    float** gup_ptrs = nullptr; float** gdown_ptrs = nullptr;
+    std::vector<const void*> up_seen, down_seen;
+    std::vector<float*> gup_seen, gdown_seen;
+    // staging for the host-buffer entry point
+    uint16_t *Xs = nullptr, *Ys = nullptr, *dYs = nullptr, *dXs = nullptr;
+    // NVFP4 scratch: dequantised bf16 weights and per-expert tensor scales
+    uint16_t* q_up = nullptr; uint16_t* q_down = nullptr; float* q_scales = nullptr;
+    std::vector<const void*> q_ptrs_host;
+    bool q_expert_scales = false;   // forward applies q_scales[e] / q_scales[E+e] to the accumulators
+    // expert parallelism
+    tmt_ep_state* ep = nullptr;
+    int* ep_world_counts = nullptr;
+    long long launches = 0;
+    int last_tokens = 0;
+    bool have_forward = false;
+    size_t bytes = 0;
+    std::vector<void*> allocs;
+};
+
+namespace tmt {
+void set_error(const char* fmt, ...);
+void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
+                  float beta, int tokens);
+void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
+                   float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef);
+void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
+                float beta, int tokens);
+void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
+                 float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef);
+void ep_teardown(tmt_moe* h);
+}  // namespace tmt

@@ -1,0 +1,397 @@
+// Dispatch / combine and their backward twins: one warp per token row, 16-byte vector
+// loads and stores, every row of X / Y / dY / dX read or written exactly once and the K
+// grouped rows of a token touched once each. Replaces fill_kernel, gather_slot_kernel (and
+// the memset before it), combine_kernel, combine_bwd_kernel, sdot_kernel,
+// router_bwd_kernel, to_bf16_kernel, the two skinny router GEMMs and scatter_add_kernel of
+// tmt-cuda/src/moe.cu:103-249, 513-531.
+#include "kernels.cuh"
+
+namespace tmt {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kMaxK = 8;
+
+__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
+    f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
+    f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack_bf2(f[0], f[1]), pack_bf2(f[2], f[3]), pack_bf2(f[4], f[5]), pack_bf2(f[6], f[7]));
+}
+
+// Blocks [0, tok_blocks) handle tokens; blocks [tok_blocks, tok_blocks + E) zero the pad rows
+// of expert (blockIdx - tok_blocks). The offset table (padded group starts and this router
+// block's per-expert base) is staged in shared memory.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) dispatch_kernel(const RouteDims d, const RouteBufs b,
+                                                                        const uint16_t* __restrict__ X,
+                                                                        uint16_t* __restrict__ Xg, int tok_blocks) {
+    extern __shared__ int table[];     // [E] poff + block_base of the router block these 8 tokens belong to
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nvec = d.D >> 3;
+    if ((int)blockIdx.x >= tok_blocks) {
+        const int e = blockIdx.x - tok_blocks;
+        const int r0 = b.poff[e] + b.counts[e], r1 = b.poff[e + 1];
+        for (int r = r0 + warp; r < r1; r += kWarpsPerBlock) {
+            if (r >= d.cap) { report(b.status, kErrSlotRange); break; }
+            for (int v = lane; v < nvec; v += 32) stg16(Xg + (long)r * d.D + v * 8, make_uint4(0, 0, 0, 0));
+            if (lane == 0) { b.slotw[r] = 0.0f; b.tok_of_slot[r] = -1; }
+        }
+        return;
+    }
+    // kTokBlock is a multiple of the 8 tokens of this block, so one router block covers them all
+    const long t0 = (long)blockIdx.x * kWarpsPerBlock;
+    const int rb = (int)(t0 / kTokBlock);
+    for (int e = threadIdx.x; e < d.E; e += blockDim.x) table[e] = b.poff[e] + b.block_base[(long)rb * d.E + e];
+    __syncthreads();
+    const long t = t0 + warp;
+    if (t >= d.T) return;
+    int slot = -1;
+    if (lane < d.K) {
+        const int e = b.idx[t * d.K + lane];
+        if (e < 0 || e >= d.E) report(b.status, kErrSlotRange);
+        else {
+            slot = table[e] + b.rank[t * d.K + lane];
+            if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+            else {
+                b.slot_of[t * d.K + lane] = slot;
+                b.slotw[slot] = b.w[t * d.K + lane];
+                b.tok_of_slot[slot] = (int)t;
+            }
+        }
+    }
+    int slots[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) slots[j] = __shfl_sync(0xffffffffu, slot, j);
+    const uint16_t* src = X + t * d.D;
+    for (int v = lane; v < nvec; v += 32) {
+        const uint4 x = ldg16(src + v * 8);
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j)
+            if (j < d.K && slots[j] >= 0) stg16(Xg + (long)slots[j] * d.D + v * 8, x);
+    }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const RouteDims d, const RouteBufs b,
+                                                                       const uint16_t* __restrict__ Yg,
+                                                                       uint16_t* __restrict__ Y, float beta,
+                                                                       int silu_in_combine) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
+    if (t >= d.T) return;
+    int slot = -1; float wj = 0.0f;
+    if (lane < d.K) {
+        slot = b.slot_of[t * d.K + lane];
+        if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+        else wj = b.slotw[slot];
+    }
+    int slots[kMaxK]; float ws[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) { slots[j] = __shfl_sync(0xffffffffu, slot, j); ws[j] = __shfl_sync(0xffffffffu, wj, j); }
+    const int nvec = d.D >> 3;
+    uint16_t* dst = Y + t * d.D;
+    for (int v = lane; v < nvec; v += 32) {
+        float acc[8];
+        if (beta != 0.0f) {
+            unpack8(ldg16(dst + v * 8), acc);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = beta * acc[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+            if (j < d.K && slots[j] >= 0) {
+                float y[8];
+                unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), y);
+                if (silu_in_combine) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] += ws[j] * silu_f(y[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] += y[i];
+                }
+            }
+        }
+        stg16(dst + v * 8, pack8(acc));
+    }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(const RouteDims d, const RouteBufs b,
+                                                                             const uint16_t* __restrict__ dY,
+                                                                             const uint16_t* __restrict__ Yg,
+                                                                             uint16_t* __restrict__ dYg,
+                                                                             float* __restrict__ s_j, int reference_mode,
+                                                                             int tok_blocks) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nvec = d.D >> 3;
+    if ((int)blockIdx.x >= tok_blocks) {
+        const int e = blockIdx.x - tok_blocks;
+        const int r0 = b.poff[e] + b.counts[e], r1 = b.poff[e + 1];
+        for (int r = r0 + warp; r < r1 && r < d.cap; r += kWarpsPerBlock)
+            for (int v = lane; v < nvec; v += 32) stg16(dYg + (long)r * d.D + v * 8, make_uint4(0, 0, 0, 0));
+        return;
+    }
+    const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
+    if (t >= d.T) return;
+    int slot = -1; float wj = 0.0f;
+    if (lane < d.K) {
+        slot = b.slot_of[t * d.K + lane];
+        if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+        else wj = b.slotw[slot];
+    }
+    int slots[kMaxK]; float ws[kMaxK]; float sdot[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) {
+        slots[j] = __shfl_sync(0xffffffffu, slot, j); ws[j] = __shfl_sync(0xffffffffu, wj, j); sdot[j] = 0.0f;
+    }
+    const uint16_t* src = dY + t * d.D;
+    for (int v = lane; v < nvec; v += 32) {
+        float g[8];
+        unpack8(ldg16(src + v * 8), g);
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+            if (j < d.K && slots[j] >= 0) {
+                float o[8];
+                if (reference_mode) {
+                    float pre[8];
+                    unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), pre);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float sg = sigmoid_f(pre[i]);
+                        sdot[j] += g[i] * (pre[i] * sg);
+                        o[i] = (ws[j] * g[i]) * sg * (1.0f + pre[i] * (1.0f - sg));     // silu_bwd, common.h:21-24
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] = ws[j] * g[i];
+                }
+                stg16(dYg + (long)slots[j] * d.D + v * 8, pack8(o));
+            }
+        }
+    }
+    if (reference_mode) {
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+            if (j < d.K) {
+                float s = sdot[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) s_j[t * d.K + j] = s;
+            }
+        }
+    }
+}
+
+// One thread per token; dlogits doubles as scratch exactly as in moe.cu:213-221.
+__global__ void router_bwd_kernel(const RouteDims d, const RouteBufs b, const float* __restrict__ sw_part, int sw_ld,
+                                  float* __restrict__ s_j, float* __restrict__ dlogits, float aux, float zcoef) {
+    const long r = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= d.T) return;
+    const int E = d.E, K = d.K;
+    const float* probs = b.probs + r * E;
+    float* g = dlogits + r * E;
+    const float nk = (float)((long)d.T * K);
+    if (sw_part) {
+        // dH-GEMM partials hold w * dL/dw; one per 256-column tile, added in tile order
+        for (int j = 0; j < K; ++j) {
+            const int slot = b.slot_of[r * K + j];
+            float s = 0.0f;
+            for (int q = 0; q < sw_ld; ++q) s += sw_part[(long)slot * sw_ld + q];
+            const float wj = b.slotw[slot];
+            s_j[r * K + j] = wj > 0.0f ? s / wj : 0.0f;
+        }
+    }
+    float Z = 0, sp = 0;
+    for (int j = 0; j < K; ++j) {
+        const float p = probs[b.idx[r * K + j]];
+        Z += p; sp += s_j[r * K + j] * p;
+    }
+    const float Z2 = Z * Z + 1e-12f;
+    for (int e = 0; e < E; ++e) g[e] = 0;
+    for (int j = 0; j < K; ++j) g[b.idx[r * K + j]] = (s_j[r * K + j] * Z - sp) / Z2;
+    float acc = 0;
+    for (int e = 0; e < E; ++e) acc += g[e] * probs[e];
+    float expected = 0;
+    for (int e = 0; e < E; ++e) {
+        g[e] = probs[e] * (g[e] - acc);
+        expected += probs[e] * b.counts[e] / nk;
+    }
+    const float lse = b.lse[r];
+    for (int e = 0; e < E; ++e) {
+        const float p = probs[e];
+        g[e] += aux * E / d.T * p * (b.counts[e] / nk - expected) + zcoef * 2.f / d.T * lse * p;
+    }
+}
+
+// Partial router weight gradient of one token chunk: block = 256 threads x 2 columns.
+template <int EC>
+__global__ void __launch_bounds__(256) router_dw_kernel(const RouteDims d, const RouteBufs b,
+                                                         const float* __restrict__ dlogits,
+                                                         const uint16_t* __restrict__ Xg, float* __restrict__ partial,
+                                                         int chunks) {
+    __shared__ float dl[32 * 64];      // 32 tokens x EC (<= 64) rounded gradients
+    __shared__ int srow[32];
+    const int d0 = (blockIdx.x * 256 + threadIdx.x) * 2;
+    const int chunk = blockIdx.y;
+    const long per = (d.T + chunks - 1) / chunks;
+    const long tbeg = chunk * per, tend = min((long)d.T, tbeg + per);
+    const bool dok = d0 < d.D;
+    for (int ec0 = 0; ec0 < d.E; ec0 += EC) {
+        float a0[EC], a1[EC];
+#pragma unroll
+        for (int e = 0; e < EC; ++e) { a0[e] = 0.0f; a1[e] = 0.0f; }
+        for (long tb = tbeg; tb < tend; tb += 32) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < 32 * EC; i += 256) {
+                const int tt = i / EC, e = i - tt * EC;
+                const long t = tb + tt;
+                dl[tt * EC + e] = (t < tend && ec0 + e < d.E) ? round_bf(dlogits[t * d.E + ec0 + e]) : 0.0f;
+            }
+            if (threadIdx.x < 32) {
+                const long t = tb + threadIdx.x;
+                srow[threadIdx.x] = t < tend ? b.slot_of[t * d.K] : -1;
+            }
+            __syncthreads();
+            if (dok) {
+                for (int tt = 0; tt < 32; ++tt) {
+                    const int row = srow[tt];
+                    if (row < 0) break;
+                    const uint32_t xv = __ldg(reinterpret_cast<const uint32_t*>(Xg + (long)row * d.D + d0));
+                    const float x0 = bf_lo(xv), x1 = bf_hi(xv);
+#pragma unroll
+                    for (int e = 0; e < EC; ++e) {
+                        const float gq = dl[tt * EC + e];
+                        a0[e] += gq * x0; a1[e] += gq * x1;
+                    }
+                }
+            }
+        }
+        if (dok) {
+#pragma unroll
+            for (int e = 0; e < EC; ++e)
+                if (ec0 + e < d.E) {
+                    float* dst = partial + ((long)chunk * d.E + ec0 + e) * d.D + d0;
+                    dst[0] = a0[e]; dst[1] = a1[e];
+                }
+        }
+    }
+}
+
+__global__ void router_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dWr, long n, int chunks) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = 0.0f;
+    for (int c = 0; c < chunks; ++c) s += partial[(long)c * n + i];
+    dWr[i] = s;
+}
+
+template <bool WF32>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) scatter_kernel(const RouteDims d, const RouteBufs b,
+                                                                       const float* __restrict__ dlogits,
+                                                                       const void* __restrict__ Wr,
+                                                                       const uint16_t* __restrict__ dXg,
+                                                                       uint16_t* __restrict__ dX) {
+    extern __shared__ float dls[];     // [warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
+    if (t >= d.T) return;
+    float* mine = dls + warp * d.E;
+    const bool router = d.E > 1;       // dense shortcut has no router gradient (moe.cu:488-494)
+    if (router)
+        for (int e = lane; e < d.E; e += 32) mine[e] = round_bf(dlogits[t * d.E + e]);
+    int slot = -1;
+    if (lane < d.K) {
+        slot = b.slot_of[t * d.K + lane];
+        if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+    }
+    int slots[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) slots[j] = __shfl_sync(0xffffffffu, slot, j);
+    __syncwarp();
+    const int nvec = d.D >> 3;
+    for (int v = lane; v < nvec; v += 32) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        if (router) {
+            for (int e = 0; e < d.E; ++e) {
+                const float gq = mine[e];
+                float wv[8];
+                if constexpr (WF32) {
+                    const float4* wp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(Wr) + (long)e * d.D + v * 8);
+                    const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+                    wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+                } else {
+                    unpack8(ldg16(reinterpret_cast<const uint16_t*>(Wr) + (long)e * d.D + v * 8), wv);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += gq * wv[i];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+            if (j < d.K && slots[j] >= 0) {
+                float x[8];
+                unpack8(ldg16(dXg + (long)slots[j] * d.D + v * 8), x);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += x[i];
+            }
+        }
+        stg16(dX + t * d.D + v * 8, pack8(acc));
+    }
+}
+
+inline int tok_blocks_of(int T) { return (T + kWarpsPerBlock - 1) / kWarpsPerBlock; }
+
+}  // namespace
+
+cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s) {
+    const int tb = tok_blocks_of(d.T);
+    dispatch_kernel<<<tb + d.E, kWarpsPerBlock * 32, d.E * sizeof(int), s>>>(d, b, X, Xg, tb);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
+                           int silu_in_combine, cudaStream_t s) {
+    combine_kernel<<<tok_blocks_of(d.T), kWarpsPerBlock * 32, 0, s>>>(d, b, Yg, Y, beta, silu_in_combine);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
+                                 uint16_t* dYg, float* s_j, int reference_mode, cudaStream_t s) {
+    const int tb = tok_blocks_of(d.T);
+    grad_dispatch_kernel<<<tb + d.E, kWarpsPerBlock * 32, 0, s>>>(d, b, dY, Yg, dYg, s_j, reference_mode, tb);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
+                              float* dlogits, float aux, float zcoef, cudaStream_t s) {
+    router_bwd_kernel<<<(d.T + 127) / 128, 128, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float* dlogits, const uint16_t* Xg,
+                             float* partial, int chunks, float* dWr, cudaStream_t s) {
+    dim3 grid((d.D / 2 + 255) / 256, chunks);
+    if (d.E <= 8) router_dw_kernel<8><<<grid, 256, 0, s>>>(d, b, dlogits, Xg, partial, chunks);
+    else if (d.E <= 16) router_dw_kernel<16><<<grid, 256, 0, s>>>(d, b, dlogits, Xg, partial, chunks);
+    else if (d.E <= 32) router_dw_kernel<32><<<grid, 256, 0, s>>>(d, b, dlogits, Xg, partial, chunks);
+    else router_dw_kernel<64><<<grid, 256, 0, s>>>(d, b, dlogits, Xg, partial, chunks);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const long n = (long)d.E * d.D;
+    router_dw_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, dWr, n, chunks);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
+                           const uint16_t* dXg, uint16_t* dX, cudaStream_t s) {
+    const size_t smem = (size_t)kWarpsPerBlock * d.E * sizeof(float);
+    if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dX);
+    else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dX);
+    return cudaGetLastError();
+}
+
+}  // namespace tmt

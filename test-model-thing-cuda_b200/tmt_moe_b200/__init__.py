@@ -1,0 +1,204 @@
+"""Python front end of the B200 MoE block: a thin ctypes layer over the C ABI in
+include/tmt_moe.h (libtmt_moe_b200.so, built in-tree by build.py).
+
+The class mirrors the reference's operator interface for this path
+(tmt-cuda/src/moe.cu:330-545): create once (moe_keep_alloc + moe_ws_alloc), then
+forward / stats / backward with the same argument meaning. Tensors are anything with a
+`data_ptr()` (torch CUDA tensors) or raw integer device addresses. There is no CPU or
+library fallback: if the shared library is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+
+from . import build as _build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtmt_moe_b200.so")
+
+BF16, F32 = 0, 1
+GEMM_TCGEN05, GEMM_SIMT = 0, 1
+
+EXPORTS = (
+    "tmt_moe_create", "tmt_moe_destroy", "tmt_moe_last_error", "tmt_moe_set_router_bias",
+    "tmt_moe_forward", "tmt_moe_stats", "tmt_moe_backward", "tmt_moe_step_host", "tmt_moe_read",
+    "tmt_moe_launch_count", "tmt_moe_device_status", "tmt_moe_quantize_nvfp4",
+    "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init",
+)
+
+
+class MoeError(RuntimeError):
+    pass
+
+
+class Desc(ctypes.Structure):
+    _fields_ = [("tokens", ctypes.c_int), ("dim", ctypes.c_int), ("hidden", ctypes.c_int),
+                ("experts", ctypes.c_int), ("topk", ctypes.c_int), ("router_dtype", ctypes.c_int),
+                ("training", ctypes.c_int), ("gemm_impl", ctypes.c_int), ("device", ctypes.c_int),
+                ("host_io", ctypes.c_int), ("stream", ctypes.c_void_p), ("ep_world", ctypes.c_int),
+                ("ep_rank", ctypes.c_int)]
+
+
+class Nvfp4Weight(ctypes.Structure):
+    _fields_ = [("packed", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+                ("tensor_scale", ctypes.c_float), ("rows", ctypes.c_int), ("cols", ctypes.c_int)]
+
+
+_lib = None
+
+
+def load():
+    """Loads the shared library (never builds it implicitly on a machine without nvcc)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise MoeError("libtmt_moe_b200.so is missing: run `python -m tmt_moe_b200.build` "
+                       "(or __graft_entry__.build()) first; there is no fallback path")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.tmt_moe_last_error.restype = ctypes.c_char_p
+    lib.tmt_moe_read.restype = ctypes.c_longlong
+    lib.tmt_moe_launch_count.restype = ctypes.c_longlong
+    lib.tmt_moe_destroy.restype = None
+    for name in EXPORTS:
+        getattr(lib, name)
+    _lib = lib
+    return lib
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return ctypes.c_void_p(x)
+    if hasattr(x, "data_ptr"):
+        return ctypes.c_void_p(x.data_ptr())
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data_as(ctypes.c_void_p)
+    raise TypeError("expected a tensor, a numpy array or an address, got %r" % type(x))
+
+
+def _ptr_array(xs):
+    if xs is None:
+        return None
+    arr = (ctypes.c_void_p * len(xs))()
+    for i, x in enumerate(xs):
+        arr[i] = _ptr(x).value
+    return arr
+
+
+def _check(rc, lib):
+    if rc != 0:
+        raise MoeError(lib.tmt_moe_last_error().decode())
+
+
+class MoE:
+    """One MoE layer's state (the reference's MoeKeep + MoeWs)."""
+
+    def __init__(self, tokens, dim, experts, topk, hidden=0, router_dtype=BF16, training=True,
+                 gemm_impl=GEMM_TCGEN05, device=0, host_io=False, stream=None, ep_world=1, ep_rank=0):
+        self.lib = load()
+        self.desc = Desc(tokens, dim, hidden, experts, topk, router_dtype, int(training), gemm_impl, device,
+                         int(host_io), stream, ep_world, ep_rank)
+        self.h = ctypes.c_void_p()
+        _check(self.lib.tmt_moe_create(ctypes.byref(self.desc), ctypes.byref(self.h)), self.lib)
+        self.tokens, self.dim, self.hidden, self.experts, self.topk = tokens, dim, hidden, experts, topk
+        self._keep = None
+
+    def close(self):
+        if getattr(self, "h", None) is not None and self.h.value:
+            self.lib.tmt_moe_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_router_bias(self, bias):
+        import numpy as np
+        arr = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        _check(self.lib.tmt_moe_set_router_bias(self.h, _ptr(arr)), self.lib)
+
+    def forward(self, X, Wrouter, Wup, Wdown, Y, beta=0.0, tokens=None):
+        t = self.tokens if tokens is None else tokens
+        up, down = _ptr_array(Wup), _ptr_array(Wdown)
+        self._keep = (up, down)
+        _check(self.lib.tmt_moe_forward(self.h, _ptr(X), _ptr(Wrouter), up, down, _ptr(Y), ctypes.c_float(beta), t),
+               self.lib)
+
+    def backward(self, dY, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, dX, aux=0.0, zcoef=0.0):
+        _check(self.lib.tmt_moe_backward(self.h, _ptr(dY), _ptr(Wrouter), _ptr_array(Wup), _ptr_array(Wdown),
+                                         _ptr(dWrouter), _ptr_array(dWup), _ptr_array(dWdown), _ptr(dX),
+                                         ctypes.c_float(aux), ctypes.c_float(zcoef)), self.lib)
+
+    def step_host(self, X_host, dY_host, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, Y_host, dX_host, stat_host,
+                  beta=0.0, aux=0.0, zcoef=0.0, tokens=None):
+        t = self.tokens if tokens is None else tokens
+        _check(self.lib.tmt_moe_step_host(self.h, _ptr(X_host), _ptr(dY_host), _ptr(Wrouter), _ptr_array(Wup),
+                                          _ptr_array(Wdown), _ptr(dWrouter), _ptr_array(dWup), _ptr_array(dWdown),
+                                          _ptr(Y_host), _ptr(dX_host), _ptr(stat_host), ctypes.c_float(beta),
+                                          ctypes.c_float(aux), ctypes.c_float(zcoef), t), self.lib)
+
+    def stats(self):
+        """Returns (stat[E+1], counts[E], aux) as numpy arrays / float (moe_aux_from, moe.cu:470-475)."""
+        import numpy as np
+        stat = np.zeros(self.experts + 1, np.float32)
+        counts = np.zeros(self.experts, np.int64)
+        aux = ctypes.c_float(0)
+        _check(self.lib.tmt_moe_stats(self.h, _ptr(stat), _ptr(counts), ctypes.byref(aux)), self.lib)
+        return stat, counts, aux.value
+
+    def read(self, name, tokens=None):
+        import numpy as np
+        t = self.tokens if tokens is None else tokens
+        E, K = self.experts, self.topk
+        shapes = {"logits": ((t, E), np.float32), "probs": ((t, E), np.float32), "idx": ((t, K), np.int32),
+                  "slot_of": ((t, K), np.int32), "w": ((t, K), np.float32), "lse": ((t,), np.float32),
+                  "counts": ((E,), np.int32), "poff": ((E + 1,), np.int32), "dlogits": ((t, E), np.float32),
+                  "s_j": ((t, K), np.float32)}
+        if name not in shapes:
+            cap = np.zeros(1, np.int32)
+            self.lib.tmt_moe_read(self.h, b"cap", _ptr(cap), ctypes.c_size_t(4))
+            cap = int(cap[0])
+            D, H = self.dim, self.hidden
+            shapes.update({"slotw": ((cap,), np.float32), "tok_of_slot": ((cap,), np.int32),
+                           "tile_expert": ((cap // 128,), np.int32), "num_m_tiles": ((1,), np.int32),
+                           "Xg": ((cap, D), np.uint16), "Yg": ((cap, D), np.uint16), "dYg": ((cap, D), np.uint16),
+                           "dXg": ((cap, D), np.uint16), "P": ((cap, H), np.uint16), "Hact": ((cap, H), np.uint16),
+                           "dP": ((cap, H), np.uint16), "sw_part": ((cap, (H + 255) // 256), np.float32)})
+        shape, dt = shapes[name]
+        out = np.empty(shape, dt)
+        n = self.lib.tmt_moe_read(self.h, name.encode(), _ptr(out), ctypes.c_size_t(out.nbytes))
+        if n < 0:
+            raise MoeError(self.lib.tmt_moe_last_error().decode())
+        assert n == out.nbytes, (n, out.nbytes)
+        return out
+
+    def forward_nvfp4(self, X, Wrouter, Wup, Wdown, Y, beta=0.0, tokens=None):
+        """Wup / Wdown: lists of (packed, scales, tensor_scale, rows, cols)."""
+        t = self.tokens if tokens is None else tokens
+
+        def arr(ws):
+            a = (Nvfp4Weight * len(ws))()
+            for i, (p, s, ts, r, c) in enumerate(ws):
+                a[i] = Nvfp4Weight(_ptr(p), _ptr(s), ts, r, c)
+            return a
+        _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), arr(Wup), arr(Wdown), _ptr(Y),
+                                              ctypes.c_float(beta), t), self.lib)
+
+    @property
+    def launch_count(self):
+        return self.lib.tmt_moe_launch_count(self.h)
+
+    def device_status(self):
+        return self.lib.tmt_moe_device_status(self.h)
+
+
+def quantize_nvfp4(W, rows, cols, packed, scales, stream=None):
+    """Quantises a bf16 device matrix; returns the per-tensor scale."""
+    lib = load()
+    ts = ctypes.c_float(0)
+    _check(lib.tmt_moe_quantize_nvfp4(_ptr(W), rows, cols, _ptr(packed), _ptr(scales), ctypes.byref(ts),
+                                      ctypes.c_void_p(stream)), lib)
+    return ts.value

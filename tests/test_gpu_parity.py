@@ -1,0 +1,215 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Tolerances (bf16 path, fp32 accumulation): routing (logits, indices, counts, offsets, slots)
+bit-exact; outputs relative L2 <= 1e-2 and max-abs <= 2e-2 * max|ref|; gradients relative L2
+<= 3e-2 per tensor (the reference's own bar, architecture_test.cu:254); aux / z relative 1e-4."""
+import numpy as np
+import pytest
+import torch
+
+import synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+M = None
+G = None
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _mods():
+    global M, G
+    import tmt_moe_b200
+    import gpu_util
+    M, G = tmt_moe_b200, gpu_util
+    assert torch.cuda.is_available()
+    O.build()
+
+
+IMPLS = [pytest.param(0, id="tcgen05"), pytest.param(1, id="simt")]
+OUT_L2, OUT_MAX, GRAD_L2 = 1e-2, 2e-2, 3e-2
+
+
+def _fwd_bwd(cfg, impl, seed=0, bias=None, beta=0.0, aux=0.1, zcoef=0.001, backward=True, w_std=0.02,
+             router_std=0.02):
+    T, D, H, E, K = cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"]
+    rf = cfg.get("router_f32", False)
+    data = synth.make(T, D, H, E, K, rf, seed=seed, need_res=beta != 0.0, w_std=w_std, router_std=router_std)
+    ref = O.forward(data["X"], data["Wr"], data["Wup"], data["Wdown"], K, Y=data.get("Y0"), beta=beta, bias=bias)
+    layer = G.Layer(data, T, D, E, K, H, rf, training=backward, gemm_impl=impl, bias=bias)
+    Y = layer.forward(data.get("Y0"), beta)
+    assert layer.moe.device_status() == 0
+    G.check_routing(layer, ref)
+    yr, yg = O.bf16_to_f32(ref["Y"]), O.bf16_to_f32(Y)
+    assert np.isfinite(yg).all()
+    assert synth.rel_l2(yg, yr) <= OUT_L2 and synth.max_rel(yg, yr) <= OUT_MAX
+    stat, counts, aux_v = layer.moe.stats()
+    np.testing.assert_array_equal(counts, ref["counts"])
+    if E > 1:
+        np.testing.assert_allclose(stat, ref["stat"], rtol=1e-4, atol=1e-6)
+        assert abs(aux_v - ref["aux"]) <= 1e-4 * abs(ref["aux"])
+    else:
+        assert aux_v == 0 and (stat == 0).all()
+    if not backward:
+        return layer, ref, None
+    rb = O.backward(ref, data["dY"], aux, zcoef)
+    g = layer.backward(data["dY"], aux, zcoef)
+    assert layer.moe.device_status() == 0
+    assert synth.rel_l2(O.bf16_to_f32(g["dX"]), O.bf16_to_f32(rb["dX"])) <= GRAD_L2
+    assert synth.rel_l2(g["dWup"], rb["dWup"]) <= GRAD_L2
+    if H > 0:
+        assert synth.rel_l2(g["dWdown"], rb["dWdown"]) <= GRAD_L2
+    if E > 1:
+        assert synth.rel_l2(g["dWr"], rb["dWr"]) <= GRAD_L2
+        np.testing.assert_allclose(layer.moe.read("s_j"), rb["s_j"], rtol=3e-2, atol=3e-2 * np.abs(rb["s_j"]).max())
+    else:
+        assert (g["dWr"] == 0).all()
+    for e in range(E):      # an expert without tokens gets an exactly zero gradient
+        if ref["counts"][e] == 0:
+            assert (g["dWup"][e] == 0).all()
+    return layer, ref, g
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("hidden", [0, 256])
+def test_small_ragged(impl, hidden):
+    """Token count that is no multiple of the 64-token router block or of 8; 5 experts."""
+    _fwd_bwd(dict(T=301, D=128, H=hidden, E=5, K=2), impl, seed=1, w_std=0.1, router_std=0.2)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_fp32_router_and_residual(impl):
+    _fwd_bwd(dict(T=512, D=256, H=320, E=8, K=2, router_f32=True), impl, seed=2, beta=1.0, w_std=0.08, router_std=0.1)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_empty_expert_and_heavy_skew(impl):
+    """Expert 2 never selected (empty group -> zero gradient); expert 0 takes a slot of every token."""
+    bias = np.array([30, 0, -1e4, 0, 0, 0], np.float32)
+    layer, ref, _ = _fwd_bwd(dict(T=700, D=128, H=128, E=6, K=2), impl, seed=3, bias=bias, w_std=0.1)
+    assert ref["counts"][2] == 0 and ref["counts"][0] == 700
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("hidden", [0, 128])
+def test_dense_shortcut(impl, hidden):
+    """experts = 1 (the reference's default config): no router gradient, no statistics."""
+    _fwd_bwd(dict(T=200, D=128, H=hidden, E=1, K=1), impl, seed=4, w_std=0.1)
+
+
+def test_tie_break_lowest_index():
+    """Identical router rows give exactly equal logits: the lowest indices must win."""
+    T, D, E, K = 130, 64, 6, 3
+    data = synth.make(T, D, 64, E, K, seed=5)
+    data["Wr"][:] = data["Wr"][0]
+    layer = G.Layer(data, T, D, E, K, 64)
+    layer.forward()
+    idx = layer.moe.read("idx")
+    assert (idx == np.array([0, 1, 2])).all()
+    ref = O.forward(data["X"], data["Wr"], data["Wup"], data["Wdown"], K)
+    G.check_routing(layer, ref)
+
+
+def test_topk4_64_experts():
+    """Config-5 routing shape at reduced size: 64 experts, top-4, fp32 router."""
+    _fwd_bwd(dict(T=1024, D=256, H=256, E=64, K=4, router_f32=True), 0, seed=6, w_std=0.08, router_std=0.1)
+
+
+def test_single_token_and_partial_batch():
+    cfg = dict(T=257, D=128, H=192, E=4, K=2)
+    data = synth.make(257, 128, 192, 4, 2, seed=7, w_std=0.1)
+    layer = G.Layer(data, 257, 128, 4, 2, 192, training=False)
+    for tokens in (1, 63, 257):
+        sub = dict(data, X=data["X"][:tokens])
+        ref = O.forward(sub["X"], data["Wr"], data["Wup"], data["Wdown"], 2)
+        Y = layer.forward(tokens=tokens)
+        G.check_routing(layer, ref, tokens)
+        assert synth.rel_l2(O.bf16_to_f32(Y), O.bf16_to_f32(ref["Y"])) <= OUT_L2
+
+
+def test_tcgen05_matches_simt_buffers():
+    """Every grouped GEMM of the tensor-core path against the independent SIMT kernel on the
+    same inputs: pre-activation, SiLU output, gated output, dP, dXg and the weight gradients."""
+    cfg = dict(T=900, D=192, H=448, E=4, K=2)
+    data = synth.make(cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"], seed=8, w_std=0.08)
+    got = {}
+    for impl in (0, 1):
+        layer = G.Layer(data, cfg["T"], cfg["D"], cfg["E"], cfg["K"], cfg["H"], gemm_impl=impl)
+        layer.forward()
+        g = layer.backward(data["dY"], 0.1, 0.001)
+        rows = int(layer.moe.read("poff")[-1])
+        bufs = {n: O.bf16_to_f32(layer.moe.read(n)[:rows]) for n in ("Xg", "P", "Hact", "Yg", "dYg", "dP", "dXg")}
+        bufs.update(dWup=g["dWup"], dWdown=g["dWdown"], sw=layer.moe.read("sw_part")[:rows].sum(1))
+        got[impl] = bufs
+        assert layer.moe.device_status() == 0
+    for n in got[0]:
+        assert np.isfinite(got[0][n]).all(), n
+        assert synth.rel_l2(got[0][n], got[1][n]) <= 4e-3, n
+
+
+def test_config1_full():
+    """Config 1 at full size, forward only, fp32 router: identical top-2 indices, outputs within
+    1e-2 relative error."""
+    _fwd_bwd(synth.CONFIGS["c1"], 0, seed=11, backward=False)
+
+
+@pytest.mark.parametrize("name,tokens", [("c2", 1024), ("c4", 2048)])
+def test_training_configs_reduced_tokens(name, tokens):
+    """Configs 2 and 4 with their true widths and expert counts on a token subsample the CPU
+    oracle finishes in seconds; config 4 with its Zipf(1.2) logit bias."""
+    cfg = dict(synth.CONFIGS[name], T=tokens)
+    bias = synth.zipf_bias(cfg["E"], 2.0) if name == "c4" else None
+    _fwd_bwd(cfg, 0, seed=12, bias=bias)
+
+
+def test_full_size_routing_and_invariants():
+    """Config 2 at full size: routing bit-exact against the oracle's router; the layer is
+    position-wise, so permuting the tokens permutes the outputs (exactly) and the weight
+    gradients agree up to summation order."""
+    cfg = synth.CONFIGS["c2"]
+    T, D, H, E, K = cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"]
+    data = synth.make(T, D, H, E, K, seed=13)
+    r = O.router(data["X"], data["Wr"], K)
+    counts, off, poff, slot_of = O.layout(r["idx"], E)
+    layer = G.Layer(data, T, D, E, K, H)
+    Y = layer.forward()
+    ref = dict(r, counts=counts, poff=poff, slot_of=slot_of)
+    G.check_routing(layer, ref)
+    g = layer.backward(data["dY"], 0.1, 0.001)
+    perm = np.random.default_rng(0).permutation(T)
+    data2 = dict(data, X=data["X"][perm], dY=data["dY"][perm])
+    layer2 = G.Layer(data2, T, D, E, K, H)
+    Y2 = layer2.forward()
+    np.testing.assert_array_equal(Y2, Y[perm])
+    g2 = layer2.backward(data2["dY"], 0.1, 0.001)
+    assert synth.rel_l2(O.bf16_to_f32(g2["dX"]), O.bf16_to_f32(g["dX"][perm])) <= 2e-3
+    assert synth.rel_l2(g2["dWup"], g["dWup"]) <= 1e-3
+    assert synth.rel_l2(g2["dWdown"], g["dWdown"]) <= 1e-3
+    assert synth.rel_l2(g2["dWr"], g["dWr"]) <= 1e-3
+    assert layer.moe.device_status() == 0 and layer2.moe.device_status() == 0
+
+
+def test_deterministic_reruns():
+    cfg = dict(T=2048, D=256, H=512, E=8, K=2)
+    data = synth.make(cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"], seed=14)
+    layer = G.Layer(data, cfg["T"], cfg["D"], cfg["E"], cfg["K"], cfg["H"])
+    a = layer.forward().copy()
+    ga = layer.backward(data["dY"], 0.1, 0.001)
+    b = layer.forward().copy()
+    gb = layer.backward(data["dY"], 0.1, 0.001)
+    np.testing.assert_array_equal(a, b)
+    for k in ("dX", "dWr", "dWup", "dWdown"):
+        np.testing.assert_array_equal(ga[k], gb[k])
+
+
+def test_argument_errors():
+    with pytest.raises(M.MoeError):
+        M.MoE(64, 100, 4, 2)           # dim not a multiple of 64
+    with pytest.raises(M.MoeError):
+        M.MoE(64, 128, 4, 5)           # topk > experts (the reference rejects it too, config.h:51-52)
+    m = M.MoE(64, 128, 4, 2, hidden=128, training=False)
+    x = torch.zeros(64, 128, dtype=torch.int16, device="cuda")
+    with pytest.raises(M.MoeError):
+        m.forward(x, x, [x] * 4, [x] * 4, x, tokens=65)
+    with pytest.raises(M.MoeError):
+        m.backward(x, x, [x] * 4, [x] * 4, x, [x] * 4, [x] * 4, x)
