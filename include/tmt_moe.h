@@ -99,6 +99,16 @@ int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const
  * Returns the number of bytes written, or -1. */
 long long tmt_moe_read(tmt_moe* h, const char* name, void* dst_host, size_t dst_bytes);
 
+/* Per-phase device timing, the counterpart of the reference's TMT_PROFILE switch
+ * (moe.cu:380-394, 459-464) without its per-phase cudaDeviceSynchronize: while on, every
+ * kernel of a step is bracketed by CUDA events on the handle's stream. tmt_moe_profile
+ * synchronises, then returns accumulated milliseconds and launch counts per phase (arrays of
+ * tmt_moe_num_phases() entries, names from tmt_moe_phase_name) and optionally resets them. */
+int tmt_moe_set_profile(tmt_moe* h, int on);
+int tmt_moe_profile(tmt_moe* h, float* ms, long long* count, int reset);
+int tmt_moe_num_phases(void);
+const char* tmt_moe_phase_name(int i);
+
 /* Number of kernel launches the handle has queued since creation (the reference counts
  * nothing; used by the benchmark to report its launch count). */
 long long tmt_moe_launch_count(const tmt_moe* h);

@@ -202,11 +202,45 @@ void run_gemm(tmt_moe* h, const GemmParams& p) {
     h->launches += 1;
 }
 
+const char* const kPhaseNames[kNumPhases] = {
+    "router", "scan", "dispatch", "gemm_up", "gemm_down", "combine", "grad_dispatch", "gemm_dh", "gemm_dwdown",
+    "gemm_dwup", "gemm_dx", "router_bwd", "router_dw", "scatter", "exchange"};
+
+void prof_collect(tmt_moe* h) {
+    Profiler& pr = h->prof;
+    if (pr.marks.empty()) return;
+    CK(cudaStreamSynchronize(h->stream));
+    for (size_t i = 0; i + 1 < pr.marks.size(); ++i) {
+        const int ph = pr.marks[i].first;
+        if (ph < 0) continue;
+        float ms = 0;
+        CK(cudaEventElapsedTime(&ms, pr.pool[pr.marks[i].second], pr.pool[pr.marks[i + 1].second]));
+        pr.ms[ph] += ms;
+        pr.count[ph] += 1;
+    }
+    pr.marks.clear();
+    pr.used = 0;
+}
+
 void check_tokens(tmt_moe* h, int tokens) {
     if (tokens < 1 || tokens > h->d.tokens) throw std::runtime_error("tokens outside [1, desc.tokens]");
 }
 
 }  // namespace
+
+// Records an event that closes the previous phase and opens `phase` (-1 closes the step).
+void prof_mark(tmt_moe* h, int phase) {
+    Profiler& pr = h->prof;
+    if (!pr.on) return;
+    if (pr.used == pr.pool.size()) {
+        cudaEvent_t e;
+        CK(cudaEventCreate(&e));
+        pr.pool.push_back(e);
+    }
+    CK(cudaEventRecord(pr.pool[pr.used], h->stream));
+    pr.marks.emplace_back(phase, pr.used);
+    pr.used += 1;
+}
 
 void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
                   float beta, int tokens) {
@@ -218,8 +252,11 @@ void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* 
     h->last_tokens = tokens;
     refresh_weights(h, Wup, Wdown);
     const uint16_t* Xb = static_cast<const uint16_t*>(X);
+    prof_mark(h, kPhRouter);
     CK(launch_router(h->dims, h->rb, Xb, Wr, h->has_bias ? h->bias : nullptr, h->stream));
+    prof_mark(h, kPhScan);
     CK(launch_scan(h->dims, h->rb, h->stream));
+    prof_mark(h, kPhDispatch);
     CK(launch_dispatch(h->dims, h->rb, Xb, h->Xg, h->stream));
     h->launches += 3;
     if (H > 0) {
@@ -227,18 +264,23 @@ void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* 
         up.out0 = h->d.training ? h->P : nullptr;
         up.out1 = h->Hact;
         if (h->q_expert_scales) up.expert_scale = h->q_scales;
+        prof_mark(h, kPhGemmUp);
         run_gemm(h, up);
         GemmParams down = rows_gemm(h, kHactK, h->Hact, kDownK, h->down_ptrs, false, D, H, kEpiDown);
         down.out0 = h->Yg;
         down.row_scale = h->rb.slotw;
         if (h->q_expert_scales) down.expert_scale = h->q_scales + h->d.experts;
+        prof_mark(h, kPhGemmDown);
         run_gemm(h, down);
     } else {
         GemmParams g = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, D, D, kEpiBf16);
         g.out0 = h->Yg;
+        prof_mark(h, kPhGemmUp);
         run_gemm(h, g);
     }
+    prof_mark(h, kPhCombine);
     CK(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, H == 0, h->stream));
+    prof_mark(h, -1);
     h->launches += 1;
     h->have_forward = true;
 }
@@ -254,31 +296,42 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
     refresh_weights(h, Wup, Wdown);
     refresh_grads(h, dWup, dWdown);
     const uint16_t* dYb = static_cast<const uint16_t*>(dY);
+    prof_mark(h, kPhGradDispatch);
     CK(launch_grad_dispatch(h->dims, h->rb, dYb, h->Yg, h->dYg, h->s_j, H == 0, h->stream));
     h->launches += 1;
     if (H > 0) {
         GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
         dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
+        prof_mark(h, kPhGemmDh);
         run_gemm(h, dh);
+        prof_mark(h, kPhGemmDwDown);
         run_gemm(h, red_gemm(h, kDYgMN, h->dYg, D, kHactMN, h->Hact, H, h->gdown_ptrs));
+        prof_mark(h, kPhGemmDwUp);
         run_gemm(h, red_gemm(h, kDPMN, h->dP, H, kXgMN, h->Xg, D, h->gup_ptrs));
         GemmParams dx = rows_gemm(h, kDPK, h->dP, kUpMN, h->up_ptrs, true, D, H, kEpiBf16);
         dx.out0 = h->dXg;
+        prof_mark(h, kPhGemmDx);
         run_gemm(h, dx);
     } else {
+        prof_mark(h, kPhGemmDwUp);
         run_gemm(h, red_gemm(h, kDYgMN, h->dYg, D, kXgMN, h->Xg, D, h->gup_ptrs));
         GemmParams dx = rows_gemm(h, kDYgK, h->dYg, kUpMN, h->up_ptrs, true, D, D, kEpiBf16);
         dx.out0 = h->dXg;
+        prof_mark(h, kPhGemmDx);
         run_gemm(h, dx);
     }
     if (E > 1) {
+        prof_mark(h, kPhRouterBwd);
         CK(launch_router_bwd(h->dims, h->rb, H > 0 ? h->sw_part : nullptr, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, h->stream));
+        prof_mark(h, kPhRouterDw);
         CK(launch_router_dw(h->dims, h->rb, h->dlogits, h->Xg, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
         h->launches += 3;
     } else {
         CK(cudaMemsetAsync(dWr, 0, (size_t)E * D * sizeof(float), h->stream));
     }
+    prof_mark(h, kPhScatter);
     CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, h->dXg, static_cast<uint16_t*>(dX), h->stream));
+    prof_mark(h, -1);
     h->launches += 1;
 }
 
@@ -392,6 +445,7 @@ void tmt_moe_destroy(tmt_moe* h) {
     cudaSetDevice(h->d.device);
     cudaStreamSynchronize(h->stream);
     ep_teardown(h);
+    for (cudaEvent_t e : h->prof.pool) cudaEventDestroy(e);
     for (void* p : h->allocs) cudaFree(p);
     delete h;
 }
@@ -516,6 +570,31 @@ long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes
         return (long long)n;
     } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
 }
+
+int tmt_moe_set_profile(tmt_moe* h, int on) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        CK(cudaSetDevice(h->d.device));
+        prof_collect(h);
+        h->prof.on = on != 0;
+    })
+}
+
+int tmt_moe_profile(tmt_moe* h, float* ms, long long* count, int reset) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        CK(cudaSetDevice(h->d.device));
+        prof_collect(h);
+        for (int i = 0; i < kNumPhases; ++i) {
+            if (ms) ms[i] = (float)h->prof.ms[i];
+            if (count) count[i] = h->prof.count[i];
+            if (reset) { h->prof.ms[i] = 0; h->prof.count[i] = 0; }
+        }
+    })
+}
+
+int tmt_moe_num_phases(void) { return kNumPhases; }
+const char* tmt_moe_phase_name(int i) { return i >= 0 && i < kNumPhases ? kPhaseNames[i] : ""; }
 
 long long tmt_moe_launch_count(const tmt_moe* h) { return h ? h->launches : -1; }
 

@@ -13,6 +13,24 @@
 
 struct tmt_ep_state;
 
+namespace tmt {
+// Phases of one step, timed with CUDA events on the handle's stream when profiling is on
+// (the reference's TMT_PROFILE phases, tmt-cuda/src/moe.cu:380-394, at kernel granularity).
+enum Phase : int {
+    kPhRouter = 0, kPhScan, kPhDispatch, kPhGemmUp, kPhGemmDown, kPhCombine,
+    kPhGradDispatch, kPhGemmDh, kPhGemmDwDown, kPhGemmDwUp, kPhGemmDx, kPhRouterBwd, kPhRouterDw, kPhScatter,
+    kPhExchange, kNumPhases
+};
+struct Profiler {
+    bool on = false;
+    std::vector<cudaEvent_t> pool;
+    size_t used = 0;
+    std::vector<std::pair<int, size_t>> marks;   // (phase or -1 = end of step, event index)
+    double ms[kNumPhases] = {0};
+    long long count[kNumPhases] = {0};
+};
+}  // namespace tmt
+
 struct tmt_moe {
     tmt_moe_desc d{};
     cudaStream_t stream = nullptr;
@@ -44,6 +62,7 @@ struct tmt_moe {
     tmt_ep_state* ep = nullptr;
     int* ep_world_counts = nullptr;
     long long launches = 0;
+    tmt::Profiler prof;
     int last_tokens = 0;
     bool have_forward = false;
     size_t bytes = 0;
@@ -61,4 +80,5 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
 void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
                  float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef);
 void ep_teardown(tmt_moe* h);
+void prof_mark(tmt_moe* h, int phase);
 }  // namespace tmt

@@ -22,7 +22,8 @@ EXPORTS = (
     "tmt_moe_create", "tmt_moe_destroy", "tmt_moe_last_error", "tmt_moe_set_router_bias",
     "tmt_moe_forward", "tmt_moe_stats", "tmt_moe_backward", "tmt_moe_step_host", "tmt_moe_read",
     "tmt_moe_launch_count", "tmt_moe_device_status", "tmt_moe_quantize_nvfp4",
-    "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init",
+    "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init", "tmt_moe_set_profile",
+    "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name",
 )
 
 
@@ -59,6 +60,7 @@ def load():
     lib.tmt_moe_read.restype = ctypes.c_longlong
     lib.tmt_moe_launch_count.restype = ctypes.c_longlong
     lib.tmt_moe_destroy.restype = None
+    lib.tmt_moe_phase_name.restype = ctypes.c_char_p
     for name in EXPORTS:
         getattr(lib, name)
     _lib = lib
@@ -186,6 +188,17 @@ class MoE:
             return a
         _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), arr(Wup), arr(Wdown), _ptr(Y),
                                               ctypes.c_float(beta), t), self.lib)
+
+    def set_profile(self, on):
+        _check(self.lib.tmt_moe_set_profile(self.h, int(on)), self.lib)
+
+    def profile(self, reset=True):
+        """{phase name: (milliseconds, launches)} accumulated since the last reset."""
+        n = self.lib.tmt_moe_num_phases()
+        ms = (ctypes.c_float * n)()
+        cnt = (ctypes.c_longlong * n)()
+        _check(self.lib.tmt_moe_profile(self.h, ms, cnt, int(reset)), self.lib)
+        return {self.lib.tmt_moe_phase_name(i).decode(): (ms[i], cnt[i]) for i in range(n) if cnt[i]}
 
     @property
     def launch_count(self):
