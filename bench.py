@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark (tokens/s, forward + backward) on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5] [--impl reference]
+
+One step = one forward + backward pass of the MoE layer over one batch of seeded synthetic
+tokens (N(0,1) activations, N(0,0.02^2) weights, N(0,1e-2^2) upstream gradient), through the
+C ABI of include/tmt_moe.h. Default workload: config 5 of BASELINE.json (131072 tokens per
+GPU, dim 2048, 64 experts, top-4, expert FFN 2048->2048->2048, fp32 router), the one the
+1/2/4/8-GPU metric is quoted on; at N > 1 the experts are partitioned over the ranks (expert
+parallel, weak scaling: tokens per GPU fixed). Rank 0 prints ONE JSON line.
+
+`value` is timed with the inputs resident in HBM; `e2e` runs the same step through the
+host-buffer entry point (pinned host X / dY in, Y / dX / statistics out, copies inside the
+timed region). `roofline` is the grouped expert GEMM kernel against the measured bf16 peak;
+`cpu_baseline` times the CPU oracle (a port of the reference's math; the reference itself has
+no CPU path) on a bounded token sample of the same workload. `--impl reference` prints that
+CPU timing as its own line.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+CONFIGS = {
+    "c1": dict(T=2048, D=512, H=1024, E=4, K=2, router_f32=True, backward=False,
+               desc="config 1: tokens=2048 dim=512 experts=4 topk=2 ffn 512-1024-512, forward only, fp32 router"),
+    "c2": dict(T=16384, D=1024, H=4096, E=8, K=2, router_f32=False, backward=True,
+               desc="config 2: tokens=16384 dim=1024 experts=8 topk=2 ffn 1024-4096-1024, fwd+bwd, aux 0.1 + z-loss"),
+    "c4": dict(T=65536, D=1024, H=4096, E=16, K=2, router_f32=False, backward=True, zipf=True,
+               desc="config 4: tokens=65536 dim=1024 experts=16 topk=2 ffn 1024-4096-1024, Zipf(1.2) logit bias, fwd+bwd"),
+    "c5": dict(T=131072, D=2048, H=2048, E=64, K=4, router_f32=True, backward=True,
+               desc="config 5: tokens=131072 per GPU dim=2048 experts=64 topk=4 ffn 2048-2048-2048, fp32 router, fwd+bwd"),
+}
+AUX, ZCOEF = 0.1, 0.001
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = []
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 9 and parts[1].isdigit():
+                    rows.append(parts)
+        os.unlink(self.path)
+        if not rows:
+            return out
+        out["samples"] = len(rows)
+        out["sm_mhz"] = statistics.median(int(r[1]) for r in rows)
+        out["sm_max_mhz"] = max(int(r[2]) for r in rows)
+        try:
+            out["power_w_max"] = max(float(r[3]) for r in rows)
+        except ValueError:
+            pass
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for i, n in enumerate(names):
+            if any(r[5 + i].lower().startswith("active") for r in rows):
+                out["reasons"].append(n)
+        return out
+
+
+def cpu_sample_tokens(cfg):
+    """Token sample whose forward+backward costs the oracle roughly 4e11 flops (10-30 s of host work)."""
+    per_token = 12.0 * cfg["K"] * cfg["D"] * cfg["H"] if cfg["backward"] else 4.0 * cfg["K"] * cfg["D"] * cfg["H"]
+    s = int(4e11 / per_token)
+    s = max(256, min(cfg["T"], s // 256 * 256))
+    return s
+
+
+def run_cpu(cfg, host, sample, steps, warmup):
+    """Times the CPU oracle on the first `sample` tokens. Returns (tokens/s, threads, seconds per step)."""
+    from oracle import oracle as O
+    O.build()
+    threads = O.host_threads()
+    X = host["X"][:sample]
+    dY = host["dY"][:sample]
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        f = O.forward(X, host["Wr"], host["Wup"], host["Wdown"], cfg["K"], bias=host.get("bias"), threads=threads)
+        if cfg["backward"]:
+            O.backward(f, dY, AUX, ZCOEF, threads=threads)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    return sample / sec, threads, sec
+
+
+def make_device_data(cfg, T, local_experts, rank, torch):
+    """Seeded synthetic tensors created on the GPU (bf16 as int16 views for the C ABI)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234 + rank)
+    D, H, E = cfg["D"], cfg["H"], cfg["E"]
+
+    def bf(shape, std):
+        return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * std).to(torch.bfloat16)
+    d = {}
+    d["X"] = bf((T, D), 1.0)
+    d["dY"] = bf((T, D), 1e-2)
+    gw = torch.Generator(device="cuda")
+    gw.manual_seed(99)                      # router identical on every rank (replicated parameter)
+    wr = torch.randn((E, D), generator=gw, device="cuda", dtype=torch.float32) * 0.02
+    d["Wr"] = wr if cfg["router_f32"] else wr.to(torch.bfloat16)
+    # expert weights: one chunk per local expert, generated in slices to bound temporary memory
+    d["Wup"] = torch.empty((local_experts, H, D), device="cuda", dtype=torch.bfloat16)
+    d["Wdown"] = torch.empty((local_experts, D, H), device="cuda", dtype=torch.bfloat16)
+    for e in range(local_experts):
+        d["Wup"][e] = bf((H, D), 0.02)
+        d["Wdown"][e] = bf((D, H), 0.02)
+    d["dWr"] = torch.zeros((E, D), device="cuda", dtype=torch.float32)
+    d["dWup"] = torch.zeros((local_experts, H, D), device="cuda", dtype=torch.float32)
+    d["dWdown"] = torch.zeros((local_experts, D, H), device="cuda", dtype=torch.float32)
+    d["Y"] = torch.zeros((T, D), device="cuda", dtype=torch.bfloat16)
+    d["dX"] = torch.zeros((T, D), device="cuda", dtype=torch.bfloat16)
+    return d
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    cfg = dict(CONFIGS[args.config])
+    if args.tokens:
+        cfg["T"] = args.tokens
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus and world > 1:
+        raise SystemExit("--gpus %d does not match WORLD_SIZE %d" % (args.gpus, world))
+    T, D, H, E, K = cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"]
+    workload = cfg["desc"] + ("" if not args.tokens else " [tokens overridden to %d]" % args.tokens)
+    base = {"metric": "moe_layer_tokens_per_s_fwd_bwd" if cfg["backward"] else "moe_layer_tokens_per_s_fwd",
+            "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"}
+
+    if args.impl == "reference":
+        # The reference ships only a GPU path; its math restated on the host (oracle/) is what this arm times.
+        if rank != 0:
+            return
+        import numpy as np
+        import synth
+        sample = min(cpu_sample_tokens(cfg), 1024 if args.steps + args.warmup > 4 else 1 << 30)
+        host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
+        if cfg.get("zipf"):
+            host["bias"] = synth.zipf_bias(E, 2.0)
+        tps, threads, sec = run_cpu(cfg, host, sample, args.steps, args.warmup)
+        line = dict(base, impl="reference", value=tps, ms_per_step=sec * 1e3,
+                    config={"workload": workload, "sample_tokens_per_step": sample},
+                    cpu_baseline={"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                  "sample": "first %d tokens of the workload per step, all %d experts" % (sample, E)},
+                    e2e={"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    gpu_launches=0)
+        print(json.dumps(line), flush=True)
+        return
+
+    import torch
+    import tmt_moe_b200 as M
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    local_experts = E // world
+    d = make_device_data(cfg, T, local_experts, rank, torch)
+    stream = torch.cuda.current_stream().cuda_stream
+    moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32 if cfg["router_f32"] else M.BF16,
+                training=cfg["backward"], device=local_rank, host_io=(world == 1 and not args.no_e2e),
+                stream=stream, ep_world=world, ep_rank=rank)
+    if cfg.get("zipf"):
+        import synth
+        moe.set_router_bias(synth.zipf_bias(E, 2.0))
+    if world > 1:
+        moe.ep_init_torch(dist)
+    Wup = [d["Wup"][e] for e in range(local_experts)]
+    Wdown = [d["Wdown"][e] for e in range(local_experts)]
+    dWup = [d["dWup"][e] for e in range(local_experts)]
+    dWdown = [d["dWdown"][e] for e in range(local_experts)]
+
+    def step():
+        moe.forward(d["X"], d["Wr"], Wup, Wdown, d["Y"], 0.0)
+        if cfg["backward"]:
+            moe.backward(d["dY"], d["Wr"], Wup, Wdown, d["dWr"], dWup, dWdown, d["dX"], AUX, ZCOEF)
+
+    working_set = d["X"].numel() * 2 * (2 + 2 * K)
+    flush = working_set < 2 * L2_BYTES
+    scrub = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda") if flush else None
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    if moe.device_status() != 0:
+        raise SystemExit("device status %d after warm-up" % moe.device_status())
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = moe.launch_count
+    moe.set_profile(True)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for a, b in evs:
+        if scrub is not None:
+            scrub.zero_()
+        a.record()
+        step()
+        b.record()
+    barrier()
+    phases = moe.profile(reset=True)
+    moe.set_profile(False)
+    launches = moe.launch_count - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    status = moe.device_status()
+    if status != 0:
+        raise SystemExit("device status %d after the timed region" % status)
+    value = T * world / (ms * 1e-3)
+
+    # ---- end to end through the host-buffer entry point (single GPU) ----
+    e2e = None
+    if world == 1 and not args.no_e2e:
+        hX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+        hX.copy_(d["X"])
+        hdY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+        hdY.copy_(d["dY"])
+        hY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+        hdX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+        hstat = torch.empty(E + 1, dtype=torch.float32).pin_memory()
+        nbytes = T * D * 2
+
+        def host_step():
+            moe.step_host(hX, hdY if cfg["backward"] else None, d["Wr"], Wup, Wdown, d["dWr"], dWup, dWdown,
+                          hY, hdX if cfg["backward"] else None, hstat, 0.0, AUX, ZCOEF)
+        for _ in range(2):
+            host_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            host_step()
+        e1.record()
+        torch.cuda.synchronize()
+        e_ms = e0.elapsed_time(e1) / args.steps
+        nio = 2 if cfg["backward"] else 1
+        e2e = {"value": T / (e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nio * nbytes,
+               "d2h_bytes_per_step": nio * nbytes + (E + 1) * 4, "ms_per_step": e_ms}
+
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    pk, pk_kind = peaks()
+    A = T * K
+    gemm_names = [n for n in phases if n.startswith("gemm_")]
+    gemm_ms = sum(phases[n][0] for n in gemm_names) / args.steps
+    gemm_launches = sum(phases[n][1] for n in gemm_names) // args.steps
+    flops = (12.0 if cfg["backward"] else 4.0) * A * D * H          # all ranks' tokens processed by... this rank's share
+    achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
+    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (%d launches per step)" % gemm_launches,
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
+                "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}
+    hbm = {}
+    bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12), "combine": (A * D * 2 + T * D * 2),
+                "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + T * D * 2)}
+    for n, nb in bytes_of.items():
+        if n in phases and phases[n][0] > 0:
+            gbs = nb / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
+            hbm[n] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                      "bytes_per_launch": nb}
+    line = dict(base, value=value, ms_per_step=ms,
+                config={"workload": workload, "tokens_per_gpu": T, "parallelism": "ep%d" % world if world > 1 else "single",
+                        "l2": "L2 flushed between steps" if flush else "working set larger than L2 (no flush needed)"},
+                clocks=clocks, gpu_launches=launches, roofline=roofline, hbm_kernels=hbm,
+                phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world == 1 and not args.no_cpu_baseline:
+        import synth
+        sample = cpu_sample_tokens(cfg)
+        host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
+        if cfg.get("zipf"):
+            host["bias"] = synth.zipf_bias(E, 2.0)
+        tps, threads, sec = run_cpu(cfg, host, sample, 1, 0)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": "first %d tokens of the workload, all %d experts, one pass (%.1f s)" % (sample, E, sec)}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -48,6 +48,8 @@ typedef struct tmt_moe_desc {
     void* stream;      /* cudaStream_t all work is queued on; NULL = legacy default stream  */
     int ep_world;      /* expert-parallel ranks (1 = all experts local)                    */
     int ep_rank;       /* this rank; it owns experts [rank*E/world, (rank+1)*E/world)        */
+    float ep_capacity_factor; /* expert-parallel only: rows other ranks may route to this rank's
+                          experts, as a multiple of tokens*topk (0 = 1.5); a step that needs more fails */
 } tmt_moe_desc;
 
 /* moe_keep_alloc + moe_ws_alloc (moe.cu:330-362): every buffer is allocated here, none later. */
@@ -142,6 +144,13 @@ int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter,
  * exchanges of grouped rows; Wup/Wdown hold only the E/world local experts. */
 int tmt_moe_ep_unique_id(void* id128);
 int tmt_moe_ep_init(tmt_moe* h, const void* id128);
+/* Host arithmetic of one exchange (no GPU needed; exported so that it can be tested on CPU ranks).
+ * cnt_all[g*E + e] = rows rank g routes to global expert e. For rank r: tok_poff[E+1] token-side
+ * group starts padded to `pad` rows; x_counts[E/G], x_poff[E/G+1] the expert-side groups of r's
+ * experts (rows of all source ranks in rank order, padded); src_off[s*(E/G) + le] where source
+ * s's rows start inside local group le. Returns the expert-side row count, -1 on bad arguments. */
+long long tmt_moe_ep_plan(int G, int r, int E, int pad, const int* cnt_all, int* tok_poff, int* x_counts,
+                          int* x_poff, int* src_off);
 
 #ifdef __cplusplus
 }

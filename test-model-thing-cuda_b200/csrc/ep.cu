@@ -1,19 +1,334 @@
-// Expert parallelism over NCCL (placeholder until the exchange path is built).
+// Expert parallelism: experts are partitioned over the ranks of one NCCL communicator (one
+// process per GPU, rank g owns experts [g*E/G, (g+1)*E/G)). Every rank routes its own tokens;
+// grouped rows travel to the owning rank, run through the grouped GEMMs there and travel back.
+// The reference has no counterpart (single GPU, no communication library).
+//
+// One step: forward = dispatch exchange + combine exchange, backward = the two mirrors.
+// An exchange is ONE NCCL group of point-to-point sends and receives, one message per
+// (peer, expert) pair, so that rows land directly in their expert group on the owner (no
+// re-permutation pass) and come back directly into the token-side slots. Message sizes come
+// from an all-gather of the per-expert counts, read on the host once per step (NCCL's
+// send/recv sizes are host arguments). All kernels read local memory only.
+//
+// NCCL is bound at run time (dlopen of the process's libnccl.so.2): the library has no link
+// dependency on it, and a host program that never uses expert parallelism does not need it.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <algorithm>
+#include <cstring>
 #include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "gemm.cuh"
 #include "moe_internal.h"
 
+struct tmt_ep_state {
+    void* lib = nullptr;
+    ncclComm_t comm = nullptr;
+    int G = 1, r = 0, EL = 0;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    // token side (cap rows, padded layout by global expert)
+    uint16_t *Xs = nullptr, *Yr = nullptr, *dYs = nullptr, *dXr = nullptr;
+    // expert side layout (x_cap rows): tables live in one device block, filled from the host each step
+    int x_cap = 0, x_max_tiles = 0;
+    int* x_tables = nullptr;          // [EL+1] poff | [EL] counts | [1] num tiles | [x_max_tiles] tile -> expert
+    std::vector<int> x_tables_host;
+    int* cnt_all_dev = nullptr;       // [G][E]
+    std::vector<int> cnt_all, tok_poff, x_counts, x_poff, src_off;
+    float* stat_global = nullptr;     // E+1
+};
+
 namespace tmt {
-void ep_forward(tmt_moe*, const void*, const void*, const void* const*, const void* const*, void*, float, int) {
-    throw std::runtime_error("expert parallelism is not initialised on this handle");
+namespace {
+
+#define CKE(call)                                                                                              \
+    do {                                                                                                       \
+        cudaError_t e__ = (call);                                                                              \
+        if (e__ != cudaSuccess) throw std::runtime_error(std::string(#call) + " failed: " + cudaGetErrorString(e__)); \
+    } while (0)
+
+#define NC(ep, call)                                                                                           \
+    do {                                                                                                       \
+        ncclResult_t r__ = (call);                                                                             \
+        if (r__ != ncclSuccess)                                                                                \
+            throw std::runtime_error(std::string(#call) + " failed: " + ((ep)->GetErrorString ? (ep)->GetErrorString(r__) : "?")); \
+    } while (0)
+
+template <class F>
+void bind(void* lib, const char* name, F& fn) {
+    fn = reinterpret_cast<F>(dlsym(lib, name));
+    if (!fn) throw std::runtime_error(std::string("NCCL symbol missing: ") + name);
 }
-void ep_backward(tmt_moe*, const void*, const void*, const void* const*, const void* const*, float*, float* const*,
-                 float* const*, void*, float, float) {
-    throw std::runtime_error("expert parallelism is not initialised on this handle");
+
+void load_nccl(tmt_ep_state* ep) {
+    if (ep->lib) return;
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+        ep->lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (ep->lib) break;
+    }
+    if (!ep->lib) throw std::runtime_error("libnccl.so.2 not found (expert parallelism needs NCCL in the process)");
+    bind(ep->lib, "ncclGetUniqueId", ep->GetUniqueId);
+    bind(ep->lib, "ncclCommInitRank", ep->CommInitRank);
+    bind(ep->lib, "ncclCommDestroy", ep->CommDestroy);
+    bind(ep->lib, "ncclGroupStart", ep->GroupStart);
+    bind(ep->lib, "ncclGroupEnd", ep->GroupEnd);
+    bind(ep->lib, "ncclSend", ep->Send);
+    bind(ep->lib, "ncclRecv", ep->Recv);
+    bind(ep->lib, "ncclAllGather", ep->AllGather);
+    bind(ep->lib, "ncclAllReduce", ep->AllReduce);
+    bind(ep->lib, "ncclGetErrorString", ep->GetErrorString);
 }
-void ep_teardown(tmt_moe*) {}
+
+template <class T>
+T* ep_alloc(tmt_moe* h, size_t n) {
+    void* p = nullptr;
+    CKE(cudaMalloc(&p, std::max<size_t>(n, 1) * sizeof(T)));
+    h->allocs.push_back(p);
+    h->bytes += n * sizeof(T);
+    return static_cast<T*>(p);
+}
+
+}  // namespace
 }  // namespace tmt
 
+using namespace tmt;
+
 extern "C" {
-int tmt_moe_ep_unique_id(void*) { tmt::set_error("expert parallelism is not built yet"); return -1; }
-int tmt_moe_ep_init(tmt_moe*, const void*) { tmt::set_error("expert parallelism is not built yet"); return -1; }
+
+// Pure host arithmetic of one exchange plan (testable without a GPU). cnt_all[g*E + e] = rows
+// rank g routes to global expert e. Outputs for rank r: tok_poff[E+1] (token-side group starts,
+// padded to `pad`), x_counts[EL] / x_poff[EL+1] (expert-side groups of the local experts, rows
+// of all sources concatenated in source order, padded), src_off[s*EL + le] (start of source s's
+// rows inside local group le). Returns the expert-side row count x_poff[EL], or -1.
+long long tmt_moe_ep_plan(int G, int r, int E, int pad, const int* cnt_all, int* tok_poff, int* x_counts,
+                          int* x_poff, int* src_off) {
+    if (G < 1 || r < 0 || r >= G || E < 1 || E % G || pad < 1 || !cnt_all) return -1;
+    const int EL = E / G;
+    long long p = 0;
+    for (int e = 0; e < E; ++e) {
+        tok_poff[e] = (int)p;
+        p += (cnt_all[(size_t)r * E + e] + pad - 1) / pad * pad;
+    }
+    tok_poff[E] = (int)p;
+    long long xp = 0;
+    for (int le = 0; le < EL; ++le) {
+        int n = 0;
+        for (int s = 0; s < G; ++s) {
+            src_off[(size_t)s * EL + le] = n;
+            n += cnt_all[(size_t)s * E + r * EL + le];
+        }
+        x_counts[le] = n;
+        x_poff[le] = (int)xp;
+        xp += (n + pad - 1) / pad * pad;
+        if (xp > 0x7fffffffLL) return -1;
+    }
+    x_poff[EL] = (int)xp;
+    return xp;
 }
+
+int tmt_moe_ep_unique_id(void* id128) {
+    try {
+        if (!id128) throw std::runtime_error("null argument");
+        tmt_ep_state tmp;
+        load_nccl(&tmp);
+        ncclUniqueId id;
+        NC(&tmp, tmp.GetUniqueId(&id));
+        static_assert(sizeof(id) == 128, "ncclUniqueId is 128 bytes");
+        memcpy(id128, &id, sizeof id);
+        return 0;
+    } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
+}
+
+int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
+    if (!h || !id128) { set_error("null argument"); return -1; }
+    try {
+        if (h->d.ep_world < 2) throw std::runtime_error("handle was created with ep_world = 1");
+        if (h->ep) throw std::runtime_error("expert parallelism is already initialised");
+        if (h->d.hidden == 0) throw std::runtime_error("expert parallelism needs the two-matrix mode (hidden > 0)");
+        CKE(cudaSetDevice(h->d.device));
+        std::unique_ptr<tmt_ep_state> ep(new tmt_ep_state());
+        load_nccl(ep.get());
+        ep->G = h->d.ep_world; ep->r = h->d.ep_rank; ep->EL = h->local_experts;
+        ncclUniqueId id;
+        memcpy(&id, id128, sizeof id);
+        NC(ep.get(), ep->CommInitRank(&ep->comm, ep->G, id, ep->r));
+        const int E = h->d.experts, D = h->d.dim;
+        const size_t cap = h->dims.cap;
+        ep->Xs = ep_alloc<uint16_t>(h, cap * D);
+        ep->Yr = ep_alloc<uint16_t>(h, cap * D);
+        if (h->d.training) {
+            ep->dYs = ep_alloc<uint16_t>(h, cap * D);
+            ep->dXr = ep_alloc<uint16_t>(h, cap * D);
+        }
+        ep->x_cap = h->x_cap;
+        ep->x_max_tiles = ep->x_cap / kPad;
+        ep->x_tables_host.assign((size_t)2 * ep->EL + 2 + ep->x_max_tiles, 0);
+        ep->x_tables = ep_alloc<int>(h, ep->x_tables_host.size());
+        ep->cnt_all_dev = ep_alloc<int>(h, (size_t)ep->G * E);
+        ep->cnt_all.assign((size_t)ep->G * E, 0);
+        ep->tok_poff.assign(E + 1, 0);
+        ep->x_counts.assign(ep->EL, 0);
+        ep->x_poff.assign(ep->EL + 1, 0);
+        ep->src_off.assign((size_t)ep->G * ep->EL, 0);
+        ep->stat_global = ep_alloc<float>(h, E + 1);
+        h->ep_world_counts = ep_alloc<int>(h, E);
+        h->ep = ep.release();
+        return 0;
+    } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
+}
+
+}  // extern "C"
+
+namespace tmt {
+
+void ep_teardown(tmt_moe* h) {
+    if (!h->ep) return;
+    if (h->ep->comm && h->ep->CommDestroy) h->ep->CommDestroy(h->ep->comm);
+    delete h->ep;
+    h->ep = nullptr;
+}
+
+namespace {
+
+// Counts of every rank -> host, exchange plan, expert-side tables -> device. One stream sync.
+void plan_step(tmt_moe* h) {
+    tmt_ep_state* ep = h->ep;
+    const int E = h->d.experts, G = ep->G, EL = ep->EL;
+    NC(ep, ep->AllGather(h->rb.counts, ep->cnt_all_dev, E, ncclInt32, ep->comm, h->stream));
+    CKE(cudaMemcpyAsync(ep->cnt_all.data(), ep->cnt_all_dev, (size_t)G * E * sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    CKE(cudaStreamSynchronize(h->stream));
+    const long long rows = tmt_moe_ep_plan(G, ep->r, E, kPad, ep->cnt_all.data(), ep->tok_poff.data(), ep->x_counts.data(),
+                                           ep->x_poff.data(), ep->src_off.data());
+    if (rows < 0 || rows > ep->x_cap)
+        throw std::runtime_error("expert-side capacity exceeded: " + std::to_string(rows) + " rows routed to this rank, room for " +
+                                 std::to_string(ep->x_cap) + " (raise desc.ep_capacity_factor)");
+    int* t = ep->x_tables_host.data();
+    memcpy(t, ep->x_poff.data(), (EL + 1) * sizeof(int));
+    memcpy(t + EL + 1, ep->x_counts.data(), EL * sizeof(int));
+    t[2 * EL + 1] = (int)(rows / kPad);
+    int* te = t + 2 * EL + 2;
+    std::fill(te, te + ep->x_max_tiles, -1);
+    for (int le = 0; le < EL; ++le)
+        for (int i = ep->x_poff[le] / kPad; i < ep->x_poff[le + 1] / kPad; ++i) te[i] = le;
+    CKE(cudaMemcpyAsync(ep->x_tables, t, ep->x_tables_host.size() * sizeof(int), cudaMemcpyHostToDevice, h->stream));
+    std::vector<int> world(E, 0);
+    for (int g = 0; g < G; ++g)
+        for (int e = 0; e < E; ++e) world[e] += ep->cnt_all[(size_t)g * E + e];
+    CKE(cudaMemcpyAsync(h->ep_world_counts, world.data(), E * sizeof(int), cudaMemcpyHostToDevice, h->stream));
+    h->launches += 1;
+}
+
+// Pad rows of the expert-side groups must read as zero (they feed the weight-gradient GEMMs).
+void zero_pads(tmt_moe* h, uint16_t* buf, int width) {
+    tmt_ep_state* ep = h->ep;
+    for (int le = 0; le < ep->EL; ++le) {
+        const size_t r0 = (size_t)ep->x_poff[le] + ep->x_counts[le], r1 = ep->x_poff[le + 1];
+        if (r1 > r0) CKE(cudaMemsetAsync(buf + r0 * width, 0, (r1 - r0) * width * 2, h->stream));
+    }
+}
+
+// to_experts: token-side groups -> owning ranks' expert-side groups; otherwise the way back.
+void exchange(tmt_moe* h, bool to_experts, const uint16_t* src, uint16_t* dst, int width) {
+    tmt_ep_state* ep = h->ep;
+    const int E = h->d.experts, G = ep->G, EL = ep->EL, r = ep->r;
+    prof_mark(h, kPhExchange);
+    NC(ep, ep->GroupStart());
+    for (int g = 0; g < G; ++g)
+        for (int le = 0; le < EL; ++le) {
+            const int e = g * EL + le;
+            const size_t n_tok = (size_t)ep->cnt_all[(size_t)r * E + e];                 // my rows for expert e (owner g)
+            const size_t n_exp = (size_t)ep->cnt_all[(size_t)g * E + r * EL + le];       // rank g's rows for my expert le
+            const size_t tok_row = ep->tok_poff[e];
+            const size_t exp_row = (size_t)ep->x_poff[le] + ep->src_off[(size_t)g * EL + le];
+            if (to_experts) {
+                if (n_tok) NC(ep, ep->Send(src + tok_row * width, n_tok * width, ncclBfloat16, g, ep->comm, h->stream));
+                if (n_exp) NC(ep, ep->Recv(dst + exp_row * width, n_exp * width, ncclBfloat16, g, ep->comm, h->stream));
+            } else {
+                if (n_exp) NC(ep, ep->Send(src + exp_row * width, n_exp * width, ncclBfloat16, g, ep->comm, h->stream));
+                if (n_tok) NC(ep, ep->Recv(dst + tok_row * width, n_tok * width, ncclBfloat16, g, ep->comm, h->stream));
+            }
+        }
+    NC(ep, ep->GroupEnd());
+    h->launches += 1;
+}
+
+void use_expert_layout(tmt_moe* h) {
+    tmt_ep_state* ep = h->ep;
+    h->g_poff = ep->x_tables;
+    h->g_num_m_tiles = ep->x_tables + 2 * ep->EL + 1;
+    h->g_tile_expert = ep->x_tables + 2 * ep->EL + 2;
+    h->g_max_tiles = ep->x_max_tiles;
+}
+
+}  // namespace
+
+void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
+                float beta, int tokens) {
+    tmt_ep_state* ep = h->ep;
+    if (!ep) throw std::runtime_error("expert parallelism is not initialised on this handle (tmt_moe_ep_init)");
+    if (tokens != h->d.tokens) throw std::runtime_error("expert-parallel steps carry exactly desc.tokens rows");
+    if (!X || !Wr || !Wup || !Wdown || !Y) throw std::runtime_error("null argument");
+    CKE(cudaSetDevice(h->d.device));
+    use_expert_layout(h);
+    h->dims.T = tokens;
+    h->last_tokens = tokens;
+    const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
+    route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
+    plan_step(h);
+    zero_pads(h, h->Xg, D);
+    exchange(h, true, ep->Xs, h->Xg, D);
+    expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
+    exchange(h, false, h->Yg, ep->Yr, D);
+    prof_mark(h, kPhCombine);
+    CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
+    h->launches += 1;
+    // statistics over all ranks' tokens: sum of probabilities and of lse^2 / T
+    NC(ep, ep->AllReduce(h->rb.stat, ep->stat_global, E + 1, ncclFloat32, ncclSum, ep->comm, h->stream));
+    prof_mark(h, -1);
+    h->have_forward = true;
+}
+
+void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
+                 float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef) {
+    tmt_ep_state* ep = h->ep;
+    if (!ep) throw std::runtime_error("expert parallelism is not initialised on this handle (tmt_moe_ep_init)");
+    if (!h->d.training || !h->have_forward) throw std::runtime_error("backward needs training = 1 and a preceding forward");
+    if (!dY || !Wr || !Wup || !Wdown || !dWr || !dWup || !dWdown || !dX) throw std::runtime_error("null argument");
+    CKE(cudaSetDevice(h->d.device));
+    use_expert_layout(h);
+    const int D = h->d.dim, E = h->d.experts;
+    prof_mark(h, kPhGradDispatch);
+    // token side: dYs[slot] = w * dY[token]; s_j = <dY[token], Yr[slot]> (the expert output came back unscaled)
+    CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
+    h->launches += 1;
+    zero_pads(h, h->dYg, D);
+    exchange(h, true, ep->dYs, h->dYg, D);
+    expert_backward(h, Wup, Wdown, dWup, dWdown);
+    exchange(h, false, h->dXg, ep->dXr, D);
+    prof_mark(h, kPhRouterBwd);
+    CKE(launch_router_bwd(h->dims, h->rb, nullptr, 0, h->s_j, h->dlogits, aux, zcoef, h->ep_world_counts,
+                          (long)h->d.tokens * ep->G, h->stream));
+    prof_mark(h, kPhRouterDw);
+    CKE(launch_router_dw(h->dims, h->rb, h->dlogits, ep->Xs, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
+    NC(ep, ep->AllReduce(dWr, dWr, (size_t)E * D, ncclFloat32, ncclSum, ep->comm, h->stream));
+    prof_mark(h, kPhScatter);
+    CKE(launch_scatter(h->dims, h->rb, h->dlogits, Wr, ep->dXr, static_cast<uint16_t*>(dX), h->stream));
+    prof_mark(h, -1);
+    h->launches += 5;
+}
+
+const float* ep_stat(tmt_moe* h) { return h->ep ? h->ep->stat_global : h->rb.stat; }
+
+}  // namespace tmt

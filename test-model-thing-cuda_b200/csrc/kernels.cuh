@@ -40,17 +40,21 @@ cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t
 cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, cudaStream_t s);
 // Xg[slot] = X[token]; pad rows zeroed; fills slot_of / slotw / tok_of_slot (moe.cu:103-140).
 cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s);
-// Y = beta*Y + sum_j Yg[slot_j]                       (two-matrix mode, gate applied by the GEMM)
-// Y = beta*Y + sum_j w_j * silu(Yg[slot_j])           (reference mode, moe.cu:144-158)
+// mode 0: Y = beta*Y + sum_j Yg[slot_j]               (two-matrix experts, gate applied by the GEMM)
+// mode 1: Y = beta*Y + sum_j w_j * silu(Yg[slot_j])   (reference mode, moe.cu:144-158)
+// mode 2: Y = beta*Y + sum_j w_j * Yg[slot_j]         (expert parallel: rows come back unscaled)
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
-                           int silu_in_combine, cudaStream_t s);
-// two-matrix mode: dYg[slot] = bf16(w * dY[token]), pad rows zero.
-// reference mode:  dYg[slot] = silu_bwd(Yg[slot], w * dY[token]); s_j = <dY, silu(Yg[slot])> (moe.cu:162-197).
+                           int mode, cudaStream_t s);
+// mode 0: dYg[slot] = bf16(w * dY[token]), pad rows zero                         (two-matrix experts)
+// mode 1: dYg[slot] = silu_bwd(Yg[slot], w * dY[token]); s_j = <dY, silu(Yg[slot])>  (reference, moe.cu:162-197)
+// mode 2: as mode 0 and s_j = <dY, Yg[slot]>                                     (expert parallel)
 cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
-                                 uint16_t* dYg, float* s_j, int reference_mode, cudaStream_t s);
+                                 uint16_t* dYg, float* s_j, int mode, cudaStream_t s);
 // moe.cu:200-234. sw_part (may be NULL): per-row partial sums of w * dL/dw from the dH GEMM.
+// counts / n_norm: per-expert counts and token count the aux and z terms are normalised by
+// (the local ones on one GPU, the totals over all ranks under expert parallelism).
 cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
-                              float* dlogits, float aux, float zcoef, cudaStream_t s);
+                              float* dlogits, float aux, float zcoef, const int* counts, long n_norm, cudaStream_t s);
 // dWr[e, :] = sum_t bf16(dlogits[t, e]) * X[t, :] with X[t] read from Xg[slot_of[t, 0]] (moe.cu:519-521).
 cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float* dlogits, const uint16_t* Xg,
                              float* partial, int chunks, float* dWr, cudaStream_t s);

@@ -91,7 +91,7 @@ enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kNum
 enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };
 
 void build_act_maps(tmt_moe* h) {
-    const uint64_t D = h->d.dim, H = h->d.hidden, cap = h->dims.cap;
+    const uint64_t D = h->d.dim, H = h->d.hidden, cap = h->gcap;
     std::vector<CUtensorMap> m(kNumActMaps);
     memset(m.data(), 0, m.size() * sizeof(CUtensorMap));
     make_map(&m[kXgK], h->Xg, D, cap, 64, 128);
@@ -159,9 +159,9 @@ GemmParams base_params(tmt_moe* h) {
     GemmParams p;
     memset(&p, 0, sizeof p);
     p.experts = h->local_experts;
-    p.tile_expert = h->rb.tile_expert;
-    p.num_m_tiles = h->rb.num_m_tiles;
-    p.poff = h->rb.poff;
+    p.tile_expert = h->g_tile_expert;
+    p.num_m_tiles = h->g_num_m_tiles;
+    p.poff = h->g_poff;
     p.status = h->rb.status;
     p.a_boxes = 1; p.b_boxes = 1; p.a_box_step = 64; p.b_box_step = 64;
     return p;
@@ -198,7 +198,7 @@ GemmParams red_gemm(tmt_moe* h, ActMap a, const uint16_t* A, int M, ActMap b, co
 
 void run_gemm(tmt_moe* h, const GemmParams& p) {
     if (h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05) CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
-    else CK(launch_gemm_simt(p, h->dims.max_tiles, h->stream));
+    else CK(launch_gemm_simt(p, h->g_max_tiles, h->stream));
     h->launches += 1;
 }
 
@@ -242,23 +242,22 @@ void prof_mark(tmt_moe* h, int phase) {
     pr.used += 1;
 }
 
-void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
-                  float beta, int tokens) {
-    check_tokens(h, tokens);
-    if (!X || !Wr || !Wup || !Y || (h->d.hidden > 0 && !Wdown)) throw std::runtime_error("null argument");
-    CK(cudaSetDevice(h->d.device));
-    const int D = h->d.dim, H = h->d.hidden;
-    h->dims.T = tokens;
-    h->last_tokens = tokens;
-    refresh_weights(h, Wup, Wdown);
-    const uint16_t* Xb = static_cast<const uint16_t*>(X);
+// Router, offset tables and the row copies into `grouped` (token-side grouped layout).
+void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped) {
     prof_mark(h, kPhRouter);
-    CK(launch_router(h->dims, h->rb, Xb, Wr, h->has_bias ? h->bias : nullptr, h->stream));
+    CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream));
     prof_mark(h, kPhScan);
     CK(launch_scan(h->dims, h->rb, h->stream));
     prof_mark(h, kPhDispatch);
-    CK(launch_dispatch(h->dims, h->rb, Xb, h->Xg, h->stream));
+    CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream));
     h->launches += 3;
+}
+
+// Grouped expert products over the rows in h->Xg: Yg = expert(Xg). With gate_in_epilogue the
+// down-projection scales each row by its gate weight (single-GPU layout, where slotw is local).
+void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue) {
+    const int D = h->d.dim, H = h->d.hidden;
+    refresh_weights(h, Wup, Wdown);
     if (H > 0) {
         GemmParams up = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, H, D, kEpiUp);
         up.out0 = h->d.training ? h->P : nullptr;
@@ -266,7 +265,7 @@ void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* 
         if (h->q_expert_scales) up.expert_scale = h->q_scales;
         prof_mark(h, kPhGemmUp);
         run_gemm(h, up);
-        GemmParams down = rows_gemm(h, kHactK, h->Hact, kDownK, h->down_ptrs, false, D, H, kEpiDown);
+        GemmParams down = rows_gemm(h, kHactK, h->Hact, kDownK, h->down_ptrs, false, D, H, gate_in_epilogue ? kEpiDown : kEpiBf16);
         down.out0 = h->Yg;
         down.row_scale = h->rb.slotw;
         if (h->q_expert_scales) down.expert_scale = h->q_scales + h->d.experts;
@@ -278,27 +277,30 @@ void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* 
         prof_mark(h, kPhGemmUp);
         run_gemm(h, g);
     }
+}
+
+void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* Wup, const void* const* Wdown, void* Y,
+                  float beta, int tokens) {
+    check_tokens(h, tokens);
+    if (!X || !Wr || !Wup || !Y || (h->d.hidden > 0 && !Wdown)) throw std::runtime_error("null argument");
+    CK(cudaSetDevice(h->d.device));
+    h->dims.T = tokens;
+    h->last_tokens = tokens;
+    route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, h->Xg);
+    expert_forward(h, Wup, Wdown, true);
     prof_mark(h, kPhCombine);
-    CK(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, H == 0, h->stream));
+    CK(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, h->d.hidden == 0 ? 1 : 0, h->stream));
     prof_mark(h, -1);
     h->launches += 1;
     h->have_forward = true;
 }
 
-void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
-                   float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef) {
-    if (!h->d.training) throw std::runtime_error("handle was created with training = 0");
-    if (!h->have_forward) throw std::runtime_error("backward without a preceding forward");
-    if (!dY || !Wr || !Wup || !dWr || !dWup || !dX || (h->d.hidden > 0 && (!Wdown || !dWdown)))
-        throw std::runtime_error("null argument");
-    CK(cudaSetDevice(h->d.device));
-    const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
+// The four (reference mode: two) grouped gradient products over the rows in h->dYg.
+void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup,
+                     float* const* dWdown) {
+    const int D = h->d.dim, H = h->d.hidden;
     refresh_weights(h, Wup, Wdown);
     refresh_grads(h, dWup, dWdown);
-    const uint16_t* dYb = static_cast<const uint16_t*>(dY);
-    prof_mark(h, kPhGradDispatch);
-    CK(launch_grad_dispatch(h->dims, h->rb, dYb, h->Yg, h->dYg, h->s_j, H == 0, h->stream));
-    h->launches += 1;
     if (H > 0) {
         GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
         dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
@@ -320,9 +322,24 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
         prof_mark(h, kPhGemmDx);
         run_gemm(h, dx);
     }
+}
+
+void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
+                   float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef) {
+    if (!h->d.training) throw std::runtime_error("handle was created with training = 0");
+    if (!h->have_forward) throw std::runtime_error("backward without a preceding forward");
+    if (!dY || !Wr || !Wup || !dWr || !dWup || !dX || (h->d.hidden > 0 && (!Wdown || !dWdown)))
+        throw std::runtime_error("null argument");
+    CK(cudaSetDevice(h->d.device));
+    const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
+    prof_mark(h, kPhGradDispatch);
+    CK(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), h->Yg, h->dYg, h->s_j, H == 0 ? 1 : 0, h->stream));
+    h->launches += 1;
+    expert_backward(h, Wup, Wdown, dWup, dWdown);
     if (E > 1) {
         prof_mark(h, kPhRouterBwd);
-        CK(launch_router_bwd(h->dims, h->rb, H > 0 ? h->sw_part : nullptr, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, h->stream));
+        CK(launch_router_bwd(h->dims, h->rb, H > 0 ? h->sw_part : nullptr, h->sw_ld, h->s_j, h->dlogits, aux, zcoef,
+                             h->rb.counts, (long)h->dims.T, h->stream));
         prof_mark(h, kPhRouterDw);
         CK(launch_router_dw(h->dims, h->rb, h->dlogits, h->Xg, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
         h->launches += 3;
@@ -359,6 +376,16 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     // rows of the grouped buffers: every assignment plus up to kPad-1 pad rows per expert (moe.cu:331)
     const long cap = ((long)T * K + kPad - 1) / kPad * kPad + (long)kPad * E;
     h->dims = RouteDims{T, D, E, K, (int)cap, (int)(cap / kPad), d.router_dtype == TMT_MOE_F32};
+    // rows of the grouped GEMM buffers: the token-side layout on one GPU; under expert parallelism the
+    // rows other ranks may route here, bounded by the capacity factor (default 1.5 x tokens x topk)
+    long gcap = cap;
+    if (d.ep_world > 1) {
+        const double f = d.ep_capacity_factor > 0 ? d.ep_capacity_factor : 1.5;
+        gcap = ((long)(f * T * K) + kPad - 1) / kPad * kPad + (long)kPad * h->local_experts;
+        if (gcap > 0x7fffff00L) throw std::runtime_error("expert-side capacity exceeds the supported index range");
+    }
+    h->gcap = gcap;
+    h->x_cap = (int)gcap;
     const int NB = (T + kTokBlock - 1) / kTokBlock;
     RouteBufs& b = h->rb;
     b.logits = dalloc<float>(h, (size_t)T * E);
@@ -383,20 +410,20 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     b.status = dalloc<int>(h, 1);
     CK(cudaMemsetAsync(b.status, 0, sizeof(int), h->stream));
     h->bias = dalloc<float>(h, E);
-    h->Xg = dalloc<uint16_t>(h, (size_t)cap * D);
-    h->Yg = dalloc<uint16_t>(h, (size_t)cap * D);
-    if (H > 0) h->Hact = dalloc<uint16_t>(h, (size_t)cap * H);
+    h->Xg = dalloc<uint16_t>(h, (size_t)gcap * D);
+    h->Yg = dalloc<uint16_t>(h, (size_t)gcap * D);
+    if (H > 0) h->Hact = dalloc<uint16_t>(h, (size_t)gcap * H);
     if (d.training) {
-        h->dYg = dalloc<uint16_t>(h, (size_t)cap * D);
-        h->dXg = dalloc<uint16_t>(h, (size_t)cap * D);
+        h->dYg = dalloc<uint16_t>(h, (size_t)gcap * D);
+        h->dXg = dalloc<uint16_t>(h, (size_t)gcap * D);
         h->s_j = dalloc<float>(h, (size_t)T * K);
         h->dlogits = dalloc<float>(h, (size_t)T * E);
         h->dwr_partial = dalloc<float>(h, (size_t)kRouterDwChunks * E * D);
         if (H > 0) {
-            h->P = dalloc<uint16_t>(h, (size_t)cap * H);
-            h->dP = dalloc<uint16_t>(h, (size_t)cap * H);
+            h->P = dalloc<uint16_t>(h, (size_t)gcap * H);
+            h->dP = dalloc<uint16_t>(h, (size_t)gcap * H);
             h->sw_ld = (H + kBN - 1) / kBN;
-            h->sw_part = dalloc<float>(h, (size_t)cap * h->sw_ld);
+            h->sw_part = dalloc<float>(h, (size_t)gcap * h->sw_ld);
         }
     } else {
         // forward-only handles still need valid map bases for the unused gradient maps
@@ -408,6 +435,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->down_ptrs = dalloc<const uint16_t*>(h, h->local_experts);
     h->gup_ptrs = dalloc<float*>(h, h->local_experts);
     h->gdown_ptrs = dalloc<float*>(h, h->local_experts);
+    h->g_poff = b.poff; h->g_num_m_tiles = b.num_m_tiles; h->g_tile_expert = b.tile_expert; h->g_max_tiles = h->dims.max_tiles;
     if (d.gemm_impl == TMT_MOE_GEMM_TCGEN05) build_act_maps(h);
     if (d.host_io) {
         h->Xs = dalloc<uint16_t>(h, (size_t)T * D);
@@ -487,11 +515,12 @@ int tmt_moe_stats(tmt_moe* h, float* stat, int64_t* counts, float* aux) {
         const int E = h->d.experts, K = h->d.topk;
         std::vector<float> st(E + 1);
         std::vector<int> cn(E);
-        CK(cudaMemcpyAsync(st.data(), h->rb.stat, (E + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaMemcpyAsync(st.data(), ep_stat(h), (E + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
         CK(cudaMemcpyAsync(cn.data(), h->ep_world_counts ? h->ep_world_counts : h->rb.counts, E * sizeof(int),
                            cudaMemcpyDeviceToHost, h->stream));
         CK(cudaStreamSynchronize(h->stream));
         const double N = (double)h->last_tokens * h->d.ep_world;
+        st[E] /= (float)h->d.ep_world;     // every rank contributed the mean over its own tokens
         if (stat) memcpy(stat, st.data(), (E + 1) * sizeof(float));
         if (counts) for (int e = 0; e < E; ++e) counts[e] = cn[e];
         if (aux) {
@@ -554,10 +583,10 @@ long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes
         else if (s == "tile_expert") { src = h->rb.tile_expert; n = (size_t)h->dims.max_tiles * 4; }
         else if (s == "num_m_tiles") { src = h->rb.num_m_tiles; n = 4; }
         // grouped activations, all cap rows (debugging / cross-checks; cap comes from "cap")
-        else if (s == "Xg") { src = h->Xg; n = (size_t)h->dims.cap * h->d.dim * 2; }
-        else if (s == "Yg") { src = h->Yg; n = (size_t)h->dims.cap * h->d.dim * 2; }
-        else if (s == "dYg") { src = h->d.training ? h->dYg : nullptr; n = (size_t)h->dims.cap * h->d.dim * 2; }
-        else if (s == "dXg") { src = h->dXg; n = (size_t)h->dims.cap * h->d.dim * 2; }
+        else if (s == "Xg") { src = h->Xg; n = (size_t)h->gcap * h->d.dim * 2; }
+        else if (s == "Yg") { src = h->Yg; n = (size_t)h->gcap * h->d.dim * 2; }
+        else if (s == "dYg") { src = h->d.training ? h->dYg : nullptr; n = (size_t)h->gcap * h->d.dim * 2; }
+        else if (s == "dXg") { src = h->dXg; n = (size_t)h->gcap * h->d.dim * 2; }
         else if (s == "P") { src = h->P; n = (size_t)h->dims.cap * h->d.hidden * 2; }
         else if (s == "Hact") { src = h->Hact; n = (size_t)h->dims.cap * h->d.hidden * 2; }
         else if (s == "dP") { src = h->d.training ? h->dP : nullptr; n = (size_t)h->dims.cap * h->d.hidden * 2; }

@@ -38,6 +38,10 @@ struct tmt_moe {
     int local_experts = 0;
     tmt::RouteDims dims{};
     tmt::RouteBufs rb{};
+    // layout tables the grouped GEMMs run on: the token-side tables on one GPU, the expert-side ones under EP
+    const int* g_poff = nullptr; const int* g_num_m_tiles = nullptr; const int* g_tile_expert = nullptr; int g_max_tiles = 0;
+    long gcap = 0;      // rows of the grouped GEMM buffers
+    int x_cap = 0;
     float* bias = nullptr;
     bool has_bias = false;
     // grouped activations (cap rows): input copies, up-projection pre-activation, SiLU output,
@@ -80,5 +84,9 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
 void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* Wup, const void* const* Wdown,
                  float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef);
 void ep_teardown(tmt_moe* h);
+const float* ep_stat(tmt_moe* h);
+void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped);
+void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue);
+void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown);
 void prof_mark(tmt_moe* h, int phase);
 }  // namespace tmt

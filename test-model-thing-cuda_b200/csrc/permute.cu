@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dispatch_kernel(const Rou
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const RouteDims d, const RouteBufs b,
                                                                        const uint16_t* __restrict__ Yg,
                                                                        uint16_t* __restrict__ Y, float beta,
-                                                                       int silu_in_combine) {
+                                                                       int mode) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
     if (t >= d.T) return;
@@ -105,9 +105,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
             if (j < d.K && slots[j] >= 0) {
                 float y[8];
                 unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), y);
-                if (silu_in_combine) {
+                if (mode == 1) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[i] += ws[j] * silu_f(y[i]);
+                } else if (mode == 2) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] += ws[j] * y[i];
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[i] += y[i];
@@ -122,7 +125,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
                                                                              const uint16_t* __restrict__ dY,
                                                                              const uint16_t* __restrict__ Yg,
                                                                              uint16_t* __restrict__ dYg,
-                                                                             float* __restrict__ s_j, int reference_mode,
+                                                                             float* __restrict__ s_j, int mode,
                                                                              int tok_blocks) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = d.D >> 3;
@@ -154,7 +157,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
         for (int j = 0; j < kMaxK; ++j) {
             if (j < d.K && slots[j] >= 0) {
                 float o[8];
-                if (reference_mode) {
+                if (mode == 1) {
                     float pre[8];
                     unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), pre);
 #pragma unroll
@@ -164,6 +167,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
                         o[i] = (ws[j] * g[i]) * sg * (1.0f + pre[i] * (1.0f - sg));     // silu_bwd, common.h:21-24
                     }
                 } else {
+                    if (mode == 2) {
+                        float y[8];
+                        unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), y);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) sdot[j] += g[i] * y[i];
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[i] = ws[j] * g[i];
                 }
@@ -171,7 +180,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
             }
         }
     }
-    if (reference_mode) {
+    if (mode != 0) {
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
             if (j < d.K) {
@@ -186,13 +195,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
 
 // One thread per token; dlogits doubles as scratch exactly as in moe.cu:213-221.
 __global__ void router_bwd_kernel(const RouteDims d, const RouteBufs b, const float* __restrict__ sw_part, int sw_ld,
-                                  float* __restrict__ s_j, float* __restrict__ dlogits, float aux, float zcoef) {
+                                  float* __restrict__ s_j, float* __restrict__ dlogits, float aux, float zcoef,
+                                  const int* __restrict__ counts, long n_norm) {
     const long r = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= d.T) return;
     const int E = d.E, K = d.K;
     const float* probs = b.probs + r * E;
     float* g = dlogits + r * E;
-    const float nk = (float)((long)d.T * K);
+    const float nk = (float)(n_norm * K);
+    const float nn = (float)n_norm;
     if (sw_part) {
         // dH-GEMM partials hold w * dL/dw; one per 256-column tile, added in tile order
         for (int j = 0; j < K; ++j) {
@@ -216,12 +227,12 @@ __global__ void router_bwd_kernel(const RouteDims d, const RouteBufs b, const fl
     float expected = 0;
     for (int e = 0; e < E; ++e) {
         g[e] = probs[e] * (g[e] - acc);
-        expected += probs[e] * b.counts[e] / nk;
+        expected += probs[e] * counts[e] / nk;
     }
     const float lse = b.lse[r];
     for (int e = 0; e < E; ++e) {
         const float p = probs[e];
-        g[e] += aux * E / d.T * p * (b.counts[e] / nk - expected) + zcoef * 2.f / d.T * lse * p;
+        g[e] += aux * E / nn * p * (counts[e] / nk - expected) + zcoef * 2.f / nn * lse * p;
     }
 }
 
@@ -354,21 +365,21 @@ cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16
 }
 
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
-                           int silu_in_combine, cudaStream_t s) {
-    combine_kernel<<<tok_blocks_of(d.T), kWarpsPerBlock * 32, 0, s>>>(d, b, Yg, Y, beta, silu_in_combine);
+                           int mode, cudaStream_t s) {
+    combine_kernel<<<tok_blocks_of(d.T), kWarpsPerBlock * 32, 0, s>>>(d, b, Yg, Y, beta, mode);
     return cudaGetLastError();
 }
 
 cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
-                                 uint16_t* dYg, float* s_j, int reference_mode, cudaStream_t s) {
+                                 uint16_t* dYg, float* s_j, int mode, cudaStream_t s) {
     const int tb = tok_blocks_of(d.T);
-    grad_dispatch_kernel<<<tb + d.E, kWarpsPerBlock * 32, 0, s>>>(d, b, dY, Yg, dYg, s_j, reference_mode, tb);
+    grad_dispatch_kernel<<<tb + d.E, kWarpsPerBlock * 32, 0, s>>>(d, b, dY, Yg, dYg, s_j, mode, tb);
     return cudaGetLastError();
 }
 
 cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
-                              float* dlogits, float aux, float zcoef, cudaStream_t s) {
-    router_bwd_kernel<<<(d.T + 127) / 128, 128, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef);
+                              float* dlogits, float aux, float zcoef, const int* counts, long n_norm, cudaStream_t s) {
+    router_bwd_kernel<<<(d.T + 127) / 128, 128, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef, counts, n_norm);
     return cudaGetLastError();
 }
 

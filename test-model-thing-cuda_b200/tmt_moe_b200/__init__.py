@@ -23,7 +23,7 @@ EXPORTS = (
     "tmt_moe_forward", "tmt_moe_stats", "tmt_moe_backward", "tmt_moe_step_host", "tmt_moe_read",
     "tmt_moe_launch_count", "tmt_moe_device_status", "tmt_moe_quantize_nvfp4",
     "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init", "tmt_moe_set_profile",
-    "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name",
+    "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name", "tmt_moe_ep_plan",
 )
 
 
@@ -36,7 +36,7 @@ class Desc(ctypes.Structure):
                 ("experts", ctypes.c_int), ("topk", ctypes.c_int), ("router_dtype", ctypes.c_int),
                 ("training", ctypes.c_int), ("gemm_impl", ctypes.c_int), ("device", ctypes.c_int),
                 ("host_io", ctypes.c_int), ("stream", ctypes.c_void_p), ("ep_world", ctypes.c_int),
-                ("ep_rank", ctypes.c_int)]
+                ("ep_rank", ctypes.c_int), ("ep_capacity_factor", ctypes.c_float)]
 
 
 class Nvfp4Weight(ctypes.Structure):
@@ -59,6 +59,7 @@ def load():
     lib.tmt_moe_last_error.restype = ctypes.c_char_p
     lib.tmt_moe_read.restype = ctypes.c_longlong
     lib.tmt_moe_launch_count.restype = ctypes.c_longlong
+    lib.tmt_moe_ep_plan.restype = ctypes.c_longlong
     lib.tmt_moe_destroy.restype = None
     lib.tmt_moe_phase_name.restype = ctypes.c_char_p
     for name in EXPORTS:
@@ -97,10 +98,11 @@ class MoE:
     """One MoE layer's state (the reference's MoeKeep + MoeWs)."""
 
     def __init__(self, tokens, dim, experts, topk, hidden=0, router_dtype=BF16, training=True,
-                 gemm_impl=GEMM_TCGEN05, device=0, host_io=False, stream=None, ep_world=1, ep_rank=0):
+                 gemm_impl=GEMM_TCGEN05, device=0, host_io=False, stream=None, ep_world=1, ep_rank=0,
+                 ep_capacity_factor=0.0):
         self.lib = load()
         self.desc = Desc(tokens, dim, hidden, experts, topk, router_dtype, int(training), gemm_impl, device,
-                         int(host_io), stream, ep_world, ep_rank)
+                         int(host_io), stream, ep_world, ep_rank, ep_capacity_factor)
         self.h = ctypes.c_void_p()
         _check(self.lib.tmt_moe_create(ctypes.byref(self.desc), ctypes.byref(self.h)), self.lib)
         self.tokens, self.dim, self.hidden, self.experts, self.topk = tokens, dim, hidden, experts, topk
@@ -188,6 +190,19 @@ class MoE:
             return a
         _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), arr(Wup), arr(Wdown), _ptr(Y),
                                               ctypes.c_float(beta), t), self.lib)
+
+    def ep_init_torch(self, dist):
+        """Creates the handle's NCCL communicator: rank 0 makes the id, torch.distributed ships it."""
+        import torch
+        buf = torch.zeros(128, dtype=torch.uint8)
+        if dist.get_rank() == 0:
+            raw = (ctypes.c_ubyte * 128)()
+            _check(self.lib.tmt_moe_ep_unique_id(raw), self.lib)
+            buf = torch.tensor(list(raw), dtype=torch.uint8)
+        dev = buf.cuda() if dist.get_backend() == "nccl" else buf
+        dist.broadcast(dev, src=0)
+        raw = (ctypes.c_ubyte * 128)(*dev.cpu().tolist())
+        _check(self.lib.tmt_moe_ep_init(self.h, raw), self.lib)
 
     def set_profile(self, on):
         _check(self.lib.tmt_moe_set_profile(self.h, int(on)), self.lib)
