@@ -1,0 +1,145 @@
+"""Expert-parallel host logic on CPU ranks: two gloo processes route their own tokens with the
+oracle, exchange per-expert counts, compute the exchange plan with the library's own
+tmt_moe_ep_plan and move rows with point-to-point messages in exactly the order the CUDA path
+posts its NCCL sends and receives. The rows that arrive in each expert group must be the rows a
+single process would have grouped, and the way back must restore every token-side slot."""
+import ctypes
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PAD = 128
+
+
+def _plan(lib, G, r, E, cnt_all):
+    EL = E // G
+    tok_poff = np.zeros(E + 1, np.int32)
+    x_counts = np.zeros(EL, np.int32)
+    x_poff = np.zeros(EL + 1, np.int32)
+    src_off = np.zeros(G * EL, np.int32)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    rows = lib.tmt_moe_ep_plan(G, r, E, PAD, p(np.ascontiguousarray(cnt_all, np.int32)), p(tok_poff), p(x_counts),
+                               p(x_poff), p(src_off))
+    return rows, tok_poff, x_counts, x_poff, src_off.reshape(G, EL)
+
+
+def _exchange(to_experts, src, dst, G, r, E, cnt_all, tok_poff, x_poff, src_off):
+    """Same loop as exchange() in csrc/ep.cu, with gloo isend / irecv (gloo has no message to
+    oneself, so the rank's own rows are copied; NCCL handles that pair like any other)."""
+    EL = E // G
+    ops = []
+    for g in range(G):
+        for le in range(EL):
+            e = g * EL + le
+            n_tok = int(cnt_all[r, e])
+            n_exp = int(cnt_all[g, r * EL + le])
+            tok_row = int(tok_poff[e])
+            exp_row = int(x_poff[le] + src_off[g, le])
+            if g == r:
+                if to_experts:
+                    dst[exp_row:exp_row + n_exp] = src[tok_row:tok_row + n_tok]
+                else:
+                    dst[tok_row:tok_row + n_tok] = src[exp_row:exp_row + n_exp]
+                continue
+            if to_experts:
+                if n_tok:
+                    ops.append(dist.P2POp(dist.isend, src[tok_row:tok_row + n_tok].contiguous(), g))
+                if n_exp:
+                    ops.append(dist.P2POp(dist.irecv, dst[exp_row:exp_row + n_exp], g))
+            else:
+                if n_exp:
+                    ops.append(dist.P2POp(dist.isend, src[exp_row:exp_row + n_exp].contiguous(), g))
+                if n_tok:
+                    ops.append(dist.P2POp(dist.irecv, dst[tok_row:tok_row + n_tok], g))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+
+
+def _worker(rank, world, port, q):
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import synth
+        import tmt_moe_b200 as M
+        from oracle import oracle as O
+        lib = M.load()
+        T, D, E, K = 200, 64, 6, 2
+        data = [synth.make(T, D, 0, E, K, seed=50 + g, router_std=0.3) for g in range(world)]
+        for d in data:
+            d["Wr"] = data[0]["Wr"]                     # replicated router
+        mine = data[rank]
+        rt = O.router(mine["X"], mine["Wr"], K)
+        counts, off, poff, slot_of = O.layout(rt["idx"], E, PAD)
+        gathered = [torch.zeros(E, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(counts.astype(np.int32)))
+        cnt_all = torch.stack(gathered).numpy()
+        rows, tok_poff, x_counts, x_poff, src_off = _plan(lib, world, rank, E, cnt_all)
+        assert (tok_poff == poff).all()                  # the plan's token-side layout is the single-GPU layout
+        EL = E // world
+        assert rows == x_poff[EL] and (x_poff % PAD == 0).all()
+        # token-side grouped rows: value = (global token id, column) so that arrivals can be identified
+        Xs = torch.zeros((int(poff[E]), 4), dtype=torch.float32)
+        for t in range(T):
+            for j in range(K):
+                Xs[slot_of[t, j]] = torch.tensor([rank, t, j, rt["idx"][t, j]], dtype=torch.float32)
+        Xg = torch.full((int(rows), 4), -1.0)
+        _exchange(True, Xs, Xg, world, rank, E, cnt_all, tok_poff, x_poff, src_off)
+        # expectation from a single process that sees every rank's routing
+        for le in range(EL):
+            e = rank * EL + le
+            want = []
+            for g in range(world):
+                rg = O.router(data[g]["X"], data[g]["Wr"], K)
+                for t in range(T):
+                    for j in range(K):
+                        if rg["idx"][t, j] == e:
+                            want.append([g, t, j, e])
+            got = Xg[x_poff[le]:x_poff[le] + x_counts[le]].numpy()
+            assert x_counts[le] == len(want)
+            np.testing.assert_array_equal(got, np.array(want, np.float32).reshape(-1, 4))
+            assert (Xg[x_poff[le] + x_counts[le]:x_poff[le + 1]] == -1).all()    # pad rows untouched
+        # the way back restores every slot
+        back = torch.full_like(Xs, -2.0)
+        _exchange(False, Xg * 2, back, world, rank, E, cnt_all, tok_poff, x_poff, src_off)
+        for t in range(T):
+            for j in range(K):
+                np.testing.assert_array_equal(back[slot_of[t, j]].numpy(), 2 * Xs[slot_of[t, j]].numpy())
+        q.put((rank, "ok"))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAIL: %s\n%s" % (exc, traceback.format_exc())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_plan_rejects_bad_arguments():
+    sys.path[:0] = [os.path.join(ROOT, "test-model-thing-cuda_b200")]
+    import tmt_moe_b200 as M
+    lib = M.load()
+    z = np.zeros(16, np.int32)
+    p = z.ctypes.data_as(ctypes.c_void_p)
+    assert lib.tmt_moe_ep_plan(2, 0, 5, 128, p, p, p, p, p) == -1     # experts not divisible by ranks
+    assert lib.tmt_moe_ep_plan(2, 2, 4, 128, p, p, p, p, p) == -1     # rank out of range
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_exchange_plan_two_cpu_ranks(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 400 + world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in res:
+        assert msg == "ok", "rank %d: %s" % (rank, msg)
