@@ -56,8 +56,9 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms. Samples are kept with their
+    timestamps; stop(t0, t1) reports those taken inside the timed region [t0, t1] (wall clock)."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -71,13 +72,14 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    def stop(self, t0, t1):
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": "timed region"}
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -90,20 +92,30 @@ class ClockSampler:
             for line in f:
                 parts = [x.strip() for x in line.split(",")]
                 if len(parts) >= 9 and parts[1].isdigit():
-                    rows.append(parts)
+                    try:
+                        ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    except ValueError:
+                        ts = None
+                    rows.append((ts, parts))
         os.unlink(self.path)
-        if not rows:
+        inside = [p for ts, p in rows if ts is not None and t0 - 0.05 <= ts <= t1 + 0.05]
+        if len(inside) >= 2:
+            use = inside
+        else:       # region shorter than the sampling period: fall back to everything since warm-up began
+            use = [p for _, p in rows]
+            out["window"] = "warm-up and timed region (timed region shorter than two sampling periods)"
+        if not use:
             return out
-        out["samples"] = len(rows)
-        out["sm_mhz"] = statistics.median(int(r[1]) for r in rows)
-        out["sm_max_mhz"] = max(int(r[2]) for r in rows)
+        out["samples"] = len(use)
+        out["sm_mhz"] = statistics.median(int(r[1]) for r in use)
+        out["sm_max_mhz"] = max(int(r[2]) for r in use)
         try:
-            out["power_w_max"] = max(float(r[3]) for r in rows)
+            out["power_w_max"] = max(float(r[3]) for r in use)
         except ValueError:
             pass
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for i, n in enumerate(names):
-            if any(r[5 + i].lower().startswith("active") for r in rows):
+            if any(r[5 + i].lower().startswith("active") for r in use):
                 out["reasons"].append(n)
         return out
 
@@ -250,18 +262,19 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
     if moe.device_status() != 0:
         raise SystemExit("device status %d after warm-up" % moe.device_status())
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = moe.launch_count
     moe.set_profile(True)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
+    wall0 = time.time()
     for a, b in evs:
         if scrub is not None:
             scrub.zero_()
@@ -269,10 +282,11 @@ def main():
         step()
         b.record()
     barrier()
+    wall1 = time.time()
     phases = moe.profile(reset=True)
     moe.set_profile(False)
     launches = moe.launch_count - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
     if dist is not None:
         t = torch.tensor([ms], device="cuda")

@@ -76,6 +76,10 @@ int tmt_moe_forward(tmt_moe* h, const void* X, const void* Wrouter, const void* 
  * *aux = E * sum_e (stat[e]/N) * (counts[e]/(N*K)). Any pointer may be NULL. */
 int tmt_moe_stats(tmt_moe* h, float* stat, int64_t* counts, float* aux);
 
+/* The deferred statistics path of moe_forward (moe.cu:448-452): queues a device-to-device copy of
+ * the E+1 statistics into a caller-owned DEVICE slot on the handle's stream; no synchronisation. */
+int tmt_moe_copy_stats(tmt_moe* h, float* stat_device);
+
 /* moe_backward (moe.cu:479-545); must follow the forward call on the same handle.
  * dY (tokens,D) bf16. Outputs: dX (tokens,D) bf16 (written, not accumulated), dWrouter (E,D)
  * fp32 (written), dWup[e] / dWdown[e] fp32 with the shape of the weight (written; zero for an

@@ -479,7 +479,8 @@ void oracle_backward(const oracle_cfg* c, const uint16_t* X, const uint16_t* dY,
             for (int d = 0; d < D; ++d) {
                 float acc = 0;
                 for (int e = 0; e < E; ++e) {
-                    float wv = c->router_f32 ? ((const float*)Wr)[(size_t)e * D + d]
+                    // the input-gradient product runs on the router's bf16 work copy (model.cu:513, moe.cu:525-529)
+                    float wv = c->router_f32 ? rbf(((const float*)Wr)[(size_t)e * D + d])
                                              : bf2f(((const uint16_t*)Wr)[(size_t)e * D + d]);
                     acc += dlb[t * E + e] * wv;
                 }

@@ -185,6 +185,7 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         ep->stat_global = ep_alloc<float>(h, E + 1);
         h->ep_world_counts = ep_alloc<int>(h, E);
         h->ep = ep.release();
+        build_ep_maps(h, h->ep->Xs);
         return 0;
     } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
 }
@@ -317,16 +318,12 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
     exchange(h, true, ep->dYs, h->dYg, D);
     expert_backward(h, Wup, Wdown, dWup, dWdown);
     exchange(h, false, h->dXg, ep->dXr, D);
-    prof_mark(h, kPhRouterBwd);
-    CKE(launch_router_bwd(h->dims, h->rb, nullptr, 0, h->s_j, h->dlogits, aux, zcoef, h->ep_world_counts,
-                          (long)h->d.tokens * ep->G, h->stream));
-    prof_mark(h, kPhRouterDw);
-    CKE(launch_router_dw(h->dims, h->rb, h->dlogits, ep->Xs, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
+    // the router weight gradient of the local tokens, then summed over the ranks (the router is replicated)
+    router_backward(h, Wr, nullptr, ep->Xs, true, ep->dXr, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+                    (long)h->d.tokens * ep->G);
     NC(ep, ep->AllReduce(dWr, dWr, (size_t)E * D, ncclFloat32, ncclSum, ep->comm, h->stream));
-    prof_mark(h, kPhScatter);
-    CKE(launch_scatter(h->dims, h->rb, h->dlogits, Wr, ep->dXr, static_cast<uint16_t*>(dX), h->stream));
     prof_mark(h, -1);
-    h->launches += 5;
+    h->launches += 1;
 }
 
 const float* ep_stat(tmt_moe* h) { return h->ep ? h->ep->stat_global : h->rb.stat; }

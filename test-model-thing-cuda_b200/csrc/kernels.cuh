@@ -25,6 +25,7 @@ struct RouteBufs {
     int* slot_of;         // T*K   row of the assignment in the grouped buffers
     float* slotw;         // cap   gate weight of each grouped row (0 on pad rows)
     int* tok_of_slot;     // cap   token of each grouped row (-1 on pad rows)
+    int* split_poff;      // kMaxSplits+1 row ranges (multiples of kPad) the router weight-gradient GEMM splits its reduction into
     int* status;
 };
 
@@ -37,7 +38,8 @@ struct RouteDims {
 
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
                           const float* bias, cudaStream_t s);
-cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, cudaStream_t s);
+// splits: number of reduction ranges written to split_poff (1..kMaxSplits).
+cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s);
 // Xg[slot] = X[token]; pad rows zeroed; fills slot_of / slotw / tok_of_slot (moe.cu:103-140).
 cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s);
 // mode 0: Y = beta*Y + sum_j Yg[slot_j]               (two-matrix experts, gate applied by the GEMM)
@@ -53,15 +55,25 @@ cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const u
 // moe.cu:200-234. sw_part (may be NULL): per-row partial sums of w * dL/dw from the dH GEMM.
 // counts / n_norm: per-expert counts and token count the aux and z terms are normalised by
 // (the local ones on one GPU, the totals over all ranks under expert parallelism).
+// dl_t / dl_g (may be NULL): the gradient rounded to bf16 in the two layouts the tensor-core router
+// products read: dl_t[t][kw] token order (columns >= E zero), dl_g[slot_of[t,0]][mw] grouped order
+// (the buffer is zeroed beforehand, so every other grouped row contributes nothing).
 cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
-                              float* dlogits, float aux, float zcoef, const int* counts, long n_norm, cudaStream_t s);
+                              float* dlogits, float aux, float zcoef, const int* counts, long n_norm,
+                              uint16_t* dl_t, int kw, uint16_t* dl_g, int mw, cudaStream_t s);
 // dWr[e, :] = sum_t bf16(dlogits[t, e]) * X[t, :] with X[t] read from Xg[slot_of[t, 0]] (moe.cu:519-521).
 cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float* dlogits, const uint16_t* Xg,
                              float* partial, int chunks, float* dWr, cudaStream_t s);
 // dX[t] = sum_e bf16(dlogits[t, e]) * Wr[e] + sum_j dXg[slot_j]   (moe.cu:525-529, 238-249)
+// With dXr != NULL the router term was already computed by the tensor-core product: dX[t] = dXr[t] + sum_j ...
 cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
-                           const uint16_t* dXg, uint16_t* dX, cudaStream_t s);
+                           const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s);
+// out[i] = bf16(in[i])
+cudaError_t launch_to_bf16(const float* in, uint16_t* out, long n, cudaStream_t s);
+// dWr[e][d] = sum over `parts` partial products part[p][e][d] (row pitch of a part: mw rows x D)
+cudaError_t launch_reduce_parts(const float* parts, int nparts, int mw, int E, int D, float* dWr, cudaStream_t s);
 
 constexpr int kRouterDwChunks = 32;
+constexpr int kMaxSplits = 64;
 
 }  // namespace tmt

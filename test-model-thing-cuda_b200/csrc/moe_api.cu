@@ -87,8 +87,8 @@ T* dalloc(tmt_moe* h, size_t n) {
     return reinterpret_cast<T*>(p);
 }
 
-enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kNumActMaps };
-enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };
+enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kDlgMN, kDltK, kXsMN, kNumActMaps };
+enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };   // one more map follows the 4*E weight maps: the router, mn-major
 
 void build_act_maps(tmt_moe* h) {
     const uint64_t D = h->d.dim, H = h->d.hidden, cap = h->gcap;
@@ -103,6 +103,10 @@ void build_act_maps(tmt_moe* h) {
         make_map(&m[kDPK], h->dP, H, cap, 64, 128);
         make_map(&m[kHactMN], h->Hact, H, cap, 64, 64);
         make_map(&m[kDPMN], h->dP, H, cap, 64, 64);
+    }
+    if (h->dl_g) {
+        make_map(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, 64, 64);
+        make_map(&m[kDltK], h->dl_t, h->kw, (uint64_t)(h->d.tokens + kPad - 1) / kPad * kPad, 64, 128);
     }
     CK(cudaMemcpyAsync(h->act_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
 }
@@ -247,7 +251,12 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
     prof_mark(h, kPhRouter);
     CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream));
     prof_mark(h, kPhScan);
-    CK(launch_scan(h->dims, h->rb, h->stream));
+    CK(launch_scan(h->dims, h->rb, h->splits, h->stream));
+    const int plain = (h->dims.T + kPad - 1) / kPad;
+    if (h->plain_num && plain != h->plain_num_host) {
+        CK(cudaMemcpyAsync(h->plain_num, &plain, sizeof(int), cudaMemcpyHostToDevice, h->stream));
+        h->plain_num_host = plain;
+    }
     prof_mark(h, kPhDispatch);
     CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream));
     h->launches += 3;
@@ -336,20 +345,89 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
     CK(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), h->Yg, h->dYg, h->s_j, H == 0 ? 1 : 0, h->stream));
     h->launches += 1;
     expert_backward(h, Wup, Wdown, dWup, dWdown);
-    if (E > 1) {
-        prof_mark(h, kPhRouterBwd);
-        CK(launch_router_bwd(h->dims, h->rb, H > 0 ? h->sw_part : nullptr, h->sw_ld, h->s_j, h->dlogits, aux, zcoef,
-                             h->rb.counts, (long)h->dims.T, h->stream));
-        prof_mark(h, kPhRouterDw);
-        CK(launch_router_dw(h->dims, h->rb, h->dlogits, h->Xg, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
-        h->launches += 3;
-    } else {
+    router_backward(h, Wr, H > 0 ? h->sw_part : nullptr, h->Xg, false, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef,
+                    h->rb.counts, (long)h->dims.T);
+    prof_mark(h, -1);
+}
+
+void build_ep_maps(tmt_moe* h, const uint16_t* Xs) {
+    if (h->d.gemm_impl != TMT_MOE_GEMM_TCGEN05) return;
+    CUtensorMap m;
+    memset(&m, 0, sizeof m);
+    make_map(&m, Xs, h->d.dim, h->dims.cap, 64, 64);
+    CK(cudaMemcpyAsync(h->act_maps + kXsMN, &m, sizeof m, cudaMemcpyHostToDevice, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+}
+
+void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uint16_t* grouped_x, bool x_is_ep,
+                     const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm) {
+    const int D = h->d.dim, E = h->d.experts;
+    if (E == 1) {      // dense shortcut: no router gradient (moe.cu:488-494)
         CK(cudaMemsetAsync(dWr, 0, (size_t)E * D * sizeof(float), h->stream));
+        prof_mark(h, kPhScatter);
+        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, nullptr, dX, h->stream));
+        h->launches += 1;
+        return;
+    }
+    const bool tc = h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05;
+    prof_mark(h, kPhRouterBwd);
+    if (tc) CK(cudaMemsetAsync(h->dl_g, 0, (size_t)h->dims.cap * h->mw * 2, h->stream));
+    CK(launch_router_bwd(h->dims, h->rb, sw_part, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, counts, n_norm,
+                         tc ? h->dl_t : nullptr, h->kw, tc ? h->dl_g : nullptr, h->mw, h->stream));
+    h->launches += 1;
+    if (!tc) {
+        prof_mark(h, kPhRouterDw);
+        CK(launch_router_dw(h->dims, h->rb, h->dlogits, grouped_x, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
+        prof_mark(h, kPhScatter);
+        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, nullptr, dX, h->stream));
+        h->launches += 3;
+        return;
+    }
+    // router weights as a bf16 [E][D] matrix for the token-order product (the reference's work copy, model.cu:513)
+    const uint16_t* wr16 = static_cast<const uint16_t*>(Wr);
+    if (h->dims.router_f32) {
+        CK(launch_to_bf16(static_cast<const float*>(Wr), h->wr_bf16, (long)E * D, h->stream));
+        h->launches += 1;
+        wr16 = h->wr_bf16;
+    }
+    if (h->wr_seen != wr16) {
+        CUtensorMap m;
+        memset(&m, 0, sizeof m);
+        make_map(&m, wr16, D, E, 64, 64);
+        CK(cudaMemcpyAsync(h->w_maps + (size_t)kNumWMaps * h->local_experts, &m, sizeof m, cudaMemcpyHostToDevice, h->stream));
+        h->wr_seen = wr16;
+    }
+    prof_mark(h, kPhRouterDw);
+    {   // dWr = dl_g^T * X_grouped, reduction split into h->splits row ranges, then summed
+        GemmParams p = base_params(h);
+        p.mode = kRedRagged;
+        p.mapA = h->act_maps + kDlgMN; p.a_stride = 0;
+        p.mapB = h->act_maps + (x_is_ep ? kXsMN : kXgMN); p.b_stride = 0;
+        p.a_mn = 1; p.b_mn = 1;
+        p.a_boxes = kBM / 64; p.b_boxes = kBN / 64;
+        p.tx_bytes = (p.a_boxes + p.b_boxes) * 8192;
+        p.M = h->mw; p.N = D; p.experts = h->splits; p.poff = h->rb.split_poff;
+        p.epi = kEpiF32; p.outF = h->dwr_part_ptrs; p.ldc = D;
+        CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+        CK(launch_reduce_parts(h->dwr_partial, h->splits, h->mw, E, D, dWr, h->stream));
+        h->launches += 2;
     }
     prof_mark(h, kPhScatter);
-    CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, h->dXg, static_cast<uint16_t*>(dX), h->stream));
-    prof_mark(h, -1);
-    h->launches += 1;
+    {   // dXr = dl_t * Wr (one k block per 64 experts), then dX = dXr + sum_j dXg[slot_j]
+        GemmParams p = base_params(h);
+        p.mode = kRowsRagged;
+        p.mapA = h->act_maps + kDltK; p.a_stride = 0;
+        p.mapB = h->w_maps + (size_t)kNumWMaps * h->local_experts; p.b_stride = 0;
+        p.a_mn = 0; p.b_mn = 1;
+        p.b_boxes = kBN / 64;
+        p.tx_bytes = kBM * kBK * 2 + p.b_boxes * 8192;
+        p.N = D; p.K = h->kw; p.experts = 1;
+        p.tile_expert = h->plain_tiles; p.num_m_tiles = h->plain_num;
+        p.epi = kEpiBf16; p.out0 = h->dXr; p.ldc = D;
+        CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream));
+        h->launches += 2;
+    }
 }
 
 tmt_moe* create_impl(const tmt_moe_desc* dsc) {
@@ -407,6 +485,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     b.slot_of = dalloc<int>(h, (size_t)T * K);
     b.slotw = dalloc<float>(h, cap);
     b.tok_of_slot = dalloc<int>(h, cap);
+    b.split_poff = dalloc<int>(h, kMaxSplits + 1);
     b.status = dalloc<int>(h, 1);
     CK(cudaMemsetAsync(b.status, 0, sizeof(int), h->stream));
     h->bias = dalloc<float>(h, E);
@@ -418,7 +497,28 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
         h->dXg = dalloc<uint16_t>(h, (size_t)gcap * D);
         h->s_j = dalloc<float>(h, (size_t)T * K);
         h->dlogits = dalloc<float>(h, (size_t)T * E);
-        h->dwr_partial = dalloc<float>(h, (size_t)kRouterDwChunks * E * D);
+        if (d.gemm_impl == TMT_MOE_GEMM_TCGEN05 && E > 1) {
+            h->kw = (E + 63) / 64 * 64;
+            h->mw = (E + kBM - 1) / kBM * kBM;
+            const int tiles = (h->mw / kBM) * ((D + kBN - 1) / kBN);
+            h->splits = std::max(1, std::min(kMaxSplits, h->num_sms / tiles));
+            const size_t tpad = (size_t)(T + kPad - 1) / kPad * kPad;
+            h->dl_t = dalloc<uint16_t>(h, tpad * h->kw);
+            CK(cudaMemsetAsync(h->dl_t, 0, tpad * h->kw * 2, h->stream));
+            h->dl_g = dalloc<uint16_t>(h, (size_t)cap * h->mw);
+            h->dXr = dalloc<uint16_t>(h, tpad * D);
+            h->wr_bf16 = dalloc<uint16_t>(h, (size_t)E * D);
+            h->dwr_partial = dalloc<float>(h, (size_t)h->splits * h->mw * D);
+            h->dwr_part_ptrs = dalloc<float*>(h, h->splits);
+            std::vector<float*> ptrs(h->splits);
+            for (int i = 0; i < h->splits; ++i) ptrs[i] = h->dwr_partial + (size_t)i * h->mw * D;
+            CK(cudaMemcpyAsync(h->dwr_part_ptrs, ptrs.data(), ptrs.size() * sizeof(float*), cudaMemcpyHostToDevice, h->stream));
+            h->plain_tiles = dalloc<int>(h, tpad / kPad);
+            CK(cudaMemsetAsync(h->plain_tiles, 0, tpad / kPad * sizeof(int), h->stream));
+            h->plain_num = dalloc<int>(h, 1);
+        } else {
+            h->dwr_partial = dalloc<float>(h, (size_t)kRouterDwChunks * E * D);
+        }
         if (H > 0) {
             h->P = dalloc<uint16_t>(h, (size_t)gcap * H);
             h->dP = dalloc<uint16_t>(h, (size_t)gcap * H);
@@ -430,7 +530,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
         h->dYg = h->Xg; h->dP = h->Hact;
     }
     h->act_maps = dalloc<CUtensorMap>(h, kNumActMaps);
-    h->w_maps = dalloc<CUtensorMap>(h, (size_t)kNumWMaps * h->local_experts);
+    h->w_maps = dalloc<CUtensorMap>(h, (size_t)kNumWMaps * h->local_experts + 1);
     h->up_ptrs = dalloc<const uint16_t*>(h, h->local_experts);
     h->down_ptrs = dalloc<const uint16_t*>(h, h->local_experts);
     h->gup_ptrs = dalloc<float*>(h, h->local_experts);
@@ -532,6 +632,14 @@ int tmt_moe_stats(tmt_moe* h, float* stat, int64_t* counts, float* aux) {
     })
 }
 
+int tmt_moe_copy_stats(tmt_moe* h, float* stat_device) {
+    if (!h || !stat_device) { set_error("null argument"); return -1; }
+    GUARD({
+        CK(cudaSetDevice(h->d.device));
+        CK(cudaMemcpyAsync(stat_device, ep_stat(h), (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
+    })
+}
+
 int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter, const void* const* Wup,
                       const void* const* Wdown, float* dWrouter, float* const* dWup, float* const* dWdown, void* Y_host,
                       void* dX_host, float* stat_host, float beta, float aux, float zcoef, int tokens) {
@@ -590,7 +698,7 @@ long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes
         else if (s == "P") { src = h->P; n = (size_t)h->dims.cap * h->d.hidden * 2; }
         else if (s == "Hact") { src = h->Hact; n = (size_t)h->dims.cap * h->d.hidden * 2; }
         else if (s == "dP") { src = h->d.training ? h->dP : nullptr; n = (size_t)h->dims.cap * h->d.hidden * 2; }
-        else if (s == "sw_part") { src = h->sw_part; n = (size_t)h->dims.cap * h->sw_ld * 4; }
+        else if (s == "sw_part") { src = h->sw_part; n = (size_t)h->gcap * h->sw_ld * 4; }
         else throw std::runtime_error("unknown tensor name: " + s);
         if (!src) throw std::runtime_error("tensor not kept by this handle: " + s);
         if (n > dst_bytes) throw std::runtime_error("destination too small for " + s);

@@ -50,6 +50,14 @@ struct tmt_moe {
     uint16_t *dYg = nullptr, *dP = nullptr, *dXg = nullptr;
     float* sw_part = nullptr; int sw_ld = 0;
     float *s_j = nullptr, *dlogits = nullptr, *dwr_partial = nullptr;
+    // tensor-core router gradient products: bf16 gradient in token order (kw columns) and in grouped
+    // order (mw columns), the router term of dX, the split-reduction partials of dWr and their pointers,
+    // a bf16 copy of an fp32 router, and the one-expert tile table of the token-order product
+    uint16_t *dl_t = nullptr, *dl_g = nullptr, *dXr = nullptr, *wr_bf16 = nullptr;
+    int kw = 0, mw = 0, splits = 1;
+    float** dwr_part_ptrs = nullptr;
+    int* plain_tiles = nullptr; int* plain_num = nullptr; int plain_num_host = -1;
+    const void* wr_seen = nullptr;
     CUtensorMap* act_maps = nullptr;
     CUtensorMap* w_maps = nullptr;
     const uint16_t** up_ptrs = nullptr; const uint16_t** down_ptrs = nullptr;
@@ -88,5 +96,10 @@ const float* ep_stat(tmt_moe* h);
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped);
 void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue);
 void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown);
+// Router backward after the expert products: dlogits, dWr (local contribution) and dX.
+// grouped_x / x_is_ep: the token-side grouped copy of X (Xg, or the send buffer under expert parallelism).
+void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uint16_t* grouped_x, bool x_is_ep,
+                     const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm);
+void build_ep_maps(tmt_moe* h, const uint16_t* Xs);
 void prof_mark(tmt_moe* h, int phase);
 }  // namespace tmt

@@ -196,7 +196,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
 // One thread per token; dlogits doubles as scratch exactly as in moe.cu:213-221.
 __global__ void router_bwd_kernel(const RouteDims d, const RouteBufs b, const float* __restrict__ sw_part, int sw_ld,
                                   float* __restrict__ s_j, float* __restrict__ dlogits, float aux, float zcoef,
-                                  const int* __restrict__ counts, long n_norm) {
+                                  const int* __restrict__ counts, long n_norm, uint16_t* __restrict__ dl_t, int kw,
+                                  uint16_t* __restrict__ dl_g, int mw) {
     const long r = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= d.T) return;
     const int E = d.E, K = d.K;
@@ -234,6 +235,30 @@ __global__ void router_bwd_kernel(const RouteDims d, const RouteBufs b, const fl
         const float p = probs[e];
         g[e] += aux * E / nn * p * (counts[e] / nk - expected) + zcoef * 2.f / nn * lse * p;
     }
+    if (dl_t) {
+        uint16_t* row = dl_t + r * kw;
+        for (int e = 0; e < kw; ++e) row[e] = e < E ? f2bf(g[e]) : (uint16_t)0;
+    }
+    if (dl_g) {
+        const int slot = b.slot_of[r * K];
+        if (slot >= 0 && slot < d.cap) {
+            uint16_t* row = dl_g + (long)slot * mw;
+            for (int e = 0; e < E; ++e) row[e] = f2bf(g[e]);
+        }
+    }
+}
+
+__global__ void to_bf16_kernel(const float* __restrict__ in, uint16_t* __restrict__ out, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = f2bf(in[i]);
+}
+
+__global__ void reduce_parts_kernel(const float* __restrict__ parts, int nparts, int mw, int E, int D, float* __restrict__ dWr) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)E * D) return;
+    float s = 0.0f;
+    for (int p = 0; p < nparts; ++p) s += parts[(long)p * mw * D + i];     // rows e < E of every part, same [e][d] pitch
+    dWr[i] = s;
 }
 
 // Partial router weight gradient of one token chunk: block = 256 threads x 2 columns.
@@ -303,13 +328,14 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) scatter_kernel(const Rout
                                                                        const float* __restrict__ dlogits,
                                                                        const void* __restrict__ Wr,
                                                                        const uint16_t* __restrict__ dXg,
+                                                                       const uint16_t* __restrict__ dXr,
                                                                        uint16_t* __restrict__ dX) {
     extern __shared__ float dls[];     // [warps][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
     if (t >= d.T) return;
     float* mine = dls + warp * d.E;
-    const bool router = d.E > 1;       // dense shortcut has no router gradient (moe.cu:488-494)
+    const bool router = d.E > 1 && dXr == nullptr;     // dense shortcut has no router gradient (moe.cu:488-494)
     if (router)
         for (int e = lane; e < d.E; e += 32) mine[e] = round_bf(dlogits[t * d.E + e]);
     int slot = -1;
@@ -326,6 +352,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) scatter_kernel(const Rout
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        if (dXr != nullptr && d.E > 1) unpack8(ldg16(dXr + t * d.D + v * 8), acc);
         if (router) {
             for (int e = 0; e < d.E; ++e) {
                 const float gq = mine[e];
@@ -378,8 +405,21 @@ cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const u
 }
 
 cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
-                              float* dlogits, float aux, float zcoef, const int* counts, long n_norm, cudaStream_t s) {
-    router_bwd_kernel<<<(d.T + 127) / 128, 128, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef, counts, n_norm);
+                              float* dlogits, float aux, float zcoef, const int* counts, long n_norm,
+                              uint16_t* dl_t, int kw, uint16_t* dl_g, int mw, cudaStream_t s) {
+    router_bwd_kernel<<<(d.T + 127) / 128, 128, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef, counts, n_norm,
+                                                        dl_t, kw, dl_g, mw);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_to_bf16(const float* in, uint16_t* out, long n, cudaStream_t s) {
+    to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(in, out, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_parts(const float* parts, int nparts, int mw, int E, int D, float* dWr, cudaStream_t s) {
+    const long n = (long)E * D;
+    reduce_parts_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(parts, nparts, mw, E, D, dWr);
     return cudaGetLastError();
 }
 
@@ -398,10 +438,10 @@ cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float
 }
 
 cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
-                           const uint16_t* dXg, uint16_t* dX, cudaStream_t s) {
+                           const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s) {
     const size_t smem = (size_t)kWarpsPerBlock * d.E * sizeof(float);
-    if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dX);
-    else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dX);
+    if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX);
+    else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX);
     return cudaGetLastError();
 }
 

@@ -9,12 +9,15 @@
 // sequential fp32 FMA in increasing d; chains are added ((c0+c1)+(c2+c3))+((c4+c5)+(c6+c7)).
 // Here a chain is one lane of an 8-lane group reading 16-byte vectors, and the tree is
 // the xor-butterfly 1, 2, 4 (fp32 addition is commutative, so every lane ends equal).
+// The products themselves run as a register-tiled fp32 FMA GEMM on the CUDA cores (tensor
+// cores would fix their own accumulation order, which the CPU statement could not mirror).
 #include "kernels.cuh"
 
 namespace tmt {
 namespace {
 
-constexpr int kRouterThreads = 256;
+constexpr int kDC = 128;            // d elements staged per pipeline step (16 vectors of 8)
+constexpr int kTT = 4;              // tokens per thread
 
 struct RouterArgs {
     const uint16_t* X; const void* Wr; const float* bias;
@@ -22,67 +25,136 @@ struct RouterArgs {
     RouteBufs b;
 };
 
-template <int EC, bool WF32>
-__global__ void __launch_bounds__(kRouterThreads) router_kernel(const RouterArgs a) {
-    extern __shared__ float lg[];                 // [kTokBlock][E] logits, later probabilities
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;      // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Block = 64 tokens x (TE * ESLABS) experts per expert pass; 4 * ESLABS warps. Warp = one slab of 16
+// tokens x TE experts; lane = (chain s = lane & 7, token group g = lane >> 3); a thread keeps
+// kTT x TE accumulators of its chain. X (bf16) and the router rows (fp32 split into two 16-byte
+// planes, or bf16) are staged in shared memory by cp.async, double buffered, kDC columns at a time,
+// so that the 8 chains of a group read 128 contiguous bytes.
+template <int TE, int ESLABS, bool WF32>
+__global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a) {
+    constexpr int EP = TE * ESLABS;                 // experts per pass
+    constexpr int NTHR = 128 * ESLABS;
+    constexpr int XS_BYTES = kTokBlock * kDC * 2;
+    constexpr int WS_BYTES = EP * kDC * (WF32 ? 4 : 2);
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* stage[2] = {smem, smem + XS_BYTES + WS_BYTES};
+    float* lg = reinterpret_cast<float*>(smem + 2 * (XS_BYTES + WS_BYTES));     // [kTokBlock][E]
     __shared__ int sidx[kTokBlock * 8];
     __shared__ float zs[kTokBlock];
     const int E = a.E, K = a.K, D = a.D;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int s = lane & 7, g = lane >> 3;
+    const int tslab = warp & 3, eslab = warp >> 2;
     const int nvec = D >> 3;
+    const int nchunks = (D + kDC - 1) / kDC;
+    const long tok0 = (long)blockIdx.x * kTokBlock;
     const unsigned full = 0xffffffffu;
 
-    for (int pass = 0; pass < kTokBlock / 32; ++pass) {
-        const int tb = pass * 32 + warp * 4 + g;
-        const long t = (long)blockIdx.x * kTokBlock + tb;
-        const bool valid = t < a.T;
-        const uint16_t* xrow = a.X + (valid ? t : 0) * (long)D;
-        // ---- dot products, EC experts at a time ----
-        for (int ec0 = 0; ec0 < E; ec0 += EC) {
-            float acc[EC];
+    for (int ep0 = 0; ep0 < E; ep0 += EP) {
+        auto load_chunk = [&](int k, uint8_t* buf) {
+            const int v0 = k * (kDC / 8);
+            // X: 64 rows x 16 vectors of 16 bytes
+            for (int q = threadIdx.x; q < kTokBlock * (kDC / 8); q += NTHR) {
+                const int row = q >> 4, v = q & 15;
+                const long t = tok0 + row;
+                const bool ok = t < a.T && v0 + v < nvec;
+                cp_async16(buf + (row * (kDC / 8) + v) * 16, a.X + (ok ? t * D + (long)(v0 + v) * 8 : 0), ok);
+            }
+            uint8_t* wb = buf + XS_BYTES;
+            if constexpr (WF32) {
+                // fp32 rows: vector v = two 16-byte halves, stored in two planes [half][expert][vector]
+                for (int q = threadIdx.x; q < EP * (kDC / 4); q += NTHR) {
+                    const int row = q >> 5, piece = q & 31, v = piece >> 1, half = piece & 1;
+                    const bool ok = ep0 + row < E && v0 + v < nvec;
+                    const float* src = reinterpret_cast<const float*>(a.Wr) + (ok ? (long)(ep0 + row) * D + (long)(v0 + v) * 8 + half * 4 : 0);
+                    cp_async16(wb + ((half * EP + row) * (kDC / 8) + v) * 16, src, ok);
+                }
+            } else {
+                for (int q = threadIdx.x; q < EP * (kDC / 8); q += NTHR) {
+                    const int row = q >> 4, v = q & 15;
+                    const bool ok = ep0 + row < E && v0 + v < nvec;
+                    const uint16_t* src = reinterpret_cast<const uint16_t*>(a.Wr) + (ok ? (long)(ep0 + row) * D + (long)(v0 + v) * 8 : 0);
+                    cp_async16(wb + (row * (kDC / 8) + v) * 16, src, ok);
+                }
+            }
+            cp_async_commit();
+        };
+        float acc[kTT][TE];
 #pragma unroll
-            for (int e = 0; e < EC; ++e) acc[e] = 0.0f;
-            if (valid) {
-                for (int v = s; v < nvec; v += 8) {
-                    const uint4 xv = ldg16(xrow + v * 8);
-                    float x[8] = {bf_lo(xv.x), bf_hi(xv.x), bf_lo(xv.y), bf_hi(xv.y),
-                                  bf_lo(xv.z), bf_hi(xv.z), bf_lo(xv.w), bf_hi(xv.w)};
+        for (int i = 0; i < kTT; ++i)
 #pragma unroll
-                    for (int e = 0; e < EC; ++e) {
-                        if (ec0 + e < E) {
-                            float wv[8];
-                            if constexpr (WF32) {
-                                const float* wp = reinterpret_cast<const float*>(a.Wr) + (long)(ec0 + e) * D + v * 8;
-                                const float4 w0 = __ldg(reinterpret_cast<const float4*>(wp));
-                                const float4 w1 = __ldg(reinterpret_cast<const float4*>(wp) + 1);
-                                wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w;
-                                wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
-                            } else {
-                                const uint4 w4 = ldg16(reinterpret_cast<const uint16_t*>(a.Wr) + (long)(ec0 + e) * D + v * 8);
-                                wv[0] = bf_lo(w4.x); wv[1] = bf_hi(w4.x); wv[2] = bf_lo(w4.y); wv[3] = bf_hi(w4.y);
-                                wv[4] = bf_lo(w4.z); wv[5] = bf_hi(w4.z); wv[6] = bf_lo(w4.w); wv[7] = bf_hi(w4.w);
-                            }
+            for (int e = 0; e < TE; ++e) acc[i][e] = 0.0f;
+        load_chunk(0, stage[0]);
+        for (int k = 0; k < nchunks; ++k) {
+            if (k + 1 < nchunks) { load_chunk(k + 1, stage[(k + 1) & 1]); cp_async_wait<1>(); }
+            else cp_async_wait<0>();
+            __syncthreads();
+            const uint8_t* xb = stage[k & 1];
+            const uint8_t* wb = xb + XS_BYTES;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                const int v = c * 8 + s;                         // this chain's vector inside the chunk
+                if (k * (kDC / 8) + c * 8 < nvec) {              // uniform: nvec is a multiple of 8
+                    float x[kTT][8];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[e] = __fmaf_rn(x[i], wv[i], acc[e]);
+                    for (int i = 0; i < kTT; ++i) {
+                        const int row = tslab * 16 + g * kTT + i;
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xb + (row * (kDC / 8) + v) * 16);
+                        x[i][0] = bf_lo(xv.x); x[i][1] = bf_hi(xv.x); x[i][2] = bf_lo(xv.y); x[i][3] = bf_hi(xv.y);
+                        x[i][4] = bf_lo(xv.z); x[i][5] = bf_hi(xv.z); x[i][6] = bf_lo(xv.w); x[i][7] = bf_hi(xv.w);
+                    }
+#pragma unroll
+                    for (int e = 0; e < TE; ++e) {
+                        const int row = eslab * TE + e;
+                        float w[8];
+                        if constexpr (WF32) {
+                            const float4 w0 = *reinterpret_cast<const float4*>(wb + ((0 * EP + row) * (kDC / 8) + v) * 16);
+                            const float4 w1 = *reinterpret_cast<const float4*>(wb + ((1 * EP + row) * (kDC / 8) + v) * 16);
+                            w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+                        } else {
+                            const uint4 wv = *reinterpret_cast<const uint4*>(wb + (row * (kDC / 8) + v) * 16);
+                            w[0] = bf_lo(wv.x); w[1] = bf_hi(wv.x); w[2] = bf_lo(wv.y); w[3] = bf_hi(wv.y);
+                            w[4] = bf_lo(wv.z); w[5] = bf_hi(wv.z); w[6] = bf_lo(wv.w); w[7] = bf_hi(wv.w);
                         }
+#pragma unroll
+                        for (int i = 0; i < kTT; ++i)
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) acc[i][e] = __fmaf_rn(x[i][q], w[q], acc[i][e]);
                     }
                 }
             }
+            __syncthreads();
+        }
+        // chain tree ((c0+c1)+(c2+c3))+((c4+c5)+(c6+c7)), then lane s keeps every 8th value
 #pragma unroll
-            for (int e = 0; e < EC; ++e) {
-                float v = acc[e];
+        for (int i = 0; i < kTT; ++i)
+#pragma unroll
+            for (int e = 0; e < TE; ++e) {
+                float v = acc[i][e];
                 v = __fadd_rn(v, __shfl_xor_sync(full, v, 1));
                 v = __fadd_rn(v, __shfl_xor_sync(full, v, 2));
                 v = __fadd_rn(v, __shfl_xor_sync(full, v, 4));
-                if (ec0 + e < E && (e & 7) == s) {
-                    if (a.bias) v = __fadd_rn(v, a.bias[ec0 + e]);
-                    lg[tb * E + ec0 + e] = valid ? v : 0.0f;
+                const int ge = ep0 + eslab * TE + e;
+                if (((i * TE + e) & 7) == s && ge < E) {
+                    if (a.bias) v = __fadd_rn(v, a.bias[ge]);
+                    lg[(tslab * 16 + g * kTT + i) * E + ge] = v;
                 }
             }
-        }
-        __syncwarp();
-        // ---- softmax, top-k (on logits, lowest index wins ties), gate weights ----
+    }
+    __syncthreads();
+    // ---- softmax, top-k (on logits, lowest index wins ties), gate weights: 8 lanes per token ----
+    for (int tb = warp * 4 + g; tb < kTokBlock; tb += (NTHR / 32) * 4) {
+        const long t = tok0 + tb;
+        const bool valid = t < a.T;
         float* L = lg + tb * E;
         float mx = -INFINITY;
         for (int e = s; e < E; e += 8) mx = fmaxf(mx, L[e]);
@@ -133,14 +205,14 @@ __global__ void __launch_bounds__(kRouterThreads) router_kernel(const RouterArgs
     __syncthreads();
     // ---- block level: stable ranks, counts, statistics partials ----
     const int n_asg = kTokBlock * K;
-    for (int i = threadIdx.x; i < n_asg; i += blockDim.x) {
+    for (int i = threadIdx.x; i < n_asg; i += NTHR) {
         const int e = sidx[i];
         if (e < 0) continue;
         int r = 0;
         for (int q = 0; q < i; ++q) r += (sidx[q] == e);
         a.b.rank[(long)blockIdx.x * n_asg + i] = r;
     }
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    for (int e = threadIdx.x; e < E; e += NTHR) {
         int c = 0;
         for (int q = 0; q < n_asg; ++q) c += (sidx[q] == e);
         float sp = 0.0f;
@@ -157,7 +229,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_kernel(const RouterArgs
 
 // One block. Exclusive scan of the per-block counts per expert, totals, true and padded
 // group starts, tile -> expert table, statistics.
-__global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const RouteBufs b, int NB) {
+__global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const RouteBufs b, int NB, int splits) {
     __shared__ int cnt_s[256];
     __shared__ int poff_s[257];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -217,26 +289,29 @@ __global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const Rou
         }
         b.tile_expert[i] = e;
     }
+    // even split of the rows in use into `splits` ranges of whole tiles
+    for (int i = threadIdx.x; i <= splits; i += blockDim.x) b.split_poff[i] = (int)((long)used * i / splits) * kPad;
 }
 
-template <int EC, bool WF32>
+template <int TE, int ESLABS, bool WF32>
 cudaError_t launch_router_t(const RouterArgs& a, int nb, cudaStream_t s) {
-    const size_t smem = (size_t)kTokBlock * a.E * sizeof(float);
+    constexpr int EP = TE * ESLABS;
+    const size_t smem = 2 * ((size_t)kTokBlock * kDC * 2 + (size_t)EP * kDC * (WF32 ? 4 : 2)) + (size_t)kTokBlock * a.E * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(router_kernel<EC, WF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(router_kernel<TE, ESLABS, WF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    router_kernel<EC, WF32><<<nb, kRouterThreads, smem, s>>>(a);
+    router_kernel<TE, ESLABS, WF32><<<nb, 128 * ESLABS, smem, s>>>(a);
     return cudaGetLastError();
 }
 
 template <bool WF32>
 cudaError_t launch_router_w(const RouterArgs& a, int nb, cudaStream_t s) {
-    if (a.E <= 4) return launch_router_t<4, WF32>(a, nb, s);
-    if (a.E <= 8) return launch_router_t<8, WF32>(a, nb, s);
-    if (a.E <= 16) return launch_router_t<16, WF32>(a, nb, s);
-    if (a.E <= 32) return launch_router_t<32, WF32>(a, nb, s);
-    return launch_router_t<64, WF32>(a, nb, s);
+    if (a.E <= 4) return launch_router_t<4, 1, WF32>(a, nb, s);
+    if (a.E <= 8) return launch_router_t<8, 1, WF32>(a, nb, s);
+    if (a.E <= 16) return launch_router_t<16, 1, WF32>(a, nb, s);
+    if (a.E <= 32) return launch_router_t<16, 2, WF32>(a, nb, s);
+    return launch_router_t<16, 4, WF32>(a, nb, s);
 }
 
 }  // namespace
@@ -248,9 +323,9 @@ cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t
     return d.router_f32 ? launch_router_w<true>(a, nb, s) : launch_router_w<false>(a, nb, s);
 }
 
-cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, cudaStream_t s) {
+cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s) {
     const int nb = (d.T + kTokBlock - 1) / kTokBlock;
-    scan_kernel<<<1, 1024, 0, s>>>(d, b, nb);
+    scan_kernel<<<1, 1024, 0, s>>>(d, b, nb, splits);
     return cudaGetLastError();
 }
 

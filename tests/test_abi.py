@@ -46,3 +46,34 @@ def test_phase_names(lib):
     n = lib.tmt_moe_num_phases()
     names = [lib.tmt_moe_phase_name(i).decode() for i in range(n)]
     assert names[0] == "router" and "gemm_up" in names and "exchange" in names and len(set(names)) == n
+
+
+def test_reference_shim_compiles(tmp_path):
+    """The source-level drop-in (shim/moe.h) accepts the calls the reference's own harness makes
+    (tmt-cuda/src/profile.cu:32-55) with the reference's argument lists."""
+    import shutil
+    import subprocess
+    cuda_inc = "/usr/local/cuda/include"
+    if shutil.which("g++") is None or not os.path.exists(os.path.join(cuda_inc, "cuda_bf16.h")):
+        pytest.skip("needs g++ and the CUDA headers")
+    src = tmp_path / "use_shim.cpp"
+    src.write_text("""
+#include "%s/test-model-thing-cuda_b200/shim/moe.h"
+int run() {
+    int N = 2048, E = 8, K = 2, D = 1280;
+    bf16 *X = nullptr, *Y = nullptr, *dY = nullptr, *dX = nullptr, *Wr = nullptr, *Wx[16] = {nullptr};
+    float *dWr = nullptr, *dWx[16] = {nullptr};
+    MoeKeep keep; MoeWs ws;
+    moe_keep_alloc(keep, N, E, K, D);
+    moe_ws_alloc(ws, N, E, K, D);
+    float aux = moe_forward(X, Wr, Wx, Y, keep, ws, N, E, K, D);
+    moe_backward(dY, Wx, Wr, dWr, dWx, dX, keep, ws, 0.01f, 0.001f);
+    float hsum[17] = {0};
+    aux += moe_aux_from(keep, hsum) + keep.zloss + keep.hcnt[0];
+    moe_keep_free(keep); moe_ws_free(ws);
+    return (int)aux;
+}
+""" % ROOT)
+    r = subprocess.run(["g++", "-std=c++17", "-I", cuda_inc, "-c", str(src), "-o", str(tmp_path / "use_shim.o")],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0, r.stdout

@@ -1,0 +1,99 @@
+"""Expert parallelism on 2 GPUs (skipped with fewer): every rank routes its own tokens, rows
+travel to the owning rank over NCCL and back. Each rank's outputs and gradients must equal the
+oracle's for the concatenated batch: routing is per token, expert outputs are per row, the
+statistics, the aux/z normalisation and the router gradient are over all ranks' tokens."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    try:
+        sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        import synth
+        import gpu_util as G
+        import tmt_moe_b200 as M
+        from oracle import oracle as O
+        T, D, H, E, K = 900, 256, 384, 8, 2
+        rf = True
+        data = [synth.make(T, D, H, E, K, rf, seed=70 + g, w_std=0.06, router_std=0.1, dy_std=0.05) for g in range(world)]
+        allX = np.concatenate([d["X"] for d in data])
+        alldY = np.concatenate([d["dY"] for d in data])
+        base = data[0]                       # weights of rank 0's generator are THE weights (replicated router)
+        ref = O.forward(allX, base["Wr"], base["Wup"], base["Wdown"], K)
+        rb = O.backward(ref, alldY, 0.1, 0.001)
+        EL = E // world
+        mine = dict(base, X=data[rank]["X"], dY=data[rank]["dY"],
+                    Wup=base["Wup"][rank * EL:(rank + 1) * EL], Wdown=base["Wdown"][rank * EL:(rank + 1) * EL])
+        moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32, training=True, device=rank, ep_world=world, ep_rank=rank,
+                    ep_capacity_factor=2.0)
+        moe.ep_init_torch(dist)
+        X, dY, Wr = G.dev(mine["X"]), G.dev(mine["dY"]), G.dev(mine["Wr"])
+        Wup_all, Wdown_all = G.dev(mine["Wup"]), G.dev(mine["Wdown"])
+        Wup, Wdown = [Wup_all[e] for e in range(EL)], [Wdown_all[e] for e in range(EL)]
+        Y = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+        dX = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+        dWr = torch.full((E, D), float("nan"), device="cuda")
+        dWup_all = torch.full(tuple(Wup_all.shape), float("nan"), device="cuda")
+        dWdown_all = torch.full(tuple(Wdown_all.shape), float("nan"), device="cuda")
+        for it in range(2):                  # twice: the second step reuses every buffer
+            moe.forward(X, Wr, Wup, Wdown, Y, 0.0)
+            moe.backward(dY, Wr, Wup, Wdown, dWr, [dWup_all[e] for e in range(EL)], [dWdown_all[e] for e in range(EL)],
+                         dX, 0.1, 0.001)
+            torch.cuda.synchronize()
+        assert moe.device_status() == 0
+        sl = slice(rank * T, (rank + 1) * T)
+        np.testing.assert_array_equal(moe.read("idx"), ref["idx"][sl])
+        np.testing.assert_array_equal(moe.read("logits").view(np.uint32), ref["logits"][sl].view(np.uint32))
+        stat, counts, aux = moe.stats()
+        np.testing.assert_array_equal(counts, ref["counts"])
+        np.testing.assert_allclose(stat, ref["stat"], rtol=1e-4, atol=1e-6)
+        assert abs(aux - ref["aux"]) <= 1e-4 * abs(ref["aux"])
+        errs = {
+            "Y": synth.rel_l2(O.bf16_to_f32(G.host_u16(Y)), O.bf16_to_f32(ref["Y"][sl])),
+            "dX": synth.rel_l2(O.bf16_to_f32(G.host_u16(dX)), O.bf16_to_f32(rb["dX"][sl])),
+            "dWr": synth.rel_l2(dWr.cpu().numpy(), rb["dWr"]),
+            "dWup": synth.rel_l2(dWup_all.cpu().numpy(), rb["dWup"][rank * EL:(rank + 1) * EL]),
+            "dWdown": synth.rel_l2(dWdown_all.cpu().numpy(), rb["dWdown"][rank * EL:(rank + 1) * EL]),
+        }
+        assert errs["Y"] <= 1e-2 and max(errs.values()) <= 3e-2, errs
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok %s" % {k: "%.1e" % v for k, v in errs.items()}))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAIL: %s\n%s" % (exc, traceback.format_exc())))
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_two_gpus():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = []
+    try:
+        for _ in procs:
+            res.append(q.get(timeout=240))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    for rank, msg in res:
+        assert msg.startswith("ok"), "rank %d: %s" % (rank, msg)
+    assert len(res) == world
