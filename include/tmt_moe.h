@@ -156,6 +156,19 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128);
 long long tmt_moe_ep_plan(int G, int r, int E, int pad, const int* cnt_all, int* tok_poff, int* x_counts,
                           int* x_poff, int* src_off);
 
+/* ---- entry point that allocates nothing (no counterpart in the reference) ---------------
+ * dWrouter[e, d] = sum_t bf16(dlogits[t, e]) * X[t, d], the router_dw phase of
+ * tmt_moe_backward, for callers that cannot call cudaMalloc when they need it (the device is
+ * owned by another allocator, a latency budget forbids the driver's allocation lock, ...).
+ * No handle, no cudaMalloc / cudaFree: the partial sums live in a fixed 8 MiB array inside the
+ * library image, so experts * dim <= 131072 (larger sizes are refused with a message).
+ * dlogits (tokens, experts) fp32, X (tokens, dim) bf16, dWrouter (experts, dim) fp32: device
+ * pointers; runs on `stream` of the current device. All calls on a GPU share the array: calls
+ * that overlap on the GPU race, order them. The first call on a device looks up the array's
+ * address; make it outside any stream capture. */
+int tmt_moe_router_dw_noalloc(const float* dlogits, const void* X, int tokens, int dim, int experts,
+                              float* dWrouter, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
