@@ -187,6 +187,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: rows move by peer loads/stores inside the gather/scatter kernels, or by NCCL send/recv")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.tokens:
@@ -223,6 +225,8 @@ def main():
         print(json.dumps(line), flush=True)
         return
 
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+        os.environ.pop("NCCL_DEBUG")               # keep NCCL's version banner out of the one-line output
     import torch
     import tmt_moe_b200 as M
     torch.cuda.set_device(local_rank)
@@ -236,7 +240,8 @@ def main():
     stream = torch.cuda.current_stream().cuda_stream
     moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32 if cfg["router_f32"] else M.BF16,
                 training=cfg["backward"], device=local_rank, host_io=(world == 1 and not args.no_e2e),
-                stream=stream, ep_world=world, ep_rank=rank)
+                stream=stream, ep_world=world, ep_rank=rank,
+                ep_transport=M.EP_PEER if args.ep_transport == "peer" else M.EP_NCCL)
     if cfg.get("zipf"):
         import synth
         moe.set_router_bias(synth.zipf_bias(E, 2.0))
@@ -353,7 +358,8 @@ def main():
             hbm[n] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
                       "bytes_per_launch": nb}
     line = dict(base, value=value, ms_per_step=ms,
-                config={"workload": workload, "tokens_per_gpu": T, "parallelism": "ep%d" % world if world > 1 else "single",
+                config={"workload": workload, "tokens_per_gpu": T,
+                        "parallelism": ("ep%d/%s" % (world, args.ep_transport)) if world > 1 else "single",
                         "l2": "L2 flushed between steps" if flush else "working set larger than L2 (no flush needed)"},
                 clocks=clocks, gpu_launches=launches, roofline=roofline, hbm_kernels=hbm,
                 phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})

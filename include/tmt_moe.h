@@ -31,6 +31,7 @@ typedef struct tmt_moe tmt_moe;
 
 enum { TMT_MOE_BF16 = 0, TMT_MOE_F32 = 1 };
 enum { TMT_MOE_GEMM_TCGEN05 = 0, TMT_MOE_GEMM_SIMT = 1 };
+enum { TMT_MOE_EP_PEER = 0, TMT_MOE_EP_NCCL = 1 };
 
 /* Replaces the (N,E,K,D) arguments of moe_keep_alloc / moe_ws_alloc (moe.cu:330-362) and
  * the config knobs experts=, topk= (tmt-cuda/src/config.h:12). */
@@ -50,6 +51,8 @@ typedef struct tmt_moe_desc {
     int ep_rank;       /* this rank; it owns experts [rank*E/world, (rank+1)*E/world)        */
     float ep_capacity_factor; /* expert-parallel only: rows other ranks may route to this rank's
                           experts, as a multiple of tokens*topk (0 = 1.5); a step that needs more fails */
+    int ep_transport;  /* TMT_MOE_EP_PEER: gather / scatter kernels address the owners' buffers over NVLink
+                          (CUDA IPC peer memory); TMT_MOE_EP_NCCL: NCCL send / recv exchanges                 */
 } tmt_moe_desc;
 
 /* moe_keep_alloc + moe_ws_alloc (moe.cu:330-362): every buffer is allocated here, none later. */

@@ -3,12 +3,19 @@
 // grouped rows travel to the owning rank, run through the grouped GEMMs there and travel back.
 // The reference has no counterpart (single GPU, no communication library).
 //
-// One step: forward = dispatch exchange + combine exchange, backward = the two mirrors.
-// An exchange is ONE NCCL group of point-to-point sends and receives, one message per
-// (peer, expert) pair, so that rows land directly in their expert group on the owner (no
-// re-permutation pass) and come back directly into the token-side slots. Message sizes come
-// from an all-gather of the per-expert counts, read on the host once per step (NCCL's
-// send/recv sizes are host arguments). All kernels read local memory only.
+// Two transports (desc.ep_transport):
+//   TMT_MOE_EP_PEER (default): the four permutation kernels address the owner's buffers directly
+//     over NVLink (peer memory mapped with CUDA IPC): dispatch and the gradient dispatch STORE rows
+//     into the owner's grouped buffer, combine and scatter LOAD rows from it. No send buffer, no
+//     separate exchange pass: the all-to-all is fused into the gather / scatter kernels. Ranks
+//     meet at stream-ordered NCCL barriers (a one-word all-reduce) between writer and reader
+//     kernels. Only plain loads and stores touch peer memory; TMA reads local memory only.
+//   TMT_MOE_EP_NCCL: dispatch into a local send buffer, then ONE NCCL group of point-to-point
+//     sends and receives per exchange, one message per (peer, expert) pair, so that rows land
+//     directly in their expert group on the owner and come back directly into the token-side
+//     slots (no re-permutation pass).
+// Both size everything from an all-gather of the per-expert counts, read on the host once per
+// step (it doubles as the barrier that separates two steps).
 //
 // NCCL is bound at run time (dlopen of the process's libnccl.so.2): the library has no link
 // dependency on it, and a host program that never uses expert parallelism does not need it.
@@ -47,6 +54,14 @@ struct tmt_ep_state {
     int* cnt_all_dev = nullptr;       // [G][E]
     std::vector<int> cnt_all, tok_poff, x_counts, x_poff, src_off;
     float* stat_global = nullptr;     // E+1
+    // peer transport: owners' buffers as seen from this process, [G] pointers each, on the device
+    bool peer = false;
+    uint16_t** peer_Xg = nullptr; uint16_t** peer_Yg = nullptr; uint16_t** peer_dYg = nullptr; uint16_t** peer_dXg = nullptr;
+    std::vector<void*> opened;        // cudaIpcOpenMemHandle results to close
+    int* dest_row0 = nullptr;         // [E] this rank's first row inside the owner's group of expert e
+    std::vector<int> dest_row0_host;
+    uint16_t* Xc = nullptr;           // [T_pad][D] X in token order (router weight gradient)
+    int* bar_word = nullptr;
 };
 
 namespace tmt {
@@ -166,11 +181,47 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         NC(ep.get(), ep->CommInitRank(&ep->comm, ep->G, id, ep->r));
         const int E = h->d.experts, D = h->d.dim;
         const size_t cap = h->dims.cap;
-        ep->Xs = ep_alloc<uint16_t>(h, cap * D);
+        ep->peer = h->d.ep_transport == TMT_MOE_EP_PEER;
         ep->Yr = ep_alloc<uint16_t>(h, cap * D);
-        if (h->d.training) {
-            ep->dYs = ep_alloc<uint16_t>(h, cap * D);
-            ep->dXr = ep_alloc<uint16_t>(h, cap * D);
+        ep->bar_word = ep_alloc<int>(h, 1);
+        CKE(cudaMemsetAsync(ep->bar_word, 0, sizeof(int), h->stream));
+        if (ep->peer) {
+            const size_t tpad = (size_t)(h->d.tokens + kPad - 1) / kPad * kPad;
+            ep->Xc = ep_alloc<uint16_t>(h, tpad * D);
+            CKE(cudaMemsetAsync(ep->Xc, 0, tpad * D * 2, h->stream));
+            ep->dest_row0 = ep_alloc<int>(h, E);
+            ep->dest_row0_host.assign(E, 0);
+            // exchange CUDA IPC handles of the four buffers peers write to or read from
+            const int nbuf = h->d.training ? 4 : 2;
+            void* mine[4] = {h->Xg, h->Yg, h->dYg, h->dXg};
+            std::vector<cudaIpcMemHandle_t> local(4), all((size_t)4 * ep->G);
+            for (int i = 0; i < nbuf; ++i) CKE(cudaIpcGetMemHandle(&local[i], mine[i]));
+            unsigned char* dev_handles = ep_alloc<unsigned char>(h, sizeof(cudaIpcMemHandle_t) * 4 * (ep->G + 1));
+            CKE(cudaMemcpyAsync(dev_handles, local.data(), sizeof(cudaIpcMemHandle_t) * 4, cudaMemcpyHostToDevice, h->stream));
+            NC(ep.get(), ep->AllGather(dev_handles, dev_handles + sizeof(cudaIpcMemHandle_t) * 4, sizeof(cudaIpcMemHandle_t) * 4,
+                                       ncclUint8, ep->comm, h->stream));
+            CKE(cudaMemcpyAsync(all.data(), dev_handles + sizeof(cudaIpcMemHandle_t) * 4, sizeof(cudaIpcMemHandle_t) * 4 * ep->G,
+                                cudaMemcpyDeviceToHost, h->stream));
+            CKE(cudaStreamSynchronize(h->stream));
+            std::vector<uint16_t*> tab((size_t)4 * ep->G, nullptr);
+            for (int g = 0; g < ep->G; ++g)
+                for (int i = 0; i < nbuf; ++i) {
+                    if (g == ep->r) { tab[(size_t)i * ep->G + g] = static_cast<uint16_t*>(mine[i]); continue; }
+                    void* p = nullptr;
+                    CKE(cudaIpcOpenMemHandle(&p, all[(size_t)g * 4 + i], cudaIpcMemLazyEnablePeerAccess));
+                    ep->opened.push_back(p);
+                    tab[(size_t)i * ep->G + g] = static_cast<uint16_t*>(p);
+                }
+            uint16_t** dev_tab = ep_alloc<uint16_t*>(h, tab.size());
+            CKE(cudaMemcpyAsync(dev_tab, tab.data(), tab.size() * sizeof(uint16_t*), cudaMemcpyHostToDevice, h->stream));
+            CKE(cudaStreamSynchronize(h->stream));
+            ep->peer_Xg = dev_tab; ep->peer_Yg = dev_tab + ep->G; ep->peer_dYg = dev_tab + 2 * ep->G; ep->peer_dXg = dev_tab + 3 * ep->G;
+        } else {
+            ep->Xs = ep_alloc<uint16_t>(h, cap * D);
+            if (h->d.training) {
+                ep->dYs = ep_alloc<uint16_t>(h, cap * D);
+                ep->dXr = ep_alloc<uint16_t>(h, cap * D);
+            }
         }
         ep->x_cap = h->x_cap;
         ep->x_max_tiles = ep->x_cap / kPad;
@@ -185,7 +236,7 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         ep->stat_global = ep_alloc<float>(h, E + 1);
         h->ep_world_counts = ep_alloc<int>(h, E);
         h->ep = ep.release();
-        build_ep_maps(h, h->ep->Xs);
+        build_ep_maps(h, h->ep->peer ? h->ep->Xc : h->ep->Xs, h->ep->peer);
         return 0;
     } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
 }
@@ -196,6 +247,7 @@ namespace tmt {
 
 void ep_teardown(tmt_moe* h) {
     if (!h->ep) return;
+    for (void* p : h->ep->opened) cudaIpcCloseMemHandle(p);
     if (h->ep->comm && h->ep->CommDestroy) h->ep->CommDestroy(h->ep->comm);
     delete h->ep;
     h->ep = nullptr;
@@ -224,6 +276,18 @@ void plan_step(tmt_moe* h) {
     for (int le = 0; le < EL; ++le)
         for (int i = ep->x_poff[le] / kPad; i < ep->x_poff[le + 1] / kPad; ++i) te[i] = le;
     CKE(cudaMemcpyAsync(ep->x_tables, t, ep->x_tables_host.size() * sizeof(int), cudaMemcpyHostToDevice, h->stream));
+    if (ep->peer) {
+        // where this rank's rows start inside the owner's group: the owner's plan, computed here as well
+        std::vector<int> o_tok(E + 1), o_cnt(EL), o_poff(EL + 1), o_src((size_t)G * EL);
+        for (int g = 0; g < G; ++g) {
+            const long long orow = tmt_moe_ep_plan(G, g, E, kPad, ep->cnt_all.data(), o_tok.data(), o_cnt.data(), o_poff.data(), o_src.data());
+            if (orow < 0 || orow > ep->x_cap)
+                throw std::runtime_error("expert-side capacity exceeded on rank " + std::to_string(g) + ": " + std::to_string(orow) +
+                                         " rows, room for " + std::to_string(ep->x_cap) + " (raise desc.ep_capacity_factor)");
+            for (int le = 0; le < EL; ++le) ep->dest_row0_host[g * EL + le] = o_poff[le] + o_src[(size_t)ep->r * EL + le];
+        }
+        CKE(cudaMemcpyAsync(ep->dest_row0, ep->dest_row0_host.data(), E * sizeof(int), cudaMemcpyHostToDevice, h->stream));
+    }
     std::vector<int> world(E, 0);
     for (int g = 0; g < G; ++g)
         for (int e = 0; e < E; ++e) world[e] += ep->cnt_all[(size_t)g * E + e];
@@ -265,6 +329,19 @@ void exchange(tmt_moe* h, bool to_experts, const uint16_t* src, uint16_t* dst, i
     h->launches += 1;
 }
 
+// Stream-ordered meeting point of all ranks: when it completes here, every rank's stream has reached it.
+void rank_barrier(tmt_moe* h) {
+    tmt_ep_state* ep = h->ep;
+    NC(ep, ep->AllReduce(ep->bar_word, ep->bar_word, 1, ncclInt32, ncclSum, ep->comm, h->stream));
+    h->launches += 1;
+}
+
+PeerMap peer_map(tmt_moe* h, uint16_t** table) {
+    PeerMap pm;
+    pm.base = table; pm.dest_row0 = h->ep->dest_row0; pm.experts_per_rank = h->ep->EL;
+    return pm;
+}
+
 void use_expert_layout(tmt_moe* h) {
     tmt_ep_state* ep = h->ep;
     h->g_poff = ep->x_tables;
@@ -286,15 +363,34 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
     h->dims.T = tokens;
     h->last_tokens = tokens;
     const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
-    route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
-    plan_step(h);
-    zero_pads(h, h->Xg, D);
-    exchange(h, true, ep->Xs, h->Xg, D);
-    expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
-    exchange(h, false, h->Yg, ep->Yr, D);
-    prof_mark(h, kPhCombine);
-    CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
-    h->launches += 1;
+    if (ep->peer) {
+        route_only(h, static_cast<const uint16_t*>(X), Wr);
+        plan_step(h);                       // all-gather of counts: also separates this step from the previous one
+        zero_pads(h, h->Xg, D);
+        prof_mark(h, kPhDispatch);
+        CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, h->stream, peer_map(h, ep->peer_Xg),
+                            h->d.training ? ep->Xc : nullptr));
+        h->launches += 1;
+        prof_mark(h, kPhExchange);
+        rank_barrier(h);                    // every rank's rows have landed
+        expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
+        prof_mark(h, kPhExchange);
+        rank_barrier(h);                    // every rank's expert outputs are complete
+        prof_mark(h, kPhCombine);
+        CKE(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream,
+                           peer_map(h, ep->peer_Yg), h->d.training ? ep->Yr : nullptr));
+        h->launches += 1;
+    } else {
+        route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
+        plan_step(h);
+        zero_pads(h, h->Xg, D);
+        exchange(h, true, ep->Xs, h->Xg, D);
+        expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
+        exchange(h, false, h->Yg, ep->Yr, D);
+        prof_mark(h, kPhCombine);
+        CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
+        h->launches += 1;
+    }
     // statistics over all ranks' tokens: sum of probabilities and of lse^2 / T
     NC(ep, ep->AllReduce(h->rb.stat, ep->stat_global, E + 1, ncclFloat32, ncclSum, ep->comm, h->stream));
     prof_mark(h, -1);
@@ -311,16 +407,31 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
     use_expert_layout(h);
     const int D = h->d.dim, E = h->d.experts;
     prof_mark(h, kPhGradDispatch);
-    // token side: dYs[slot] = w * dY[token]; s_j = <dY[token], Yr[slot]> (the expert output came back unscaled)
-    CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
-    h->launches += 1;
-    zero_pads(h, h->dYg, D);
-    exchange(h, true, ep->dYs, h->dYg, D);
-    expert_backward(h, Wup, Wdown, dWup, dWdown);
-    exchange(h, false, h->dXg, ep->dXr, D);
-    // the router weight gradient of the local tokens, then summed over the ranks (the router is replicated)
-    router_backward(h, Wr, nullptr, ep->Xs, true, ep->dXr, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
-                    (long)h->d.tokens * ep->G);
+    // token side: w * dY[token] goes to the owner's gradient rows; s_j = <dY[token], Yr[slot]> (the expert output
+    // came back unscaled and was kept)
+    if (ep->peer) {
+        zero_pads(h, h->dYg, D);             // own pad rows; peers store into data rows only
+        CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, h->dYg, h->s_j, /*mode=*/2, h->stream,
+                                 peer_map(h, ep->peer_dYg)));
+        h->launches += 1;
+        prof_mark(h, kPhExchange);
+        rank_barrier(h);
+        expert_backward(h, Wup, Wdown, dWup, dWdown);
+        prof_mark(h, kPhExchange);
+        rank_barrier(h);
+        router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+                        (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg));
+    } else {
+        CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
+        h->launches += 1;
+        zero_pads(h, h->dYg, D);
+        exchange(h, true, ep->dYs, h->dYg, D);
+        expert_backward(h, Wup, Wdown, dWup, dWdown);
+        exchange(h, false, h->dXg, ep->dXr, D);
+        // the router weight gradient of the local tokens, then summed over the ranks (the router is replicated)
+        router_backward(h, Wr, nullptr, ep->Xs, true, ep->dXr, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+                        (long)h->d.tokens * ep->G);
+    }
     NC(ep, ep->AllReduce(dWr, dWr, (size_t)E * D, ncclFloat32, ncclSum, ep->comm, h->stream));
     prof_mark(h, -1);
     h->launches += 1;

@@ -36,22 +36,35 @@ struct RouteDims {
     int router_f32;
 };
 
+// Expert-parallel addressing: a grouped row of expert e lives in the buffer of the rank that owns e.
+// base[g] is that rank's buffer (peer memory mapped into this process, base[own rank] the local one);
+// this rank's rows for expert e start at row dest_row0[e] there and keep their token-side order.
+// base == nullptr: plain local addressing by token-side slot.
+struct PeerMap {
+    uint16_t* const* base = nullptr;
+    const int* dest_row0 = nullptr;
+    int experts_per_rank = 1;
+};
+
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
                           const float* bias, cudaStream_t s);
 // splits: number of reduction ranges written to split_poff (1..kMaxSplits).
 cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s);
 // Xg[slot] = X[token]; pad rows zeroed; fills slot_of / slotw / tok_of_slot (moe.cu:103-140).
-cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s);
+// x_copy (may be NULL): also keeps X in token order (the expert-parallel path reads it in backward).
+cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s,
+                            PeerMap pm = PeerMap(), uint16_t* x_copy = nullptr);
 // mode 0: Y = beta*Y + sum_j Yg[slot_j]               (two-matrix experts, gate applied by the GEMM)
 // mode 1: Y = beta*Y + sum_j w_j * silu(Yg[slot_j])   (reference mode, moe.cu:144-158)
 // mode 2: Y = beta*Y + sum_j w_j * Yg[slot_j]         (expert parallel: rows come back unscaled)
+// y_keep (may be NULL): stores every fetched row at its token-side slot (kept for the backward pass).
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
-                           int mode, cudaStream_t s);
+                           int mode, cudaStream_t s, PeerMap pm = PeerMap(), uint16_t* y_keep = nullptr);
 // mode 0: dYg[slot] = bf16(w * dY[token]), pad rows zero                         (two-matrix experts)
 // mode 1: dYg[slot] = silu_bwd(Yg[slot], w * dY[token]); s_j = <dY, silu(Yg[slot])>  (reference, moe.cu:162-197)
 // mode 2: as mode 0 and s_j = <dY, Yg[slot]>                                     (expert parallel)
 cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
-                                 uint16_t* dYg, float* s_j, int mode, cudaStream_t s);
+                                 uint16_t* dYg, float* s_j, int mode, cudaStream_t s, PeerMap pm = PeerMap());
 // moe.cu:200-234. sw_part (may be NULL): per-row partial sums of w * dL/dw from the dH GEMM.
 // counts / n_norm: per-expert counts and token count the aux and z terms are normalised by
 // (the local ones on one GPU, the totals over all ranks under expert parallelism).
@@ -67,7 +80,7 @@ cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float
 // dX[t] = sum_e bf16(dlogits[t, e]) * Wr[e] + sum_j dXg[slot_j]   (moe.cu:525-529, 238-249)
 // With dXr != NULL the router term was already computed by the tensor-core product: dX[t] = dXr[t] + sum_j ...
 cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
-                           const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s);
+                           const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s, PeerMap pm = PeerMap());
 // out[i] = bf16(in[i])
 cudaError_t launch_to_bf16(const float* in, uint16_t* out, long n, cudaStream_t s);
 // dWr[e][d] = sum over `parts` partial products part[p][e][d] (row pitch of a part: mw rows x D)

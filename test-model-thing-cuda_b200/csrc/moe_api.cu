@@ -87,7 +87,7 @@ T* dalloc(tmt_moe* h, size_t n) {
     return reinterpret_cast<T*>(p);
 }
 
-enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kDlgMN, kDltK, kXsMN, kNumActMaps };
+enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kDlgMN, kDltK, kXsMN, kDltMN, kNumActMaps };
 enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };   // one more map follows the 4*E weight maps: the router, mn-major
 
 void build_act_maps(tmt_moe* h) {
@@ -248,6 +248,13 @@ void prof_mark(tmt_moe* h, int phase) {
 
 // Router, offset tables and the row copies into `grouped` (token-side grouped layout).
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped) {
+    route_only(h, X, Wr);
+    prof_mark(h, kPhDispatch);
+    CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream));
+    h->launches += 1;
+}
+
+void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
     prof_mark(h, kPhRouter);
     CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream));
     prof_mark(h, kPhScan);
@@ -257,9 +264,7 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
         CK(cudaMemcpyAsync(h->plain_num, &plain, sizeof(int), cudaMemcpyHostToDevice, h->stream));
         h->plain_num_host = plain;
     }
-    prof_mark(h, kPhDispatch);
-    CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream));
-    h->launches += 3;
+    h->launches += 2;
 }
 
 // Grouped expert products over the rows in h->Xg: Yg = expert(Xg). With gate_in_epilogue the
@@ -350,36 +355,54 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
     prof_mark(h, -1);
 }
 
-void build_ep_maps(tmt_moe* h, const uint16_t* Xs) {
-    if (h->d.gemm_impl != TMT_MOE_GEMM_TCGEN05) return;
-    CUtensorMap m;
-    memset(&m, 0, sizeof m);
-    make_map(&m, Xs, h->d.dim, h->dims.cap, 64, 64);
-    CK(cudaMemcpyAsync(h->act_maps + kXsMN, &m, sizeof m, cudaMemcpyHostToDevice, h->stream));
+// Expert parallel: the router weight-gradient product reads X either from the token-side grouped send
+// buffer (NCCL transport) or, with peer addressing, from a token-order copy. In token order the
+// reduction runs over the tokens themselves: dl_t serves as the mn-major A operand (columns past its
+// width read as zero) and the split table is fixed.
+void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order) {
+    h->ep_x_token_order = token_order;
+    if (h->d.gemm_impl != TMT_MOE_GEMM_TCGEN05 || !h->dl_t) return;
+    const uint64_t tpad = (uint64_t)(h->d.tokens + kPad - 1) / kPad * kPad;
+    CUtensorMap m[2];
+    memset(m, 0, sizeof m);
+    make_map(&m[0], x_rows, h->d.dim, token_order ? tpad : (uint64_t)h->dims.cap, 64, 64);
+    CK(cudaMemcpyAsync(h->act_maps + kXsMN, &m[0], sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+    if (token_order) {
+        make_map(&m[1], h->dl_t, h->kw, tpad, 64, 64);
+        CK(cudaMemcpyAsync(h->act_maps + kDltMN, &m[1], sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+        std::vector<int> sp(kMaxSplits + 1, 0);
+        const long tiles = (long)tpad / kPad;
+        for (int i = 0; i <= h->splits; ++i) sp[i] = (int)(tiles * i / h->splits) * kPad;
+        h->tok_split_poff = dalloc<int>(h, kMaxSplits + 1);
+        CK(cudaMemcpyAsync(h->tok_split_poff, sp.data(), sp.size() * sizeof(int), cudaMemcpyHostToDevice, h->stream));
+    }
     CK(cudaStreamSynchronize(h->stream));
 }
 
 void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uint16_t* grouped_x, bool x_is_ep,
-                     const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm) {
+                     const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm,
+                     PeerMap pm) {
+    const bool tok_order = x_is_ep && h->ep_x_token_order;
     const int D = h->d.dim, E = h->d.experts;
     if (E == 1) {      // dense shortcut: no router gradient (moe.cu:488-494)
         CK(cudaMemsetAsync(dWr, 0, (size_t)E * D * sizeof(float), h->stream));
         prof_mark(h, kPhScatter);
-        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, nullptr, dX, h->stream));
+        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, nullptr, dX, h->stream, pm));
         h->launches += 1;
         return;
     }
     const bool tc = h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05;
     prof_mark(h, kPhRouterBwd);
-    if (tc) CK(cudaMemsetAsync(h->dl_g, 0, (size_t)h->dims.cap * h->mw * 2, h->stream));
+    if (tc && !tok_order) CK(cudaMemsetAsync(h->dl_g, 0, (size_t)h->dims.cap * h->mw * 2, h->stream));
     CK(launch_router_bwd(h->dims, h->rb, sw_part, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, counts, n_norm,
-                         tc ? h->dl_t : nullptr, h->kw, tc ? h->dl_g : nullptr, h->mw, h->stream));
+                         tc ? h->dl_t : nullptr, h->kw, tc && !tok_order ? h->dl_g : nullptr, h->mw, h->stream));
     h->launches += 1;
     if (!tc) {
         prof_mark(h, kPhRouterDw);
+        if (tok_order) throw std::runtime_error("the SIMT cross-check path does not support the peer transport");
         CK(launch_router_dw(h->dims, h->rb, h->dlogits, grouped_x, h->dwr_partial, kRouterDwChunks, dWr, h->stream));
         prof_mark(h, kPhScatter);
-        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, nullptr, dX, h->stream));
+        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, nullptr, dX, h->stream, pm));
         h->launches += 3;
         return;
     }
@@ -401,12 +424,12 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
     {   // dWr = dl_g^T * X_grouped, reduction split into h->splits row ranges, then summed
         GemmParams p = base_params(h);
         p.mode = kRedRagged;
-        p.mapA = h->act_maps + kDlgMN; p.a_stride = 0;
+        p.mapA = h->act_maps + (tok_order ? kDltMN : kDlgMN); p.a_stride = 0;
         p.mapB = h->act_maps + (x_is_ep ? kXsMN : kXgMN); p.b_stride = 0;
         p.a_mn = 1; p.b_mn = 1;
         p.a_boxes = kBM / 64; p.b_boxes = kBN / 64;
         p.tx_bytes = (p.a_boxes + p.b_boxes) * 8192;
-        p.M = h->mw; p.N = D; p.experts = h->splits; p.poff = h->rb.split_poff;
+        p.M = h->mw; p.N = D; p.experts = h->splits; p.poff = tok_order ? h->tok_split_poff : h->rb.split_poff;
         p.epi = kEpiF32; p.outF = h->dwr_part_ptrs; p.ldc = D;
         CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
         CK(launch_reduce_parts(h->dwr_partial, h->splits, h->mw, E, D, dWr, h->stream));
@@ -425,7 +448,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.tile_expert = h->plain_tiles; p.num_m_tiles = h->plain_num;
         p.epi = kEpiBf16; p.out0 = h->dXr; p.ldc = D;
         CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
-        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream));
+        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream, pm));
         h->launches += 2;
     }
 }

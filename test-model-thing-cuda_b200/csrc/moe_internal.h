@@ -58,6 +58,8 @@ struct tmt_moe {
     float** dwr_part_ptrs = nullptr;
     int* plain_tiles = nullptr; int* plain_num = nullptr; int plain_num_host = -1;
     const void* wr_seen = nullptr;
+    bool ep_x_token_order = false;     // expert parallel, peer transport: the router dW product reads X in token order
+    int* tok_split_poff = nullptr;
     CUtensorMap* act_maps = nullptr;
     CUtensorMap* w_maps = nullptr;
     const uint16_t** up_ptrs = nullptr; const uint16_t** down_ptrs = nullptr;
@@ -93,13 +95,16 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
                  float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef);
 void ep_teardown(tmt_moe* h);
 const float* ep_stat(tmt_moe* h);
+void route_only(tmt_moe* h, const uint16_t* X, const void* Wr);
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped);
 void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue);
 void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown);
 // Router backward after the expert products: dlogits, dWr (local contribution) and dX.
 // grouped_x / x_is_ep: the token-side grouped copy of X (Xg, or the send buffer under expert parallelism).
+// pm: where the rows of dXg live (expert parallel with peer addressing); x_tokens: grouped_x is X in token order.
 void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uint16_t* grouped_x, bool x_is_ep,
-                     const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm);
-void build_ep_maps(tmt_moe* h, const uint16_t* Xs);
+                     const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm,
+                     PeerMap pm = PeerMap());
+void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order);
 void prof_mark(tmt_moe* h, int phase);
 }  // namespace tmt

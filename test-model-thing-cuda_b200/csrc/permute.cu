@@ -20,12 +20,22 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return make_uint4(pack_bf2(f[0], f[1]), pack_bf2(f[2], f[3]), pack_bf2(f[4], f[5]), pack_bf2(f[6], f[7]));
 }
 
+// Address of grouped row `slot` (token-side numbering) of expert e: local, or in the owner's buffer.
+__device__ __forceinline__ uint16_t* group_row(const PeerMap& pm, const uint16_t* local, const int* poff, int e, int slot, int D) {
+    if (pm.base == nullptr) return const_cast<uint16_t*>(local) + (long)slot * D;
+    return pm.base[e / pm.experts_per_rank] + (long)(pm.dest_row0[e] + slot - poff[e]) * D;
+}
+__device__ __forceinline__ uint16_t* shfl_ptr(uint16_t* p, int lane) {
+    return reinterpret_cast<uint16_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(p), lane));
+}
+
 // Blocks [0, tok_blocks) handle tokens; blocks [tok_blocks, tok_blocks + E) zero the pad rows
 // of expert (blockIdx - tok_blocks). The offset table (padded group starts and this router
 // block's per-expert base) is staged in shared memory.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) dispatch_kernel(const RouteDims d, const RouteBufs b,
                                                                         const uint16_t* __restrict__ X,
-                                                                        uint16_t* __restrict__ Xg, int tok_blocks) {
+                                                                        uint16_t* __restrict__ Xg, int tok_blocks,
+                                                                        const PeerMap pm, uint16_t* __restrict__ x_copy) {
     extern __shared__ int table[];     // [E] poff + block_base of the router block these 8 tokens belong to
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = d.D >> 3;
@@ -46,48 +56,53 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dispatch_kernel(const Rou
     __syncthreads();
     const long t = t0 + warp;
     if (t >= d.T) return;
-    int slot = -1;
+    uint16_t* row = nullptr;
     if (lane < d.K) {
         const int e = b.idx[t * d.K + lane];
         if (e < 0 || e >= d.E) report(b.status, kErrSlotRange);
         else {
-            slot = table[e] + b.rank[t * d.K + lane];
-            if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+            const int slot = table[e] + b.rank[t * d.K + lane];
+            if (slot < 0 || slot >= d.cap) report(b.status, kErrSlotRange);
             else {
                 b.slot_of[t * d.K + lane] = slot;
                 b.slotw[slot] = b.w[t * d.K + lane];
                 b.tok_of_slot[slot] = (int)t;
+                row = group_row(pm, Xg, b.poff, e, slot, d.D);
             }
         }
     }
-    int slots[kMaxK];
+    uint16_t* rows[kMaxK];
 #pragma unroll
-    for (int j = 0; j < kMaxK; ++j) slots[j] = __shfl_sync(0xffffffffu, slot, j);
+    for (int j = 0; j < kMaxK; ++j) rows[j] = shfl_ptr(row, j);
     const uint16_t* src = X + t * d.D;
     for (int v = lane; v < nvec; v += 32) {
         const uint4 x = ldg16(src + v * 8);
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j)
-            if (j < d.K && slots[j] >= 0) stg16(Xg + (long)slots[j] * d.D + v * 8, x);
+            if (j < d.K && rows[j] != nullptr) stg16(rows[j] + v * 8, x);
+        if (x_copy) stg16(x_copy + t * d.D + v * 8, x);
     }
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const RouteDims d, const RouteBufs b,
                                                                        const uint16_t* __restrict__ Yg,
                                                                        uint16_t* __restrict__ Y, float beta,
-                                                                       int mode) {
+                                                                       int mode, const PeerMap pm,
+                                                                       uint16_t* __restrict__ y_keep) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
     if (t >= d.T) return;
-    int slot = -1; float wj = 0.0f;
+    int slot = -1; float wj = 0.0f; uint16_t* row = nullptr;
     if (lane < d.K) {
         slot = b.slot_of[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
-        else wj = b.slotw[slot];
+        else { wj = b.slotw[slot]; row = group_row(pm, Yg, b.poff, b.idx[t * d.K + lane], slot, d.D); }
     }
-    int slots[kMaxK]; float ws[kMaxK];
+    int slots[kMaxK]; float ws[kMaxK]; const uint16_t* rows[kMaxK];
 #pragma unroll
-    for (int j = 0; j < kMaxK; ++j) { slots[j] = __shfl_sync(0xffffffffu, slot, j); ws[j] = __shfl_sync(0xffffffffu, wj, j); }
+    for (int j = 0; j < kMaxK; ++j) {
+        slots[j] = __shfl_sync(0xffffffffu, slot, j); ws[j] = __shfl_sync(0xffffffffu, wj, j); rows[j] = shfl_ptr(row, j);
+    }
     const int nvec = d.D >> 3;
     uint16_t* dst = Y + t * d.D;
     for (int v = lane; v < nvec; v += 32) {
@@ -104,7 +119,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
         for (int j = 0; j < kMaxK; ++j) {
             if (j < d.K && slots[j] >= 0) {
                 float y[8];
-                unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), y);
+                const uint4 raw = ldg16(rows[j] + v * 8);
+                if (y_keep) stg16(y_keep + (long)slots[j] * d.D + v * 8, raw);
+                unpack8(raw, y);
                 if (mode == 1) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[i] += ws[j] * silu_f(y[i]);
@@ -126,7 +143,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
                                                                              const uint16_t* __restrict__ Yg,
                                                                              uint16_t* __restrict__ dYg,
                                                                              float* __restrict__ s_j, int mode,
-                                                                             int tok_blocks) {
+                                                                             int tok_blocks, const PeerMap pm) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = d.D >> 3;
     if ((int)blockIdx.x >= tok_blocks) {
@@ -138,16 +155,17 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
     }
     const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
     if (t >= d.T) return;
-    int slot = -1; float wj = 0.0f;
+    int slot = -1; float wj = 0.0f; uint16_t* row = nullptr;
     if (lane < d.K) {
         slot = b.slot_of[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
-        else wj = b.slotw[slot];
+        else { wj = b.slotw[slot]; row = group_row(pm, dYg, b.poff, b.idx[t * d.K + lane], slot, d.D); }
     }
-    int slots[kMaxK]; float ws[kMaxK]; float sdot[kMaxK];
+    int slots[kMaxK]; float ws[kMaxK]; float sdot[kMaxK]; uint16_t* rows[kMaxK];
 #pragma unroll
     for (int j = 0; j < kMaxK; ++j) {
         slots[j] = __shfl_sync(0xffffffffu, slot, j); ws[j] = __shfl_sync(0xffffffffu, wj, j); sdot[j] = 0.0f;
+        rows[j] = shfl_ptr(row, j);
     }
     const uint16_t* src = dY + t * d.D;
     for (int v = lane; v < nvec; v += 32) {
@@ -176,7 +194,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[i] = ws[j] * g[i];
                 }
-                stg16(dYg + (long)slots[j] * d.D + v * 8, pack8(o));
+                stg16(rows[j] + v * 8, pack8(o));
             }
         }
     }
@@ -329,7 +347,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) scatter_kernel(const Rout
                                                                        const void* __restrict__ Wr,
                                                                        const uint16_t* __restrict__ dXg,
                                                                        const uint16_t* __restrict__ dXr,
-                                                                       uint16_t* __restrict__ dX) {
+                                                                       uint16_t* __restrict__ dX, const PeerMap pm) {
     extern __shared__ float dls[];     // [warps][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
@@ -338,14 +356,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) scatter_kernel(const Rout
     const bool router = d.E > 1 && dXr == nullptr;     // dense shortcut has no router gradient (moe.cu:488-494)
     if (router)
         for (int e = lane; e < d.E; e += 32) mine[e] = round_bf(dlogits[t * d.E + e]);
-    int slot = -1;
+    uint16_t* row = nullptr;
     if (lane < d.K) {
-        slot = b.slot_of[t * d.K + lane];
-        if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+        const int slot = b.slot_of[t * d.K + lane];
+        if (slot < 0 || slot >= d.cap) report(b.status, kErrSlotRange);
+        else row = group_row(pm, dXg, b.poff, b.idx[t * d.K + lane], slot, d.D);
     }
-    int slots[kMaxK];
+    const uint16_t* rows[kMaxK];
 #pragma unroll
-    for (int j = 0; j < kMaxK; ++j) slots[j] = __shfl_sync(0xffffffffu, slot, j);
+    for (int j = 0; j < kMaxK; ++j) rows[j] = shfl_ptr(row, j);
     __syncwarp();
     const int nvec = d.D >> 3;
     for (int v = lane; v < nvec; v += 32) {
@@ -370,9 +389,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) scatter_kernel(const Rout
         }
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
-            if (j < d.K && slots[j] >= 0) {
+            if (j < d.K && rows[j] != nullptr) {
                 float x[8];
-                unpack8(ldg16(dXg + (long)slots[j] * d.D + v * 8), x);
+                unpack8(ldg16(rows[j] + v * 8), x);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] += x[i];
             }
@@ -385,22 +404,24 @@ inline int tok_blocks_of(int T) { return (T + kWarpsPerBlock - 1) / kWarpsPerBlo
 
 }  // namespace
 
-cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s) {
+cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* X, uint16_t* Xg, cudaStream_t s,
+                            PeerMap pm, uint16_t* x_copy) {
     const int tb = tok_blocks_of(d.T);
-    dispatch_kernel<<<tb + d.E, kWarpsPerBlock * 32, d.E * sizeof(int), s>>>(d, b, X, Xg, tb);
+    // with peer addressing the pad rows belong to the owners, who zero their own
+    dispatch_kernel<<<tb + (pm.base ? 0 : d.E), kWarpsPerBlock * 32, d.E * sizeof(int), s>>>(d, b, X, Xg, tb, pm, x_copy);
     return cudaGetLastError();
 }
 
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
-                           int mode, cudaStream_t s) {
-    combine_kernel<<<tok_blocks_of(d.T), kWarpsPerBlock * 32, 0, s>>>(d, b, Yg, Y, beta, mode);
+                           int mode, cudaStream_t s, PeerMap pm, uint16_t* y_keep) {
+    combine_kernel<<<tok_blocks_of(d.T), kWarpsPerBlock * 32, 0, s>>>(d, b, Yg, Y, beta, mode, pm, y_keep);
     return cudaGetLastError();
 }
 
 cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
-                                 uint16_t* dYg, float* s_j, int mode, cudaStream_t s) {
+                                 uint16_t* dYg, float* s_j, int mode, cudaStream_t s, PeerMap pm) {
     const int tb = tok_blocks_of(d.T);
-    grad_dispatch_kernel<<<tb + d.E, kWarpsPerBlock * 32, 0, s>>>(d, b, dY, Yg, dYg, s_j, mode, tb);
+    grad_dispatch_kernel<<<tb + (pm.base ? 0 : d.E), kWarpsPerBlock * 32, 0, s>>>(d, b, dY, Yg, dYg, s_j, mode, tb, pm);
     return cudaGetLastError();
 }
 
@@ -438,10 +459,10 @@ cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float
 }
 
 cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
-                           const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s) {
+                           const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s, PeerMap pm) {
     const size_t smem = (size_t)kWarpsPerBlock * d.E * sizeof(float);
-    if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX);
-    else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX);
+    if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX, pm);
+    else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX, pm);
     return cudaGetLastError();
 }
 

@@ -49,7 +49,7 @@ inline void moe_keep_alloc(MoeKeep& k, int N, int E, int K, int D, int hidden = 
     d.training = 1; d.gemm_impl = TMT_MOE_GEMM_TCGEN05;
     int dev = 0;
     cudaGetDevice(&dev);
-    d.device = dev; d.host_io = 0; d.stream = stream; d.ep_world = 1; d.ep_rank = 0; d.ep_capacity_factor = 0;
+    d.device = dev; d.host_io = 0; d.stream = stream; d.ep_world = 1; d.ep_rank = 0; d.ep_capacity_factor = 0; d.ep_transport = 0;
     moe_check(tmt_moe_create(&d, &k.handle));
     k.N = N; k.E = E; k.K = K; k.D = D; k.hidden = hidden;
 }

@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libtmt_moe_b200.so")
 
 BF16, F32 = 0, 1
 GEMM_TCGEN05, GEMM_SIMT = 0, 1
+EP_PEER, EP_NCCL = 0, 1
 
 EXPORTS = (
     "tmt_moe_create", "tmt_moe_destroy", "tmt_moe_last_error", "tmt_moe_set_router_bias",
@@ -37,7 +38,7 @@ class Desc(ctypes.Structure):
                 ("experts", ctypes.c_int), ("topk", ctypes.c_int), ("router_dtype", ctypes.c_int),
                 ("training", ctypes.c_int), ("gemm_impl", ctypes.c_int), ("device", ctypes.c_int),
                 ("host_io", ctypes.c_int), ("stream", ctypes.c_void_p), ("ep_world", ctypes.c_int),
-                ("ep_rank", ctypes.c_int), ("ep_capacity_factor", ctypes.c_float)]
+                ("ep_rank", ctypes.c_int), ("ep_capacity_factor", ctypes.c_float), ("ep_transport", ctypes.c_int)]
 
 
 class Nvfp4Weight(ctypes.Structure):
@@ -100,10 +101,10 @@ class MoE:
 
     def __init__(self, tokens, dim, experts, topk, hidden=0, router_dtype=BF16, training=True,
                  gemm_impl=GEMM_TCGEN05, device=0, host_io=False, stream=None, ep_world=1, ep_rank=0,
-                 ep_capacity_factor=0.0):
+                 ep_capacity_factor=0.0, ep_transport=0):
         self.lib = load()
         self.desc = Desc(tokens, dim, hidden, experts, topk, router_dtype, int(training), gemm_impl, device,
-                         int(host_io), stream, ep_world, ep_rank, ep_capacity_factor)
+                         int(host_io), stream, ep_world, ep_rank, ep_capacity_factor, ep_transport)
         self.h = ctypes.c_void_p()
         _check(self.lib.tmt_moe_create(ctypes.byref(self.desc), ctypes.byref(self.h)), self.lib)
         self.tokens, self.dim, self.hidden, self.experts, self.topk = tokens, dim, hidden, experts, topk

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, transport):
     try:
         sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -37,7 +37,7 @@ def _worker(rank, world, port, q):
         mine = dict(base, X=data[rank]["X"], dY=data[rank]["dY"],
                     Wup=base["Wup"][rank * EL:(rank + 1) * EL], Wdown=base["Wdown"][rank * EL:(rank + 1) * EL])
         moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32, training=True, device=rank, ep_world=world, ep_rank=rank,
-                    ep_capacity_factor=2.0)
+                    ep_capacity_factor=2.0, ep_transport=transport)
         moe.ep_init_torch(dist)
         X, dY, Wr = G.dev(mine["X"]), G.dev(mine["dY"]), G.dev(mine["Wr"])
         Wup_all, Wdown_all = G.dev(mine["Wup"]), G.dev(mine["Wdown"])
@@ -77,12 +77,13 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_two_gpus():
+@pytest.mark.parametrize("transport", [pytest.param(0, id="peer"), pytest.param(1, id="nccl")])
+def test_expert_parallel_two_gpus(transport):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 200
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    port = 29700 + os.getpid() % 200 + 7 * transport
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport)) for r in range(world)]
     for p in procs:
         p.start()
     res = []
