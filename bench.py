@@ -187,6 +187,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gemm", default="2cta", choices=["2cta", "1cta"],
+                    help="grouped GEMM kernel: CTA pairs on 256x256 tiles (default) or one CTA per 128x256 tile")
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows move by peer loads/stores inside the gather/scatter kernels, or by NCCL send/recv")
     args = ap.parse_args()
@@ -240,6 +242,7 @@ def main():
     stream = torch.cuda.current_stream().cuda_stream
     moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32 if cfg["router_f32"] else M.BF16,
                 training=cfg["backward"], device=local_rank, host_io=(world == 1 and not args.no_e2e),
+                gemm_impl=M.GEMM_TCGEN05_2CTA if args.gemm == "2cta" else M.GEMM_TCGEN05,
                 stream=stream, ep_world=world, ep_rank=rank,
                 ep_transport=M.EP_PEER if args.ep_transport == "peer" else M.EP_NCCL)
     if cfg.get("zipf"):
@@ -345,7 +348,8 @@ def main():
     flops = (12.0 if cfg["backward"] else 4.0) * A * D * H          # all ranks' tokens processed by... this rank's share
     achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
-    roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (%d launches per step)" % gemm_launches,
+    roofline = {"bound": "tensor", "kernel": "%s (%d launches per step)" % (
+                    "gemm_tcgen05_2cta_kernel" if args.gemm == "2cta" else "gemm_tcgen05_kernel", gemm_launches),
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                 "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
                 "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}

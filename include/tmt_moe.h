@@ -30,7 +30,7 @@ extern "C" {
 typedef struct tmt_moe tmt_moe;
 
 enum { TMT_MOE_BF16 = 0, TMT_MOE_F32 = 1 };
-enum { TMT_MOE_GEMM_TCGEN05 = 0, TMT_MOE_GEMM_SIMT = 1 };
+enum { TMT_MOE_GEMM_TCGEN05 = 0, TMT_MOE_GEMM_SIMT = 1, TMT_MOE_GEMM_TCGEN05_2CTA = 2 };
 enum { TMT_MOE_EP_PEER = 0, TMT_MOE_EP_NCCL = 1 };
 
 /* Replaces the (N,E,K,D) arguments of moe_keep_alloc / moe_ws_alloc (moe.cu:330-362) and
@@ -43,7 +43,8 @@ typedef struct tmt_moe_desc {
     int topk;          /* 1 <= K <= min(E, 8)                                               */
     int router_dtype;  /* TMT_MOE_BF16 (the reference's work copy, model.cu:513) or _F32    */
     int training;      /* 1: keep what backward needs; 0: forward only                     */
-    int gemm_impl;     /* TMT_MOE_GEMM_TCGEN05 (product) or _SIMT (slow cross-check kernel) */
+    int gemm_impl;     /* TMT_MOE_GEMM_TCGEN05 (one CTA per tile), _TCGEN05_2CTA (CTA pairs on 256x256 tiles,
+                          groups padded to 256 rows) or _SIMT (slow cross-check kernel)            */
     int device;        /* CUDA device ordinal                                              */
     int host_io;       /* 1: also allocate staging for the *_host entry points             */
     void* stream;      /* cudaStream_t all work is queued on; NULL = legacy default stream  */

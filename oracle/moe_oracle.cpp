@@ -186,9 +186,10 @@ struct oracle_cfg {
     int tokens, dim, hidden, experts, topk;
     int router_f32;  // 1: router weights are fp32, 0: bf16
     int threads;
+    int pad;         // rows every expert group is padded to (0 = 128, the reference's padding)
 };
 
-int oracle_abi_version() { return 3; }
+int oracle_abi_version() { return 4; }
 
 // moe.cu:10-68 (+ optional per-expert logit bias, which the reference lacks).
 void oracle_router(const oracle_cfg* c, const uint16_t* X, const void* Wr, const float* bias,
@@ -268,7 +269,7 @@ void oracle_forward(const oracle_cfg* c, const uint16_t* X, const void* Wr, cons
     const int T = c->tokens, D = c->dim, H = c->hidden, E = c->experts, K = c->topk;
     const int th = c->threads;
     oracle_router(c, X, Wr, bias, logits, probs, idx, w, lse);
-    int rows = oracle_layout(T, E, K, 128, idx, counts, off, poff, slot_of);
+    int rows = oracle_layout(T, E, K, c->pad > 0 ? c->pad : 128, idx, counts, off, poff, slot_of);
     std::vector<float> slotw(rows, 0.0f);
     std::fill(Xg, Xg + (size_t)rows * D, (uint16_t)0);
     for (long t = 0; t < T; ++t)

@@ -24,7 +24,7 @@ def build(force=False):
 
 class _Cfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in
-                ("tokens", "dim", "hidden", "experts", "topk", "router_f32", "threads")]
+                ("tokens", "dim", "hidden", "experts", "topk", "router_f32", "threads", "pad")]
 
 
 def lib():
@@ -36,7 +36,7 @@ def lib():
         _lib.oracle_stats.restype = ctypes.c_float
         _lib.oracle_layout.restype = ctypes.c_int
         _lib.oracle_abi_version.restype = ctypes.c_int
-        assert _lib.oracle_abi_version() == 3, "stale oracle library: run make -C oracle -B"
+        assert _lib.oracle_abi_version() == 4, "stale oracle library: run make -C oracle -B"
     return _lib
 
 
@@ -62,8 +62,8 @@ def _p(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 
 
-def _cfg(T, D, H, E, K, router_f32, threads):
-    return _Cfg(T, D, H, E, K, int(router_f32), threads or host_threads())
+def _cfg(T, D, H, E, K, router_f32, threads, pad=128):
+    return _Cfg(T, D, H, E, K, int(router_f32), threads or host_threads(), pad)
 
 
 def topk_from_logits(logits, K):
@@ -121,14 +121,14 @@ def router_bwd(probs, idx, s_j, logits, counts, aux, zcoef):
 
 
 def forward(X, Wr, Wup, Wdown, K, Y=None, beta=0.0, bias=None, up_scale=None, down_scale=None,
-            threads=None):
+            threads=None, pad=128):
     """Full forward. X (T,D) u16; Wr (E,D) u16 or f32; Wup (E,H,D) u16 [hidden>0] or (E,D,D)
     [hidden==0, Wdown=None]; Wdown (E,D,H). Returns a dict with Y and every saved tensor."""
     T, D = X.shape
     E = Wr.shape[0]
     H = 0 if Wdown is None else Wup.shape[1]
-    cfg = _cfg(T, D, H, E, K, Wr.dtype == np.float32, threads)
-    cap = (T * K + 127) // 128 * 128 + 128 * E
+    cfg = _cfg(T, D, H, E, K, Wr.dtype == np.float32, threads, pad)
+    cap = (T * K + pad - 1) // pad * pad + pad * E
     X = np.ascontiguousarray(X)
     Wr = np.ascontiguousarray(Wr)
     Wup = np.ascontiguousarray(Wup)

@@ -6,9 +6,9 @@
 
 namespace tmt {
 
-// Padded group granularity: every expert group starts on a multiple of this many rows,
-// so a 128-row GEMM tile never spans two experts (the reference pads the same way to
-// keep its cuBLAS shapes stable, tmt-cuda/src/moe.cu:414-419).
+// Rows of one GEMM row tile and unit of every tile table. Expert groups start on a multiple of the
+// handle's pad (128 rows, or 256 for the CTA-pair GEMM), so a tile never spans two experts (the
+// reference pads to 128 to keep its cuBLAS shapes stable, tmt-cuda/src/moe.cu:414-419).
 constexpr int kPad = 128;
 // Tokens per router block: the unit of the deterministic slot ranking.
 constexpr int kTokBlock = 64;

@@ -186,7 +186,7 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         ep->bar_word = ep_alloc<int>(h, 1);
         CKE(cudaMemsetAsync(ep->bar_word, 0, sizeof(int), h->stream));
         if (ep->peer) {
-            const size_t tpad = (size_t)(h->d.tokens + kPad - 1) / kPad * kPad;
+            const size_t tpad = (size_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
             ep->Xc = ep_alloc<uint16_t>(h, tpad * D);
             CKE(cudaMemsetAsync(ep->Xc, 0, tpad * D * 2, h->stream));
             ep->dest_row0 = ep_alloc<int>(h, E);
@@ -262,7 +262,7 @@ void plan_step(tmt_moe* h) {
     NC(ep, ep->AllGather(h->rb.counts, ep->cnt_all_dev, E, ncclInt32, ep->comm, h->stream));
     CKE(cudaMemcpyAsync(ep->cnt_all.data(), ep->cnt_all_dev, (size_t)G * E * sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     CKE(cudaStreamSynchronize(h->stream));
-    const long long rows = tmt_moe_ep_plan(G, ep->r, E, kPad, ep->cnt_all.data(), ep->tok_poff.data(), ep->x_counts.data(),
+    const long long rows = tmt_moe_ep_plan(G, ep->r, E, h->pad, ep->cnt_all.data(), ep->tok_poff.data(), ep->x_counts.data(),
                                            ep->x_poff.data(), ep->src_off.data());
     if (rows < 0 || rows > ep->x_cap)
         throw std::runtime_error("expert-side capacity exceeded: " + std::to_string(rows) + " rows routed to this rank, room for " +
@@ -280,7 +280,7 @@ void plan_step(tmt_moe* h) {
         // where this rank's rows start inside the owner's group: the owner's plan, computed here as well
         std::vector<int> o_tok(E + 1), o_cnt(EL), o_poff(EL + 1), o_src((size_t)G * EL);
         for (int g = 0; g < G; ++g) {
-            const long long orow = tmt_moe_ep_plan(G, g, E, kPad, ep->cnt_all.data(), o_tok.data(), o_cnt.data(), o_poff.data(), o_src.data());
+            const long long orow = tmt_moe_ep_plan(G, g, E, h->pad, ep->cnt_all.data(), o_tok.data(), o_cnt.data(), o_poff.data(), o_src.data());
             if (orow < 0 || orow > ep->x_cap)
                 throw std::runtime_error("expert-side capacity exceeded on rank " + std::to_string(g) + ": " + std::to_string(orow) +
                                          " rows, room for " + std::to_string(ep->x_cap) + " (raise desc.ep_capacity_factor)");

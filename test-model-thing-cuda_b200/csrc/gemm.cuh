@@ -125,7 +125,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int e, long 
 
 // Launchers (gemm_tcgen05.cu / gemm_simt.cu). Both return the cudaError of the launch.
 cudaError_t launch_gemm_tcgen05(const GemmParams& p, int num_sms, cudaStream_t stream);
+cudaError_t launch_gemm_tcgen05_2cta(const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_simt(const GemmParams& p, int max_m_tiles, cudaStream_t stream);
 size_t gemm_tcgen05_smem_bytes();
+size_t gemm_tcgen05_2cta_smem_bytes();
 
 }  // namespace tmt

@@ -1,0 +1,286 @@
+// Grouped expert GEMM with CTA-pair MMA (tcgen05 cta_group::2): two CTAs of a cluster work on
+// one 256x256 tile. Each CTA stages its own 128 rows of A and HALF of the B tile (128 of the 256
+// columns), the pair's tensor cores read both halves, so shared-memory traffic per flop drops by
+// a third against the single-CTA kernel, whose 128x256 tiles are bound by shared-memory
+// bandwidth (TMA fill + operand reads) rather than by the tensor pipe.
+//
+// Protocol. Both CTAs run a TMA producer (warp 0) for their own tiles and signal the LEADER's
+// (cluster rank 0) "full" barrier; the leader's warp 1 issues the MMAs and commits to the
+// "empty" and "accumulator full" barriers of BOTH CTAs (one tcgen05.commit per CTA); the
+// epilogue warps of both CTAs drain their own 128 TMEM lanes and arrive on the leader's
+// "accumulator empty" barrier. Every TMA load has exactly one destination CTA. Waits are bounded as in the single-CTA
+// kernel; both CTAs always reach the closing cluster barrier before TMEM is freed.
+//
+// Needs every group padded to 256 rows so that the two 128-row halves of a tile belong to one
+// expert (the handle pads accordingly when this kernel is selected).
+#include "gemm.cuh"
+#include "tc_util.cuh"
+
+namespace tmt {
+namespace {
+
+using namespace tc;
+
+constexpr int kStages2 = 6;
+constexpr int kATile2 = kBM * kBK * 2;          // 16 KB: this CTA's 128 rows
+constexpr int kBTile2 = (kBN / 2) * kBK * 2;    // 16 KB: this CTA's 128 of the 256 columns
+constexpr int kStageBytes2 = kATile2 + kBTile2;
+constexpr int kThreads2 = 192;
+constexpr uint32_t kTmemCols2 = 512;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory, completion counted on a barrier that may live in the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in both CTAs of the pair once the MMAs
+// issued so far are done: one commit on the leader's own barrier, one on the peer's (addressed
+// through the cluster window).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    const uint32_t peer = map_to_cta(bar, 1);
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
+}
+
+struct Tile2 {
+    int expert, row0, col0, kb0, nkb;
+};
+
+// t counts 256-row tiles; `rank` selects this CTA's 128-row half and its 128-column share of B.
+__device__ __forceinline__ bool get_tile2(const GemmParams& p, int t, int m_pairs, int n_tiles, int rank, Tile2& ti) {
+    if (p.mode == kRowsRagged) {
+        if (t >= m_pairs * n_tiles) return false;
+        const int mp = t / n_tiles, nt = t - mp * n_tiles;
+        ti.expert = p.tile_expert[2 * mp];
+        ti.row0 = mp * 2 * kBM + rank * kBM;
+        ti.col0 = nt * kBN;
+        ti.kb0 = 0;
+        ti.nkb = (p.K + kBK - 1) / kBK;
+        return ti.expert >= 0 && ti.expert < p.experts;
+    }
+    const int per = m_pairs * n_tiles;
+    if (t >= per * p.experts) return false;
+    const int e = t / per, r = t - e * per;
+    const int mp = r / n_tiles, nt = r - mp * n_tiles;
+    ti.expert = e;
+    ti.row0 = mp * 2 * kBM + rank * kBM;
+    ti.col0 = nt * kBN;
+    ti.kb0 = p.poff[e] / kBK;
+    ti.nkb = (p.poff[e + 1] - p.poff[e]) / kBK;
+    return true;
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[kStages2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();
+    const bool leader = rank == 0;
+    const uint32_t tiles_s = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    volatile int* abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < kStages2; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols2) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();            // both CTAs' barriers are initialised and both hold their TMEM
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    const int n_tiles = (p.N + kBN - 1) / kBN;
+    const int m_pairs = p.mode == kRowsRagged ? (*p.num_m_tiles + 1) / 2 : (p.M + 2 * kBM - 1) / (2 * kBM);
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer (both CTAs) ----------------
+            int s = 0; uint32_t ph = 0;
+            uint32_t issued = 0, last_parity = 0;
+            bool ok = true;
+            for (int t = pair; ok; t += npairs) {
+                Tile2 ti;
+                if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) {
+                    if (p.mode == kRowsRagged && t < m_pairs * n_tiles) report(p.status, kErrSlotRange);
+                    break;
+                }
+                const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
+                const CUtensorMap* mb = p.mapB + (size_t)ti.expert * p.b_stride;
+                tensormap_acquire(ma);
+                tensormap_acquire(mb);
+                const int bcol0 = ti.col0 + rank * (kBN / 2);
+                for (int kb = 0; kb < ti.nkb; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+                    const uint32_t fb_local = smem_u32(&full_bar[s]);
+                    const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
+                    if (leader) mbar_expect_tx(fb_local, 2 * p.tx_bytes);      // both CTAs' bytes
+                    const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
+                    const int k0 = (ti.kb0 + kb) * kBK;
+                    if (p.a_mn) {
+                        for (int j = 0; j < p.a_boxes; ++j) tma_load_2d_pair(sa + j * 8192, ma, fb, ti.row0 + j * p.a_box_step, k0);
+                    } else {
+                        tma_load_2d_pair(sa, ma, fb, k0, ti.row0);
+                    }
+                    if (p.b_mn) {
+                        for (int j = 0; j < p.b_boxes; ++j) tma_load_2d_pair(sb + j * 8192, mb, fb, bcol0 + j * p.b_box_step, k0);
+                    } else {
+                        tma_load_2d_pair(sb, mb, fb, k0, bcol0);
+                    }
+                    issued |= 1u << s;
+                    last_parity = (last_parity & ~(1u << s)) | (ph << s);
+                    if (++s == kStages2) { s = 0; ph ^= 1; }
+                }
+            }
+            if (!ok && leader) {
+                // aborting: the leader's barriers count both CTAs' copies; wait (bounded) for what was announced
+                for (int q = 0; q < kStages2; ++q) {
+                    if (!(issued >> q & 1)) continue;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---------------- MMA issuer (leader CTA only) ----------------
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
+                                   ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
+            const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
+            const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = pair; ok; t += npairs) {
+                Tile2 ti;
+                if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) break;
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+                for (int kb = 0; kb < ti.nkb; ++kb) {
+                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, p.status)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
+                    const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                    tc_commit_pair(smem_u32(&empty_bar[s]));
+                    if (++s == kStages2) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                if (ti.nkb > 0) tc_commit_pair(smem_u32(&tfull_bar[acc]));
+                else {                       // empty group: nothing to wait for, release both epilogues
+                    mbar_arrive(smem_u32(&tfull_bar[acc]));
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+                }
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue (both CTAs): own 128 TMEM lanes ----------------
+        const int quarter = warp & 3;
+        int acc = 0; uint32_t acc_ph = 0;
+        for (int t = pair;; t += npairs) {
+            Tile2 ti;
+            if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) break;
+            bool ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const long row = (long)ti.row0 + quarter * 32 + lane;
+            const bool row_ok = (p.mode == kRowsRagged) ? (row < (long)*p.num_m_tiles * kBM) : (row < p.M);
+            float sw = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < kBN / kChunk; ++c) {
+                const int col0 = ti.col0 + c * kChunk;
+                if (col0 >= p.N) break;
+                float v[kChunk];
+                if (ti.nkb > 0) {
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kBN + c * kChunk), v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+                }
+                if (row_ok) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
+            }
+            if (EPI == kEpiDh && row_ok) p.sw_part[row * p.sw_ld + ti.col0 / kBN] = sw;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();            // the peer may still be reading this CTA's shared memory or signalling its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols2) : "memory");
+    }
+}
+
+template <int EPI>
+cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
+    const size_t smem = gemm_tcgen05_2cta_smem_bytes();
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    gemm_tcgen05_2cta_kernel<EPI><<<grid, kThreads2, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t gemm_tcgen05_2cta_smem_bytes() { return (size_t)kStages2 * kStageBytes2 + 1024; }
+
+cudaError_t launch_gemm_tcgen05_2cta(const GemmParams& p, int num_sms, cudaStream_t stream) {
+    const int grid = num_sms & ~1;      // whole CTA pairs
+    switch (p.epi) {
+        case kEpiBf16: return launch_one<kEpiBf16>(p, grid, stream);
+        case kEpiUp: return launch_one<kEpiUp>(p, grid, stream);
+        case kEpiDown: return launch_one<kEpiDown>(p, grid, stream);
+        case kEpiDh: return launch_one<kEpiDh>(p, grid, stream);
+        case kEpiF32: return launch_one<kEpiF32>(p, grid, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace tmt

@@ -34,6 +34,7 @@ struct RouteDims {
     int cap;              // rows of the grouped buffers
     int max_tiles;        // cap / kPad
     int router_f32;
+    int pad;              // group padding in rows: kPad or 2 * kPad
 };
 
 // Expert-parallel addressing: a grouped row of expert e lives in the buffer of the rank that owns e.

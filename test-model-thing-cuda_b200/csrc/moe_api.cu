@@ -106,7 +106,7 @@ void build_act_maps(tmt_moe* h) {
     }
     if (h->dl_g) {
         make_map(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, 64, 64);
-        make_map(&m[kDltK], h->dl_t, h->kw, (uint64_t)(h->d.tokens + kPad - 1) / kPad * kPad, 64, 128);
+        make_map(&m[kDltK], h->dl_t, h->kw, (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad, 64, 128);
     }
     CK(cudaMemcpyAsync(h->act_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
 }
@@ -123,17 +123,18 @@ void refresh_weights(tmt_moe* h, const void* const* Wup, const void* const* Wdow
     if (H > 0) h->down_seen.assign(Wdown, Wdown + E);
     for (int e = 0; e < E; ++e)
         if (!Wup[e] || (H > 0 && !Wdown[e])) throw std::runtime_error("null expert weight pointer");
-    if (h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05) {
+    if (h->tensor_core) {
+        const uint64_t brows = h->two_cta ? kBN / 2 : kBN;       // rows of B one CTA stages per k block
         std::vector<CUtensorMap> m((size_t)kNumWMaps * E);
         memset(m.data(), 0, m.size() * sizeof(CUtensorMap));
         for (int e = 0; e < E; ++e) {
             if (H > 0) {
-                make_map(&m[kUpK * E + e], Wup[e], D, H, 64, (uint32_t)std::min<uint64_t>(256, H));       // [H][D], k = D
-                make_map(&m[kDownK * E + e], Wdown[e], H, D, 64, (uint32_t)std::min<uint64_t>(256, D));   // [D][H], k = H
+                make_map(&m[kUpK * E + e], Wup[e], D, H, 64, (uint32_t)std::min<uint64_t>(brows, H));     // [H][D], k = D
+                make_map(&m[kDownK * E + e], Wdown[e], H, D, 64, (uint32_t)std::min<uint64_t>(brows, D)); // [D][H], k = H
                 make_map(&m[kDownMN * E + e], Wdown[e], H, D, 64, 64);    // dH: k = rows (D), n = H contiguous
                 make_map(&m[kUpMN * E + e], Wup[e], D, H, 64, 64);        // dXg: k = rows (H), n = D contiguous
             } else {
-                make_map(&m[kUpK * E + e], Wup[e], D, D, 64, (uint32_t)std::min<uint64_t>(256, D));
+                make_map(&m[kUpK * E + e], Wup[e], D, D, 64, (uint32_t)std::min<uint64_t>(brows, D));
                 make_map(&m[kUpMN * E + e], Wup[e], D, D, 64, 64);
             }
         }
@@ -181,8 +182,9 @@ GemmParams rows_gemm(tmt_moe* h, ActMap a, const uint16_t* A, WMap w, const uint
     p.A = A; p.lda = K; p.Bexp = Wptrs; p.ldb = w_mn ? N : K;
     p.a_mn = 0; p.b_mn = w_mn;
     p.N = N; p.K = K; p.epi = epi; p.ldc = N;
-    if (w_mn) { p.b_boxes = kBN / 64; p.tx_bytes = kBM * kBK * 2 + p.b_boxes * 8192; }
-    else p.tx_bytes = kBM * kBK * 2 + (uint32_t)std::min(kBN, N) * kBK * 2;
+    const int bcols = h->two_cta ? kBN / 2 : kBN;     // columns of the B tile one CTA stages
+    if (w_mn) { p.b_boxes = bcols / 64; p.tx_bytes = kBM * kBK * 2 + p.b_boxes * 8192; }
+    else p.tx_bytes = kBM * kBK * 2 + (uint32_t)std::min(bcols, N) * kBK * 2;
     return p;
 }
 
@@ -194,14 +196,19 @@ GemmParams red_gemm(tmt_moe* h, ActMap a, const uint16_t* A, int M, ActMap b, co
     p.mapB = h->act_maps + b; p.b_stride = 0;
     p.A = A; p.lda = M; p.B = B; p.ldb = N;
     p.a_mn = 1; p.b_mn = 1;
-    p.a_boxes = kBM / 64; p.b_boxes = kBN / 64;
+    p.a_boxes = kBM / 64; p.b_boxes = (h->two_cta ? kBN / 2 : kBN) / 64;
     p.tx_bytes = (p.a_boxes + p.b_boxes) * 8192;
     p.M = M; p.N = N; p.epi = kEpiF32; p.outF = out; p.ldc = N;
     return p;
 }
 
+void run_tc(tmt_moe* h, const GemmParams& p) {
+    if (h->two_cta) CK(launch_gemm_tcgen05_2cta(p, h->num_sms, h->stream));
+    else CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+}
+
 void run_gemm(tmt_moe* h, const GemmParams& p) {
-    if (h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05) CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+    if (h->tensor_core) run_tc(h, p);
     else CK(launch_gemm_simt(p, h->g_max_tiles, h->stream));
     h->launches += 1;
 }
@@ -259,7 +266,7 @@ void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
     CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream));
     prof_mark(h, kPhScan);
     CK(launch_scan(h->dims, h->rb, h->splits, h->stream));
-    const int plain = (h->dims.T + kPad - 1) / kPad;
+    const int plain = (h->dims.T + h->pad - 1) / h->pad * (h->pad / kPad);     // 128-row tiles, whole pairs for the CTA-pair kernel
     if (h->plain_num && plain != h->plain_num_host) {
         CK(cudaMemcpyAsync(h->plain_num, &plain, sizeof(int), cudaMemcpyHostToDevice, h->stream));
         h->plain_num_host = plain;
@@ -362,7 +369,7 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
 void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order) {
     h->ep_x_token_order = token_order;
     if (h->d.gemm_impl != TMT_MOE_GEMM_TCGEN05 || !h->dl_t) return;
-    const uint64_t tpad = (uint64_t)(h->d.tokens + kPad - 1) / kPad * kPad;
+    const uint64_t tpad = (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
     CUtensorMap m[2];
     memset(m, 0, sizeof m);
     make_map(&m[0], x_rows, h->d.dim, token_order ? tpad : (uint64_t)h->dims.cap, 64, 64);
@@ -391,7 +398,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         h->launches += 1;
         return;
     }
-    const bool tc = h->d.gemm_impl == TMT_MOE_GEMM_TCGEN05;
+    const bool tc = h->tensor_core;
     prof_mark(h, kPhRouterBwd);
     if (tc && !tok_order) CK(cudaMemsetAsync(h->dl_g, 0, (size_t)h->dims.cap * h->mw * 2, h->stream));
     CK(launch_router_bwd(h->dims, h->rb, sw_part, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, counts, n_norm,
@@ -427,11 +434,11 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.mapA = h->act_maps + (tok_order ? kDltMN : kDlgMN); p.a_stride = 0;
         p.mapB = h->act_maps + (x_is_ep ? kXsMN : kXgMN); p.b_stride = 0;
         p.a_mn = 1; p.b_mn = 1;
-        p.a_boxes = kBM / 64; p.b_boxes = kBN / 64;
+        p.a_boxes = kBM / 64; p.b_boxes = (h->two_cta ? kBN / 2 : kBN) / 64;
         p.tx_bytes = (p.a_boxes + p.b_boxes) * 8192;
         p.M = h->mw; p.N = D; p.experts = h->splits; p.poff = tok_order ? h->tok_split_poff : h->rb.split_poff;
         p.epi = kEpiF32; p.outF = h->dwr_part_ptrs; p.ldc = D;
-        CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+        run_tc(h, p);
         CK(launch_reduce_parts(h->dwr_partial, h->splits, h->mw, E, D, dWr, h->stream));
         h->launches += 2;
     }
@@ -442,12 +449,12 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.mapA = h->act_maps + kDltK; p.a_stride = 0;
         p.mapB = h->w_maps + (size_t)kNumWMaps * h->local_experts; p.b_stride = 0;
         p.a_mn = 0; p.b_mn = 1;
-        p.b_boxes = kBN / 64;
+        p.b_boxes = (h->two_cta ? kBN / 2 : kBN) / 64;
         p.tx_bytes = kBM * kBK * 2 + p.b_boxes * 8192;
         p.N = D; p.K = h->kw; p.experts = 1;
         p.tile_expert = h->plain_tiles; p.num_m_tiles = h->plain_num;
         p.epi = kEpiBf16; p.out0 = h->dXr; p.ldc = D;
-        CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+        run_tc(h, p);
         CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream, pm));
         h->launches += 2;
     }
@@ -461,7 +468,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
         throw std::runtime_error("require 1 <= topk <= experts <= 256 and topk <= 8");
     if (d.ep_world < 1 || d.ep_rank < 0 || d.ep_rank >= d.ep_world || d.experts % d.ep_world)
         throw std::runtime_error("invalid expert-parallel layout (experts must divide by ep_world)");
-    if ((long)d.tokens * d.topk + 128L * d.experts > 0x7fffff00L)
+    if ((long)d.tokens * d.topk + 256L * d.experts > 0x7fffff00L)
         throw std::runtime_error("tokens * topk exceeds the supported index range");
     CK(cudaSetDevice(d.device));
     cudaDeviceProp prop;
@@ -474,15 +481,20 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->num_sms = prop.multiProcessorCount;
     h->local_experts = d.experts / d.ep_world;
     const int T = d.tokens, E = d.experts, K = d.topk, D = d.dim, H = d.hidden;
-    // rows of the grouped buffers: every assignment plus up to kPad-1 pad rows per expert (moe.cu:331)
-    const long cap = ((long)T * K + kPad - 1) / kPad * kPad + (long)kPad * E;
-    h->dims = RouteDims{T, D, E, K, (int)cap, (int)(cap / kPad), d.router_dtype == TMT_MOE_F32};
+    if (d.gemm_impl < 0 || d.gemm_impl > 2) throw std::runtime_error("unknown gemm_impl");
+    h->tensor_core = d.gemm_impl != TMT_MOE_GEMM_SIMT;
+    h->two_cta = d.gemm_impl == TMT_MOE_GEMM_TCGEN05_2CTA;
+    h->pad = h->two_cta ? 2 * kPad : kPad;
+    const int pad = h->pad;
+    // rows of the grouped buffers: every assignment plus up to pad-1 pad rows per expert (moe.cu:331)
+    const long cap = ((long)T * K + pad - 1) / pad * pad + (long)pad * E;
+    h->dims = RouteDims{T, D, E, K, (int)cap, (int)(cap / kPad), d.router_dtype == TMT_MOE_F32, pad};
     // rows of the grouped GEMM buffers: the token-side layout on one GPU; under expert parallelism the
     // rows other ranks may route here, bounded by the capacity factor (default 1.5 x tokens x topk)
     long gcap = cap;
     if (d.ep_world > 1) {
         const double f = d.ep_capacity_factor > 0 ? d.ep_capacity_factor : 1.5;
-        gcap = ((long)(f * T * K) + kPad - 1) / kPad * kPad + (long)kPad * h->local_experts;
+        gcap = ((long)(f * T * K) + pad - 1) / pad * pad + (long)pad * h->local_experts;
         if (gcap > 0x7fffff00L) throw std::runtime_error("expert-side capacity exceeds the supported index range");
     }
     h->gcap = gcap;
@@ -520,12 +532,12 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
         h->dXg = dalloc<uint16_t>(h, (size_t)gcap * D);
         h->s_j = dalloc<float>(h, (size_t)T * K);
         h->dlogits = dalloc<float>(h, (size_t)T * E);
-        if (d.gemm_impl == TMT_MOE_GEMM_TCGEN05 && E > 1) {
+        if (h->tensor_core && E > 1) {
             h->kw = (E + 63) / 64 * 64;
             h->mw = (E + kBM - 1) / kBM * kBM;
             const int tiles = (h->mw / kBM) * ((D + kBN - 1) / kBN);
             h->splits = std::max(1, std::min(kMaxSplits, h->num_sms / tiles));
-            const size_t tpad = (size_t)(T + kPad - 1) / kPad * kPad;
+            const size_t tpad = (size_t)(T + pad - 1) / pad * pad;
             h->dl_t = dalloc<uint16_t>(h, tpad * h->kw);
             CK(cudaMemsetAsync(h->dl_t, 0, tpad * h->kw * 2, h->stream));
             h->dl_g = dalloc<uint16_t>(h, (size_t)cap * h->mw);
@@ -559,7 +571,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->gup_ptrs = dalloc<float*>(h, h->local_experts);
     h->gdown_ptrs = dalloc<float*>(h, h->local_experts);
     h->g_poff = b.poff; h->g_num_m_tiles = b.num_m_tiles; h->g_tile_expert = b.tile_expert; h->g_max_tiles = h->dims.max_tiles;
-    if (d.gemm_impl == TMT_MOE_GEMM_TCGEN05) build_act_maps(h);
+    if (h->tensor_core) build_act_maps(h);
     if (d.host_io) {
         h->Xs = dalloc<uint16_t>(h, (size_t)T * D);
         h->Ys = dalloc<uint16_t>(h, (size_t)T * D);

@@ -41,6 +41,8 @@ struct tmt_moe {
     // layout tables the grouped GEMMs run on: the token-side tables on one GPU, the expert-side ones under EP
     const int* g_poff = nullptr; const int* g_num_m_tiles = nullptr; const int* g_tile_expert = nullptr; int g_max_tiles = 0;
     long gcap = 0;      // rows of the grouped GEMM buffers
+    bool two_cta = false; bool tensor_core = true;
+    int pad = 128;      // group padding (rows)
     int x_cap = 0;
     float* bias = nullptr;
     bool has_bias = false;
@@ -71,6 +73,7 @@ struct tmt_moe {
     // NVFP4 scratch: dequantised bf16 weights and per-expert tensor scales
     uint16_t* q_up = nullptr; uint16_t* q_down = nullptr; float* q_scales = nullptr;
     std::vector<const void*> q_ptrs_host;
+    std::vector<const void*> q_key; std::vector<float> q_scales_host;   // what the scratch was expanded from
     bool q_expert_scales = false;   // forward applies q_scales[e] / q_scales[E+e] to the accumulators
     // expert parallelism
     tmt_ep_state* ep = nullptr;

@@ -85,7 +85,9 @@ __global__ void quantize_kernel(const uint16_t* __restrict__ W, long blocks, con
 }
 
 // bf16(q * block scale): exact (at most 6 significant bits). The tensor scale is applied
-// to the GEMM accumulator.
+// to the GEMM accumulator. This first NVFP4 path keeps the weights packed in the caller's
+// memory and expands them once into bf16 scratch for the tensor-core GEMMs; the expansion is
+// not fused into the GEMM's operand staging yet.
 __global__ void dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales, long blocks,
                                   uint16_t* __restrict__ W) {
     const long b = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -168,22 +170,35 @@ int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter, const 
                 h->q_ptrs_host[E + e] = h->q_down + (size_t)e * H * D;
             }
         }
+        // The dequantised copy is derived data: it is rebuilt only when the caller hands in other weights
+        // (other pointers or scales), e.g. once after a checkpoint load; sampling steps reuse it.
+        std::vector<const void*> key;
+        key.reserve(4 * E);
         std::vector<float> sc(2 * E);
         const long blocks = (long)H * D / 16;
         for (int e = 0; e < E; ++e) {
             if (Wup[e].rows != H || Wup[e].cols != D || Wdown[e].rows != D || Wdown[e].cols != H)
                 throw std::runtime_error("NVFP4 weight shape does not match the handle");
+            if (!Wup[e].packed || !Wup[e].scales || !Wdown[e].packed || !Wdown[e].scales)
+                throw std::runtime_error("null NVFP4 weight pointer");
             sc[e] = Wup[e].tensor_scale; sc[E + e] = Wdown[e].tensor_scale;
-            dequantize_kernel<<<(unsigned)((blocks + 255) / 256), 256, 0, h->stream>>>(
-                static_cast<const uint8_t*>(Wup[e].packed), static_cast<const uint8_t*>(Wup[e].scales), blocks,
-                h->q_up + (size_t)e * H * D);
-            dequantize_kernel<<<(unsigned)((blocks + 255) / 256), 256, 0, h->stream>>>(
-                static_cast<const uint8_t*>(Wdown[e].packed), static_cast<const uint8_t*>(Wdown[e].scales), blocks,
-                h->q_down + (size_t)e * H * D);
+            key.push_back(Wup[e].packed); key.push_back(Wup[e].scales); key.push_back(Wdown[e].packed); key.push_back(Wdown[e].scales);
         }
-        h->launches += 2 * E;
-        CKQ(cudaGetLastError());
-        CKQ(cudaMemcpyAsync(h->q_scales, sc.data(), sc.size() * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+        if (key != h->q_key || sc != h->q_scales_host) {
+            for (int e = 0; e < E; ++e) {
+                dequantize_kernel<<<(unsigned)((blocks + 255) / 256), 256, 0, h->stream>>>(
+                    static_cast<const uint8_t*>(Wup[e].packed), static_cast<const uint8_t*>(Wup[e].scales), blocks,
+                    h->q_up + (size_t)e * H * D);
+                dequantize_kernel<<<(unsigned)((blocks + 255) / 256), 256, 0, h->stream>>>(
+                    static_cast<const uint8_t*>(Wdown[e].packed), static_cast<const uint8_t*>(Wdown[e].scales), blocks,
+                    h->q_down + (size_t)e * H * D);
+            }
+            h->launches += 2 * E;
+            CKQ(cudaGetLastError());
+            CKQ(cudaMemcpyAsync(h->q_scales, sc.data(), sc.size() * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+            h->q_key = key;
+            h->q_scales_host = sc;
+        }
         h->q_expert_scales = true;
         forward_impl(h, X, Wrouter, h->q_ptrs_host.data(), h->q_ptrs_host.data() + E, Y, beta, tokens);
         h->q_expert_scales = false;

@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const Rou
         for (int e = 0; e < E; ++e) {
             b.off[e] = tk; tk += cnt_s[e];
             poff_s[e] = ptk; b.poff[e] = ptk;
-            ptk += (cnt_s[e] + kPad - 1) / kPad * kPad;
+            ptk += (cnt_s[e] + d.pad - 1) / d.pad * d.pad;
         }
         b.off[E] = tk; poff_s[E] = ptk; b.poff[E] = ptk;
         if (ptk > d.cap) { report(b.status, kErrSlotRange); ptk = 0; }

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtmt_moe_b200.so")
 
 BF16, F32 = 0, 1
-GEMM_TCGEN05, GEMM_SIMT = 0, 1
+GEMM_TCGEN05, GEMM_SIMT, GEMM_TCGEN05_2CTA = 0, 1, 2
 EP_PEER, EP_NCCL = 0, 1
 
 EXPORTS = (
@@ -108,6 +108,7 @@ class MoE:
         self.h = ctypes.c_void_p()
         _check(self.lib.tmt_moe_create(ctypes.byref(self.desc), ctypes.byref(self.h)), self.lib)
         self.tokens, self.dim, self.hidden, self.experts, self.topk = tokens, dim, hidden, experts, topk
+        self.pad = 256 if gemm_impl == GEMM_TCGEN05_2CTA else 128      # rows every expert group is padded to
         self._keep = None
 
     def close(self):

@@ -26,7 +26,8 @@ def _mods():
     O.build()
 
 
-IMPLS = [pytest.param(0, id="tcgen05"), pytest.param(1, id="simt")]
+IMPLS = [pytest.param(0, id="tcgen05"), pytest.param(1, id="simt"), pytest.param(2, id="tcgen05_2cta")]
+PAD = {0: 128, 1: 128, 2: 256}
 OUT_L2, OUT_MAX, GRAD_L2 = 1e-2, 2e-2, 3e-2
 
 
@@ -35,7 +36,8 @@ def _fwd_bwd(cfg, impl, seed=0, bias=None, beta=0.0, aux=0.1, zcoef=0.001, backw
     T, D, H, E, K = cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"]
     rf = cfg.get("router_f32", False)
     data = synth.make(T, D, H, E, K, rf, seed=seed, need_res=beta != 0.0, w_std=w_std, router_std=router_std)
-    ref = O.forward(data["X"], data["Wr"], data["Wup"], data["Wdown"], K, Y=data.get("Y0"), beta=beta, bias=bias)
+    ref = O.forward(data["X"], data["Wr"], data["Wup"], data["Wdown"], K, Y=data.get("Y0"), beta=beta, bias=bias,
+                    pad=PAD[impl])
     layer = G.Layer(data, T, D, E, K, H, rf, training=backward, gemm_impl=impl, bias=bias)
     Y = layer.forward(data.get("Y0"), beta)
     assert layer.moe.device_status() == 0
@@ -110,9 +112,10 @@ def test_tie_break_lowest_index():
     G.check_routing(layer, ref)
 
 
-def test_topk4_64_experts():
+@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
+def test_topk4_64_experts(impl):
     """Config-5 routing shape at reduced size: 64 experts, top-4, fp32 router."""
-    _fwd_bwd(dict(T=1024, D=256, H=256, E=64, K=4, router_f32=True), 0, seed=6, w_std=0.08, router_std=0.1)
+    _fwd_bwd(dict(T=1024, D=256, H=256, E=64, K=4, router_f32=True), impl, seed=6, w_std=0.08, router_std=0.1)
 
 
 def test_single_token_and_partial_batch():
@@ -128,23 +131,27 @@ def test_single_token_and_partial_batch():
 
 
 def test_tcgen05_matches_simt_buffers():
-    """Every grouped GEMM of the tensor-core path against the independent SIMT kernel on the
-    same inputs: pre-activation, SiLU output, gated output, dP, dXg and the weight gradients."""
+    """Every grouped GEMM of the two tensor-core kernels against the independent SIMT kernel on the
+    same inputs: pre-activation, SiLU output, gated output, dP, dXg and the weight gradients. Group
+    padding differs between the kernels, so grouped buffers are compared on their real rows."""
     cfg = dict(T=900, D=192, H=448, E=4, K=2)
     data = synth.make(cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"], seed=8, w_std=0.08)
     got = {}
-    for impl in (0, 1):
+    for impl in (0, 1, 2):
         layer = G.Layer(data, cfg["T"], cfg["D"], cfg["E"], cfg["K"], cfg["H"], gemm_impl=impl)
         layer.forward()
         g = layer.backward(data["dY"], 0.1, 0.001)
-        rows = int(layer.moe.read("poff")[-1])
-        bufs = {n: O.bf16_to_f32(layer.moe.read(n)[:rows]) for n in ("Xg", "P", "Hact", "Yg", "dYg", "dP", "dXg")}
-        bufs.update(dWup=g["dWup"], dWdown=g["dWdown"], sw=layer.moe.read("sw_part")[:rows].sum(1))
+        poff, counts = layer.moe.read("poff"), layer.moe.read("counts")
+        real = np.concatenate([np.arange(poff[e], poff[e] + counts[e]) for e in range(cfg["E"])])
+        bufs = {n: O.bf16_to_f32(layer.moe.read(n)[real]) for n in ("Xg", "P", "Hact", "Yg", "dYg", "dP", "dXg")}
+        bufs.update(dWup=g["dWup"], dWdown=g["dWdown"], dWr=g["dWr"], dX=O.bf16_to_f32(g["dX"]),
+                    sw=layer.moe.read("sw_part")[real].sum(1))
         got[impl] = bufs
         assert layer.moe.device_status() == 0
-    for n in got[0]:
-        assert np.isfinite(got[0][n]).all(), n
-        assert synth.rel_l2(got[0][n], got[1][n]) <= 4e-3, n
+    for impl in (0, 2):
+        for n in got[impl]:
+            assert np.isfinite(got[impl][n]).all(), (impl, n)
+            assert synth.rel_l2(got[impl][n], got[1][n]) <= 4e-3, (impl, n)
 
 
 def test_config1_full():
@@ -153,13 +160,14 @@ def test_config1_full():
     _fwd_bwd(synth.CONFIGS["c1"], 0, seed=11, backward=False)
 
 
+@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
 @pytest.mark.parametrize("name,tokens", [("c2", 1024), ("c4", 2048)])
-def test_training_configs_reduced_tokens(name, tokens):
+def test_training_configs_reduced_tokens(name, tokens, impl):
     """Configs 2 and 4 with their true widths and expert counts on a token subsample the CPU
     oracle finishes in seconds; config 4 with its Zipf(1.2) logit bias."""
     cfg = dict(synth.CONFIGS[name], T=tokens)
     bias = synth.zipf_bias(cfg["E"], 2.0) if name == "c4" else None
-    _fwd_bwd(cfg, 0, seed=12, bias=bias)
+    _fwd_bwd(cfg, impl, seed=12, bias=bias)
 
 
 def test_full_size_routing_and_invariants():
