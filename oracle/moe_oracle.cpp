@@ -407,14 +407,14 @@ void oracle_backward(const oracle_cfg* c, const uint16_t* X, const uint16_t* dY,
             std::vector<uint16_t> WdT((size_t)H * D);
             for (long d = 0; d < D; ++d)
                 for (long h = 0; h < H; ++h) WdT[h * D + d] = Wdown[(size_t)e * D * H + d * H + h];
-            std::vector<float> swpart((size_t)n * ((H + 255) / 256), 0.0f);
-            const long NT = (H + 255) / 256;
+            std::vector<float> swpart((size_t)n * ((H + 127) / 128), 0.0f);
+            const long NT = (H + 127) / 128;
             // the per-row gate-gradient partial sums follow a stated order: columns in
-            // increasing h inside tiles of 256 columns, tiles added in increasing order
+            // increasing h inside blocks of 128 columns, blocks added in increasing order
             gemm_nt(dYg.data() + r0 * D, D, WdT.data(), D, n, H, D, th, [&](long m, long h, float acc) {
                 float p = bf2f(P[(r0 + m) * H + h]);
                 dP[(r0 + m) * H + h] = f2bf(acc * silu_grad(p));
-                swpart[m * NT + h / 256] += acc * silu_f(p);
+                swpart[m * NT + h / 128] += acc * silu_f(p);
             });
             for (long m = 0; m < n; ++m) {
                 float s = 0;

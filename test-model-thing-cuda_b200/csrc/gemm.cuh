@@ -20,7 +20,7 @@ enum Epilogue : int {
     kEpiBf16 = 0,   // out0 = bf16(acc)
     kEpiUp = 1,     // out0 = P = bf16(acc * expert_scale); out1 = bf16(silu(P))   (out0 may be NULL)
     kEpiDown = 2,   // out0 = bf16(row_scale[r] * expert_scale * acc)
-    kEpiDh = 3,     // acc = dH*w: out0 = bf16(acc * silu'(P)); sw_part[r, tile] = sum acc * silu(P)
+    kEpiDh = 3,     // acc = dH*w: out0 = bf16(acc * silu'(P)); sw_part[r, col / kEpiCols] = sum acc * silu(P)
     kEpiF32 = 4,    // outF[e][m, n] = acc (fp32)
 };
 
@@ -28,6 +28,7 @@ constexpr int kBM = 128;   // tile rows (UMMA M)
 constexpr int kBN = 256;   // tile columns (UMMA N)
 constexpr int kBK = 64;    // k per stage: 64 bf16 = one 128-byte swizzle span
 constexpr int kChunk = 32; // columns one epilogue step handles per row
+constexpr int kEpiCols = 128; // columns of a tile one epilogue warp drains; also the width of one gate-gradient partial
 
 struct GemmParams {
     // tensor maps in device memory; map index = expert * stride (stride 0: one shared map)
@@ -53,7 +54,7 @@ struct GemmParams {
     const float* row_scale;       // kEpiDown
     const float* expert_scale;    // optional per-expert factor (NVFP4 tensor scale), may be NULL
     const uint16_t* P;            // kEpiDh
-    float* sw_part; int sw_ld;    // kEpiDh: per-row partial sums, one per column tile
+    float* sw_part; int sw_ld;    // kEpiDh: per-row partial sums, one per kEpiCols columns
     int* status;
 };
 

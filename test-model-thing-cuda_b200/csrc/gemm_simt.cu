@@ -36,7 +36,7 @@ __global__ void gemm_simt_kernel(const GemmParams p, int max_m_tiles) {
             // handled below by recomputation per 256-column tile
         }
         epilogue_chunk<EPI>(p, e, r_all, col0, v, sw);
-        if constexpr (EPI == kEpiDh) atomicAdd(&p.sw_part[r_all * p.sw_ld + col0 / kBN], sw);
+        if constexpr (EPI == kEpiDh) atomicAdd(&p.sw_part[r_all * p.sw_ld + col0 / kEpiCols], sw);
     } else {
         const long per = p.M;
         const int e = (int)(r_all / per);

@@ -18,8 +18,13 @@ constexpr int kStages = 4;
 constexpr int kATile = kBM * kBK * 2;   // 16 KB
 constexpr int kBTile = kBN * kBK * 2;   // 32 KB
 constexpr int kStageBytes = kATile + kBTile;
-constexpr int kThreads = 192;
+// Epilogue warps per CTA: 4 (one per TMEM lane quarter, 256 columns each) or, for the epilogue that
+// also reads the saved pre-activation (measured: that one is latency-bound), 8 (two per quarter, 128
+// columns each). Threads = TMA warp + MMA warp + epilogue warps.
+template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiDh ? 8 : 4; }
+template <int EPI> __host__ __device__ constexpr int block_threads() { return 64 + 32 * epi_warps<EPI>(); }
 constexpr uint32_t kTmemCols = 512;     // two fp32 accumulators of 256 columns
+constexpr int kPrefetch = 0;            // k blocks an L2 prefetch would run ahead of the loads: measured harmful (the TMA unit is the limiter), off
 
 using namespace tc;
 
@@ -51,7 +56,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int m_tiles
 }
 
 template <int EPI>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tfull_bar[2], tempty_bar[2];
     __shared__ uint32_t tmem_base_s;
@@ -65,7 +70,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 1 * epi_warps<EPI>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -88,6 +93,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
             uint32_t issued = 0;           // bit s set once stage s has received a load
             uint32_t last_parity = 0;      // parity of the last load issued into stage s
             bool ok = true;
+            // L2 prefetch cursor: runs kPrefetch k blocks ahead of the loads (across tile boundaries), so
+            // that a stage's boxes are L2 hits by the time they are fetched into shared memory
+            int pt = blockIdx.x, pkb = 0;
+            TileInfo pti;
+            bool pvalid = get_tile(p, pt, m_tiles, n_tiles, pti);
+            auto prefetch_next = [&]() {
+                while (pvalid && pkb >= pti.nkb) { pt += gridDim.x; pkb = 0; pvalid = get_tile(p, pt, m_tiles, n_tiles, pti); }
+                if (!pvalid) return;
+                const CUtensorMap* ma = p.mapA + (size_t)pti.expert * p.a_stride;
+                const CUtensorMap* mb = p.mapB + (size_t)pti.expert * p.b_stride;
+                const int k0 = (pti.kb0 + pkb) * kBK;
+                if (p.a_mn) { for (int j = 0; j < p.a_boxes; ++j) tma_prefetch_2d(ma, pti.row0 + j * p.a_box_step, k0); }
+                else tma_prefetch_2d(ma, k0, pti.row0);
+                if (p.b_mn) { for (int j = 0; j < p.b_boxes; ++j) tma_prefetch_2d(mb, pti.col0 + j * p.b_box_step, k0); }
+                else tma_prefetch_2d(mb, k0, pti.col0);
+                ++pkb;
+            };
+            for (int i = 0; i < kPrefetch; ++i) prefetch_next();
             for (int t = blockIdx.x; ok; t += gridDim.x) {
                 TileInfo ti;
                 if (!get_tile(p, t, m_tiles, n_tiles, ti)) {
@@ -114,6 +137,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
                     } else {
                         tma_load_2d(sb, mb, fb, k0, ti.col0);
                     }
+                    if (kPrefetch > 0) prefetch_next();
                     issued |= 1u << s;
                     last_parity = (last_parity & ~(1u << s)) | (ph << s);
                     if (++s == kStages) { s = 0; ph ^= 1; }
@@ -166,6 +190,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
     } else {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
+        constexpr int kWarpCols = kBN / (epi_warps<EPI>() / 4);      // columns of the tile this warp drains
+        const int half = (warp - 2) >> 2;
         int acc = 0; uint32_t acc_ph = 0;
         for (int t = blockIdx.x;; t += gridDim.x) {
             TileInfo ti;
@@ -179,7 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
             const bool row_ok = (p.mode == kRowsRagged) || (row < p.M);
             float sw = 0.0f;
 #pragma unroll 1
-            for (int c = 0; c < kBN / kChunk; ++c) {
+            for (int c = half * (kWarpCols / kChunk); c < (half + 1) * (kWarpCols / kChunk); ++c) {
                 const int col0 = ti.col0 + c * kChunk;
                 if (col0 >= p.N) break;
                 float v[kChunk];
@@ -191,7 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
                 }
                 if (row_ok) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
             }
-            if (EPI == kEpiDh && row_ok) p.sw_part[row * p.sw_ld + ti.col0 / kBN] = sw;
+            if (EPI == kEpiDh && row_ok && ti.col0 + half * kEpiCols < p.N) p.sw_part[row * p.sw_ld + (ti.col0 + half * kEpiCols) / kEpiCols] = sw;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
@@ -211,7 +237,7 @@ cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
     const size_t smem = gemm_tcgen05_smem_bytes();
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemm_tcgen05_kernel<EPI><<<grid, kThreads, smem, stream>>>(p);
+    gemm_tcgen05_kernel<EPI><<<grid, block_threads<EPI>(), smem, stream>>>(p);
     return cudaGetLastError();
 }
 

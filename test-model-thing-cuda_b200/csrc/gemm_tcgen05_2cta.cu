@@ -21,11 +21,16 @@ namespace {
 
 using namespace tc;
 
-constexpr int kStages2 = 6;
+constexpr int kStages2 = 7;
+constexpr int kPrefetch2 = 0;           // L2 prefetch distance in k blocks: measured harmful (the TMA unit is the limiter), off
 constexpr int kATile2 = kBM * kBK * 2;          // 16 KB: this CTA's 128 rows
 constexpr int kBTile2 = (kBN / 2) * kBK * 2;    // 16 KB: this CTA's 128 of the 256 columns
 constexpr int kStageBytes2 = kATile2 + kBTile2;
-constexpr int kThreads2 = 192;
+// Epilogue warps per CTA: 4 (one per TMEM lane quarter, 256 columns each) or, for the epilogue that
+// also reads the saved pre-activation (measured: that one is latency-bound), 8 (two per quarter, 128
+// columns each). Threads = TMA warp + MMA warp + epilogue warps.
+template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiDh ? 8 : 4; }
+template <int EPI> __host__ __device__ constexpr int block_threads() { return 64 + 32 * epi_warps<EPI>(); }
 constexpr uint32_t kTmemCols2 = 512;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -96,7 +101,7 @@ __device__ __forceinline__ bool get_tile2(const GemmParams& p, int t, int m_pair
 }
 
 template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kStages2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2];
     __shared__ uint32_t tmem_base_s;
@@ -111,7 +116,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_t
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < kStages2; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 8); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 2 * epi_warps<EPI>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -135,6 +140,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_t
             int s = 0; uint32_t ph = 0;
             uint32_t issued = 0, last_parity = 0;
             bool ok = true;
+            // L2 prefetch cursor, kPrefetch2 k blocks ahead of the loads (across tile boundaries)
+            int pt = pair, pkb = 0;
+            Tile2 pti;
+            bool pvalid = get_tile2(p, pt, m_pairs, n_tiles, rank, pti);
+            auto prefetch_next = [&]() {
+                while (pvalid && pkb >= pti.nkb) { pt += npairs; pkb = 0; pvalid = get_tile2(p, pt, m_pairs, n_tiles, rank, pti); }
+                if (!pvalid) return;
+                const CUtensorMap* ma = p.mapA + (size_t)pti.expert * p.a_stride;
+                const CUtensorMap* mb = p.mapB + (size_t)pti.expert * p.b_stride;
+                const int k0 = (pti.kb0 + pkb) * kBK, bc = pti.col0 + rank * (kBN / 2);
+                if (p.a_mn) { for (int j = 0; j < p.a_boxes; ++j) tma_prefetch_2d(ma, pti.row0 + j * p.a_box_step, k0); }
+                else tma_prefetch_2d(ma, k0, pti.row0);
+                if (p.b_mn) { for (int j = 0; j < p.b_boxes; ++j) tma_prefetch_2d(mb, bc + j * p.b_box_step, k0); }
+                else tma_prefetch_2d(mb, k0, bc);
+                ++pkb;
+            };
+            for (int i = 0; i < kPrefetch2; ++i) prefetch_next();
             for (int t = pair; ok; t += npairs) {
                 Tile2 ti;
                 if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) {
@@ -163,6 +185,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_t
                     } else {
                         tma_load_2d_pair(sb, mb, fb, k0, bcol0);
                     }
+                    if (kPrefetch2 > 0) prefetch_next();
                     issued |= 1u << s;
                     last_parity = (last_parity & ~(1u << s)) | (ph << s);
                     if (++s == kStages2) { s = 0; ph ^= 1; }
@@ -217,7 +240,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_t
         __syncwarp();
     } else {
         // ---------------- epilogue (both CTAs): own 128 TMEM lanes ----------------
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
+        constexpr int kWarpCols = kBN / (epi_warps<EPI>() / 4);      // columns of the tile this warp drains
+        const int half = (warp - 2) >> 2;
         int acc = 0; uint32_t acc_ph = 0;
         for (int t = pair;; t += npairs) {
             Tile2 ti;
@@ -230,7 +255,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_t
             const bool row_ok = (p.mode == kRowsRagged) ? (row < (long)*p.num_m_tiles * kBM) : (row < p.M);
             float sw = 0.0f;
 #pragma unroll 1
-            for (int c = 0; c < kBN / kChunk; ++c) {
+            for (int c = half * (kWarpCols / kChunk); c < (half + 1) * (kWarpCols / kChunk); ++c) {
                 const int col0 = ti.col0 + c * kChunk;
                 if (col0 >= p.N) break;
                 float v[kChunk];
@@ -242,7 +267,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1) gemm_t
                 }
                 if (row_ok) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
             }
-            if (EPI == kEpiDh && row_ok) p.sw_part[row * p.sw_ld + ti.col0 / kBN] = sw;
+            if (EPI == kEpiDh && row_ok && ti.col0 + half * kEpiCols < p.N) p.sw_part[row * p.sw_ld + (ti.col0 + half * kEpiCols) / kEpiCols] = sw;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
@@ -263,7 +288,7 @@ cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
     const size_t smem = gemm_tcgen05_2cta_smem_bytes();
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemm_tcgen05_2cta_kernel<EPI><<<grid, kThreads2, smem, stream>>>(p);
+    gemm_tcgen05_2cta_kernel<EPI><<<grid, block_threads<EPI>(), smem, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -557,7 +557,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
         if (H > 0) {
             h->P = dalloc<uint16_t>(h, (size_t)gcap * H);
             h->dP = dalloc<uint16_t>(h, (size_t)gcap * H);
-            h->sw_ld = (H + kBN - 1) / kBN;
+            h->sw_ld = (H + kEpiCols - 1) / kEpiCols;
             h->sw_part = dalloc<float>(h, (size_t)gcap * h->sw_ld);
         }
     } else {

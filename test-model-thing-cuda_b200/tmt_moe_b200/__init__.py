@@ -173,7 +173,7 @@ class MoE:
                            "tile_expert": ((cap // 128,), np.int32), "num_m_tiles": ((1,), np.int32),
                            "Xg": ((cap, D), np.uint16), "Yg": ((cap, D), np.uint16), "dYg": ((cap, D), np.uint16),
                            "dXg": ((cap, D), np.uint16), "P": ((cap, H), np.uint16), "Hact": ((cap, H), np.uint16),
-                           "dP": ((cap, H), np.uint16), "sw_part": ((cap, (H + 255) // 256), np.float32)})
+                           "dP": ((cap, H), np.uint16), "sw_part": ((cap, (H + 127) // 128), np.float32)})
         shape, dt = shapes[name]
         out = np.empty(shape, dt)
         n = self.lib.tmt_moe_read(self.h, name.encode(), _ptr(out), ctypes.c_size_t(out.nbytes))
