@@ -36,6 +36,9 @@ CONFIGS = {
                desc="config 1: tokens=2048 dim=512 experts=4 topk=2 ffn 512-1024-512, forward only, fp32 router"),
     "c2": dict(T=16384, D=1024, H=4096, E=8, K=2, router_f32=False, backward=True,
                desc="config 2: tokens=16384 dim=1024 experts=8 topk=2 ffn 1024-4096-1024, fwd+bwd, aux 0.1 + z-loss"),
+    "c3": dict(T=64, D=1024, H=2048, E=16, K=2, router_f32=False, backward=False, nvfp4=True, decode_steps=256,
+               desc="config 3: NVFP4 decode, 64 streams x 1 position per decode step, 256 decode steps per step, "
+                    "dim=1024 experts=16 topk=2 ffn 1024-2048-1024, forward only, bf16 router"),
     "c4": dict(T=65536, D=1024, H=4096, E=16, K=2, router_f32=False, backward=True, zipf=True,
                desc="config 4: tokens=65536 dim=1024 experts=16 topk=2 ffn 1024-4096-1024, Zipf(1.2) logit bias, fwd+bwd"),
     "c5": dict(T=131072, D=2048, H=2048, E=64, K=4, router_f32=True, backward=True,
@@ -174,6 +177,19 @@ def make_device_data(cfg, T, local_experts, rank, torch):
     d["dWdown"] = torch.zeros((local_experts, D, H), device="cuda", dtype=torch.float32)
     d["Y"] = torch.zeros((T, D), device="cuda", dtype=torch.bfloat16)
     d["dX"] = torch.zeros((T, D), device="cuda", dtype=torch.bfloat16)
+    if cfg.get("nvfp4"):
+        import tmt_moe_b200 as M
+        n = cfg["decode_steps"]
+        d["Xsteps"] = bf((n, T, D), 1.0)                     # a fresh batch of 64 rows for every decode step
+        d["q"] = {"up": [], "down": [], "keep": []}
+        for e in range(local_experts):
+            for name, W in (("up", d["Wup"][e]), ("down", d["Wdown"][e])):
+                rows, cols = W.shape
+                packed = torch.empty((rows, cols // 2), dtype=torch.uint8, device="cuda")
+                scales = torch.empty((rows, cols // 16), dtype=torch.uint8, device="cuda")
+                ts = M.quantize_nvfp4(W, rows, cols, packed, scales)
+                d["q"][name].append((packed, scales, ts, rows, cols))
+                d["q"]["keep"] += [packed, scales]
     return d
 
 
@@ -213,7 +229,7 @@ def main():
             return
         import numpy as np
         import synth
-        sample = min(cpu_sample_tokens(cfg), 1024 if args.steps + args.warmup > 4 else 1 << 30)
+        sample = 2048 if cfg.get("nvfp4") else min(cpu_sample_tokens(cfg), 1024 if args.steps + args.warmup > 4 else 1 << 30)
         host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
         if cfg.get("zipf"):
             host["bias"] = synth.zipf_bias(E, 2.0)
@@ -238,7 +254,10 @@ def main():
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     local_experts = E // world
+    work_stream = torch.cuda.Stream()          # a real stream (not the legacy default), so the decode loop can be graph-captured
+    torch.cuda.set_stream(work_stream)
     d = make_device_data(cfg, T, local_experts, rank, torch)
+    torch.cuda.synchronize()
     stream = torch.cuda.current_stream().cuda_stream
     moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32 if cfg["router_f32"] else M.BF16,
                 training=cfg["backward"], device=local_rank, host_io=(world == 1 and not args.no_e2e),
@@ -255,10 +274,38 @@ def main():
     dWup = [d["dWup"][e] for e in range(local_experts)]
     dWdown = [d["dWdown"][e] for e in range(local_experts)]
 
-    def step():
-        moe.forward(d["X"], d["Wr"], Wup, Wdown, d["Y"], 0.0)
-        if cfg["backward"]:
-            moe.backward(d["dY"], d["Wr"], Wup, Wdown, d["dWr"], dWup, dWdown, d["dX"], AUX, ZCOEF)
+    graph_info = {}
+    launches0_per_loop = 0
+    if cfg.get("nvfp4"):
+        xs = [d["Xsteps"][i] for i in range(cfg["decode_steps"])]
+
+        def decode_loop():
+            for x in xs:
+                moe.forward_nvfp4(x, d["Wr"], d["q"]["up"], d["q"]["down"], d["Y"], 0.0)
+        decode_loop()                        # expands the weights once, allocates the scratch
+        torch.cuda.synchronize()
+        lc = moe.launch_count
+        decode_loop()
+        launches0_per_loop = moe.launch_count - lc      # kernels one replay of the captured loop launches
+        step = decode_loop
+        try:                                 # the launch-bound loop as one CUDA graph on the handle's stream
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=work_stream):
+                decode_loop()
+            g.replay()
+            torch.cuda.synchronize()
+            if moe.device_status() != 0:
+                raise RuntimeError("device status after graph replay")
+            step = g.replay
+            graph_info = {"cuda_graph": True}
+        except Exception as exc:             # noqa: BLE001  (capture is an optimisation, eager is the contract)
+            graph_info = {"cuda_graph": False, "graph_error": str(exc)[:200]}
+            torch.cuda.synchronize()
+    else:
+        def step():
+            moe.forward(d["X"], d["Wr"], Wup, Wdown, d["Y"], 0.0)
+            if cfg["backward"]:
+                moe.backward(d["dY"], d["Wr"], Wup, Wdown, d["dWr"], dWup, dWdown, d["dX"], AUX, ZCOEF)
 
     working_set = d["X"].numel() * 2 * (2 + 2 * K)
     flush = working_set < 2 * L2_BYTES
@@ -279,7 +326,7 @@ def main():
     if moe.device_status() != 0:
         raise SystemExit("device status %d after warm-up" % moe.device_status())
     launches0 = moe.launch_count
-    moe.set_profile(True)
+    moe.set_profile(not graph_info.get("cuda_graph", False))
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
     wall0 = time.time()
@@ -303,11 +350,37 @@ def main():
     status = moe.device_status()
     if status != 0:
         raise SystemExit("device status %d after the timed region" % status)
-    value = T * world / (ms * 1e-3)
+    tokens_per_step = T * cfg.get("decode_steps", 1)
+    value = tokens_per_step * world / (ms * 1e-3)
 
     # ---- end to end through the host-buffer entry point (single GPU) ----
     e2e = None
-    if world == 1 and not args.no_e2e:
+    if world == 1 and not args.no_e2e and cfg.get("nvfp4"):
+        # sampler loop: per decode step the 64 input rows come from pinned host memory and the 64 output rows go
+        # back (the sampler needs them before it can choose the next byte), so every decode step synchronises
+        n = cfg["decode_steps"]
+        hXs = torch.empty((n, T, D), dtype=torch.bfloat16).pin_memory()
+        hXs.copy_(d["Xsteps"])
+        hY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+        xin = torch.empty((T, D), dtype=torch.bfloat16, device="cuda")
+
+        def host_loop():
+            for i in range(n):
+                xin.copy_(hXs[i], non_blocking=True)
+                moe.forward_nvfp4(xin, d["Wr"], d["q"]["up"], d["q"]["down"], d["Y"], 0.0)
+                hY.copy_(d["Y"], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+        host_loop()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            host_loop()
+        e1.record()
+        torch.cuda.synchronize()
+        e_ms = e0.elapsed_time(e1) / args.steps
+        e2e = {"value": tokens_per_step / (e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": n * T * D * 2,
+               "d2h_bytes_per_step": n * T * D * 2, "ms_per_step": e_ms}
+    elif world == 1 and not args.no_e2e:
         hX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
         hX.copy_(d["X"])
         hdY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
@@ -353,6 +426,16 @@ def main():
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                 "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
                 "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}
+    if cfg.get("nvfp4"):
+        # weight-byte roofline: every expert hit in a decode step streams its packed weights once
+        # (0.5 B per value + one scale byte per 16 values), 2*D*H values per expert; with 128 assignments over
+        # 16 experts all experts are hit (P(miss) < 1e-3), plus the 64 input and output rows
+        per_decode = E * 2.0 * D * H * (0.5 + 1.0 / 16) + 2 * T * D * 2
+        gbs = per_decode * cfg["decode_steps"] / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "decode step (router, dispatch, 2 grouped GEMMs, combine)", "achieved": gbs,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                    "peak_kind": pk_kind + " copy bandwidth; algorithmic bytes are the PACKED weights, this path reads a bf16 expansion",
+                    "bytes_per_decode_step": per_decode}
     hbm = {}
     bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12), "combine": (A * D * 2 + T * D * 2),
                 "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + T * D * 2)}
@@ -365,19 +448,26 @@ def main():
                 config={"workload": workload, "tokens_per_gpu": T,
                         "parallelism": ("ep%d/%s" % (world, args.ep_transport)) if world > 1 else "single",
                         "l2": "L2 flushed between steps" if flush else "working set larger than L2 (no flush needed)"},
-                clocks=clocks, gpu_launches=launches, roofline=roofline, hbm_kernels=hbm,
+                clocks=clocks, gpu_launches=launches if not graph_info.get("cuda_graph") else launches0_per_loop * args.steps,
+                roofline=roofline, hbm_kernels=hbm,
                 phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})
+    line.update(graph_info)
+    if cfg.get("nvfp4"):
+        line["dtype"] = "nvfp4 weights, bf16 activations"
+        line["config"]["decode_steps_per_step"] = cfg["decode_steps"]
     if e2e is not None:
         line["e2e"] = e2e
     if world == 1 and not args.no_cpu_baseline:
         import synth
-        sample = cpu_sample_tokens(cfg)
+        sample = 2048 if cfg.get("nvfp4") else cpu_sample_tokens(cfg)
         host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
         if cfg.get("zipf"):
             host["bias"] = synth.zipf_bias(E, 2.0)
         tps, threads, sec = run_cpu(cfg, host, sample, 1, 0)
+        what = ("%d decode steps of %d rows as one batch, bf16 weights (same arithmetic as the dequantised ones)" % (sample // T, T)
+                if cfg.get("nvfp4") else "first %d tokens of the workload" % sample)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                "sample": "first %d tokens of the workload, all %d experts, one pass (%.1f s)" % (sample, E, sec)}
+                                "sample": "%s, all %d experts, one pass (%.1f s)" % (what, E, sec)}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

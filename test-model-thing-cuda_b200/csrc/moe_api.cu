@@ -573,6 +573,10 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->g_poff = b.poff; h->g_num_m_tiles = b.num_m_tiles; h->g_tile_expert = b.tile_expert; h->g_max_tiles = h->dims.max_tiles;
     if (h->tensor_core) build_act_maps(h);
     if (d.host_io) {
+        CK(cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+        CK(cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming));
+        CK(cudaEventCreateWithFlags(&h->ev_dy, cudaEventDisableTiming));
+        CK(cudaEventCreateWithFlags(&h->ev_fwd, cudaEventDisableTiming));
         h->Xs = dalloc<uint16_t>(h, (size_t)T * D);
         h->Ys = dalloc<uint16_t>(h, (size_t)T * D);
         if (d.training) {
@@ -609,6 +613,8 @@ void tmt_moe_destroy(tmt_moe* h) {
     cudaStreamSynchronize(h->stream);
     ep_teardown(h);
     for (cudaEvent_t e : h->prof.pool) cudaEventDestroy(e);
+    if (h->copy_stream) { cudaStreamSynchronize(h->copy_stream); cudaStreamDestroy(h->copy_stream); }
+    for (cudaEvent_t e : {h->ev_start, h->ev_dy, h->ev_fwd}) if (e) cudaEventDestroy(e);
     for (void* p : h->allocs) cudaFree(p);
     delete h;
 }
@@ -686,18 +692,30 @@ int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const
         check_tokens(h, tokens);
         CK(cudaSetDevice(h->d.device));
         const size_t bytes = (size_t)tokens * h->d.dim * 2;
+        // The gradient upload runs on a second stream under the forward pass and the output download under
+        // the backward pass (PCIe is full duplex); the compute stream only waits for what it consumes.
+        const bool bwd = dY_host != nullptr;
+        if (bwd && (!dX_host || !h->dYs)) throw std::runtime_error("backward needs dX_host and training = 1");
+        CK(cudaEventRecord(h->ev_start, h->stream));
+        if (bwd) {
+            CK(cudaStreamWaitEvent(h->copy_stream, h->ev_start, 0));     // the previous step no longer reads dYs
+            CK(cudaMemcpyAsync(h->dYs, dY_host, bytes, cudaMemcpyHostToDevice, h->copy_stream));
+            CK(cudaEventRecord(h->ev_dy, h->copy_stream));
+        }
         CK(cudaMemcpyAsync(h->Xs, X_host, bytes, cudaMemcpyHostToDevice, h->stream));
         if (beta != 0.0f) CK(cudaMemcpyAsync(h->Ys, Y_host, bytes, cudaMemcpyHostToDevice, h->stream));
         forward_impl(h, h->Xs, Wrouter, Wup, Wdown, h->Ys, beta, tokens);
-        CK(cudaMemcpyAsync(Y_host, h->Ys, bytes, cudaMemcpyDeviceToHost, h->stream));
-        if (dY_host) {
-            if (!dX_host || !h->dYs) throw std::runtime_error("backward needs dX_host and training = 1");
-            CK(cudaMemcpyAsync(h->dYs, dY_host, bytes, cudaMemcpyHostToDevice, h->stream));
+        CK(cudaEventRecord(h->ev_fwd, h->stream));
+        CK(cudaStreamWaitEvent(h->copy_stream, h->ev_fwd, 0));
+        CK(cudaMemcpyAsync(Y_host, h->Ys, bytes, cudaMemcpyDeviceToHost, h->copy_stream));
+        if (stat_host)
+            CK(cudaMemcpyAsync(stat_host, h->rb.stat, (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->copy_stream));
+        if (bwd) {
+            CK(cudaStreamWaitEvent(h->stream, h->ev_dy, 0));
             backward_impl(h, h->dYs, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, h->dXs, aux, zcoef);
             CK(cudaMemcpyAsync(dX_host, h->dXs, bytes, cudaMemcpyDeviceToHost, h->stream));
         }
-        if (stat_host)
-            CK(cudaMemcpyAsync(stat_host, h->rb.stat, (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaStreamSynchronize(h->copy_stream));
         CK(cudaStreamSynchronize(h->stream));
     })
 }

@@ -70,6 +70,8 @@ struct tmt_moe {
     std::vector<float*> gup_seen, gdown_seen;
     // staging for the host-buffer entry point
     uint16_t *Xs = nullptr, *Ys = nullptr, *dYs = nullptr, *dXs = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_dy = nullptr, ev_fwd = nullptr;
     // NVFP4 scratch: dequantised bf16 weights and per-expert tensor scales
     uint16_t* q_up = nullptr; uint16_t* q_down = nullptr; float* q_scales = nullptr;
     std::vector<const void*> q_ptrs_host;

@@ -210,6 +210,35 @@ def test_deterministic_reruns():
         np.testing.assert_array_equal(ga[k], gb[k])
 
 
+def test_host_step_equals_device_path():
+    """The host-buffer entry point (pinned host X / dY in, Y / dX / statistics out, copies overlapped with
+    compute on a second stream) returns exactly what the device-pointer calls return."""
+    cfg = dict(T=3000, D=256, H=384, E=8, K=2)
+    data = synth.make(cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"], seed=15, need_res=True)
+    layer = G.Layer(data, cfg["T"], cfg["D"], cfg["E"], cfg["K"], cfg["H"])
+    Y = layer.forward(data["Y0"], 1.0).copy()
+    g = layer.backward(data["dY"], 0.1, 0.001)
+    stat, _, _ = layer.moe.stats()
+    host = M.MoE(cfg["T"], cfg["D"], cfg["E"], cfg["K"], hidden=cfg["H"], host_io=True)
+    pin = lambda a: torch.from_numpy(a.view(np.int16).copy()).pin_memory()
+    hX, hdY, hY = pin(data["X"]), pin(data["dY"]), pin(data["Y0"])
+    hdX = torch.zeros_like(hX).pin_memory()
+    hstat = torch.zeros(cfg["E"] + 1).pin_memory()
+    E = cfg["E"]
+    dWr = torch.zeros_like(layer.dWr)
+    dWup_all, dWdown_all = torch.zeros_like(layer.dWup_all), torch.zeros_like(layer.dWdown_all)
+    for _ in range(2):
+        hY.copy_(pin(data["Y0"]))
+        host.step_host(hX, hdY, layer.Wr, layer.Wup, layer.Wdown, dWr, [dWup_all[e] for e in range(E)],
+                       [dWdown_all[e] for e in range(E)], hY, hdX, hstat, 1.0, 0.1, 0.001)
+    assert host.device_status() == 0
+    np.testing.assert_array_equal(hY.numpy().view(np.uint16), Y)
+    np.testing.assert_array_equal(hdX.numpy().view(np.uint16), g["dX"])
+    np.testing.assert_array_equal(dWr.cpu().numpy(), g["dWr"])
+    np.testing.assert_array_equal(dWup_all.cpu().numpy(), g["dWup"])
+    np.testing.assert_array_equal(hstat.numpy(), stat)
+
+
 def test_argument_errors():
     with pytest.raises(M.MoeError):
         M.MoE(64, 100, 4, 2)           # dim not a multiple of 64
