@@ -211,58 +211,79 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
     }
 }
 
-// One thread per token; dlogits doubles as scratch exactly as in moe.cu:213-221.
-__global__ void router_bwd_kernel(const RouteDims d, const RouteBufs b, const float* __restrict__ sw_part, int sw_ld,
-                                  float* __restrict__ s_j, float* __restrict__ dlogits, float aux, float zcoef,
-                                  const int* __restrict__ counts, long n_norm, uint16_t* __restrict__ dl_t, int kw,
-                                  uint16_t* __restrict__ dl_g, int mw) {
-    const long r = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= d.T) return;
+// Router backward through softmax, top-k and renormalisation plus the aux and z terms
+// (moe.cu:200-234, same formulas). Eight lanes per token, lane s owns experts s, s+8, ...; only the K
+// selected experts carry a non-zero renormalisation gradient, so the softmax correction
+// sum_e g_e p_e has K terms and needs no pass over E.
+__global__ void __launch_bounds__(256) router_bwd_kernel(const RouteDims d, const RouteBufs b,
+                                                         const float* __restrict__ sw_part, int sw_ld,
+                                                         float* __restrict__ s_j, float* __restrict__ dlogits, float aux,
+                                                         float zcoef, const int* __restrict__ counts, long n_norm,
+                                                         uint16_t* __restrict__ dl_t, int kw, uint16_t* __restrict__ dl_g,
+                                                         int mw) {
+    const int lane = threadIdx.x & 31;
+    const int s = lane & 7;
+    const unsigned full = 0xffffffffu;
+    const long r = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    const bool valid = r < d.T;
+    const long rr = valid ? r : 0;
     const int E = d.E, K = d.K;
-    const float* probs = b.probs + r * E;
-    float* g = dlogits + r * E;
+    const float* probs = b.probs + rr * E;
     const float nk = (float)(n_norm * K);
     const float nn = (float)n_norm;
-    if (sw_part) {
-        // dH-GEMM partials hold w * dL/dw; one per 256-column tile, added in tile order
-        for (int j = 0; j < K; ++j) {
-            const int slot = b.slot_of[r * K + j];
-            float s = 0.0f;
-            for (int q = 0; q < sw_ld; ++q) s += sw_part[(long)slot * sw_ld + q];
+    // lane j of the group owns selected expert j
+    int my_e = -1; float my_p = 0.0f, my_s = 0.0f;
+    if (s < K) {
+        my_e = b.idx[rr * K + s];
+        my_p = probs[my_e];
+        if (sw_part) {
+            // dH-GEMM partials hold w * dL/dw, one per kEpiCols columns, added in column order
+            const int slot = b.slot_of[rr * K + s];
+            float acc = 0.0f;
+            for (int q = 0; q < sw_ld; ++q) acc += sw_part[(long)slot * sw_ld + q];
             const float wj = b.slotw[slot];
-            s_j[r * K + j] = wj > 0.0f ? s / wj : 0.0f;
+            my_s = wj > 0.0f ? acc / wj : 0.0f;
+            if (valid) s_j[rr * K + s] = my_s;
+        } else {
+            my_s = s_j[rr * K + s];
         }
     }
-    float Z = 0, sp = 0;
-    for (int j = 0; j < K; ++j) {
-        const float p = probs[b.idx[r * K + j]];
-        Z += p; sp += s_j[r * K + j] * p;
+    float Z = 0.0f, sp = 0.0f;
+    int sel_e[8]; float sel_p[8], sel_s[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        sel_e[j] = __shfl_sync(full, my_e, (lane & 24) + j);
+        sel_p[j] = __shfl_sync(full, my_p, (lane & 24) + j);
+        sel_s[j] = __shfl_sync(full, my_s, (lane & 24) + j);
+        if (j < K) { Z += sel_p[j]; sp += sel_s[j] * sel_p[j]; }
     }
     const float Z2 = Z * Z + 1e-12f;
-    for (int e = 0; e < E; ++e) g[e] = 0;
-    for (int j = 0; j < K; ++j) g[b.idx[r * K + j]] = (s_j[r * K + j] * Z - sp) / Z2;
-    float acc = 0;
-    for (int e = 0; e < E; ++e) acc += g[e] * probs[e];
-    float expected = 0;
-    for (int e = 0; e < E; ++e) {
-        g[e] = probs[e] * (g[e] - acc);
-        expected += probs[e] * counts[e] / nk;
-    }
-    const float lse = b.lse[r];
-    for (int e = 0; e < E; ++e) {
-        const float p = probs[e];
-        g[e] += aux * E / nn * p * (counts[e] / nk - expected) + zcoef * 2.f / nn * lse * p;
-    }
-    if (dl_t) {
-        uint16_t* row = dl_t + r * kw;
-        for (int e = 0; e < kw; ++e) row[e] = e < E ? f2bf(g[e]) : (uint16_t)0;
-    }
-    if (dl_g) {
-        const int slot = b.slot_of[r * K];
-        if (slot >= 0 && slot < d.cap) {
-            uint16_t* row = dl_g + (long)slot * mw;
-            for (int e = 0; e < E; ++e) row[e] = f2bf(g[e]);
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < K) { sel_s[j] = (sel_s[j] * Z - sp) / Z2; acc += sel_s[j] * sel_p[j]; }      // sel_s now holds g_sel
+    float expected = 0.0f;
+    for (int e = s; e < E; e += 8) expected += probs[e] * counts[e] / nk;
+    expected += __shfl_xor_sync(full, expected, 1);
+    expected += __shfl_xor_sync(full, expected, 2);
+    expected += __shfl_xor_sync(full, expected, 4);
+    const float lse = b.lse[rr];
+    const int slot0 = b.slot_of[rr * K];
+    const bool slot_ok = slot0 >= 0 && slot0 < d.cap;
+    for (int e = s; e < max(E, kw); e += 8) {
+        float g = 0.0f;
+        if (e < E) {
+            const float p = probs[e];
+            float gs = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) if (j < K && sel_e[j] == e) gs = sel_s[j];
+            g = p * (gs - acc) + aux * E / nn * p * (counts[e] / nk - expected) + zcoef * 2.f / nn * lse * p;
+            if (valid) {
+                dlogits[rr * E + e] = g;
+                if (dl_g && slot_ok) dl_g[(long)slot0 * mw + e] = f2bf(g);
+            }
         }
+        if (valid && dl_t && e < kw) dl_t[rr * kw + e] = e < E ? f2bf(g) : (uint16_t)0;
     }
 }
 
@@ -428,8 +449,8 @@ cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const u
 cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const float* sw_part, int sw_ld, float* s_j,
                               float* dlogits, float aux, float zcoef, const int* counts, long n_norm,
                               uint16_t* dl_t, int kw, uint16_t* dl_g, int mw, cudaStream_t s) {
-    router_bwd_kernel<<<(d.T + 127) / 128, 128, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef, counts, n_norm,
-                                                        dl_t, kw, dl_g, mw);
+    router_bwd_kernel<<<(d.T + 31) / 32, 256, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef, counts, n_norm,
+                                                      dl_t, kw, dl_g, mw);
     return cudaGetLastError();
 }
 

@@ -227,15 +227,15 @@ __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a
     }
 }
 
-// One block. Exclusive scan of the per-block counts per expert, totals, true and padded
-// group starts, tile -> expert table, statistics.
-__global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const RouteBufs b, int NB, int splits) {
-    __shared__ int cnt_s[256];
-    __shared__ int poff_s[257];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+// Scan, part 1: one warp per expert. Exclusive scan of that expert's per-block counts (the base of
+// every router block inside the group), the expert's total and its probability sum; warp 0 of
+// block 0 also reduces the z-loss partials. Fixed orders throughout: results are deterministic.
+__global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, const RouteBufs b, int NB) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const unsigned full = 0xffffffffu;
     const int E = d.E;
-    for (int e = warp; e < E; e += nwarps) {
+    const int e = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (e < E) {
         int running = 0;
         float fs = 0.0f;
         for (int b0 = 0; b0 < NB; b0 += 32) {
@@ -254,25 +254,31 @@ __global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const Rou
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) fs += __shfl_xor_sync(full, fs, o);
         if (lane == 0) {
-            cnt_s[e] = running;
             b.counts[e] = running;
             b.stat[e] = E == 1 ? 0.0f : fs;     // dense shortcut reports no statistics (moe.cu:397-403)
         }
     }
-    if (warp == 0) {
+    if (blockIdx.x == 0 && warp == 0) {
         float z = 0.0f;
         for (int blk = lane; blk < NB; blk += 32) z += b.block_z[blk];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(full, z, o);
         if (lane == 0) b.stat[E] = E == 1 ? 0.0f : z / (float)d.T;
     }
-    __syncthreads();
+}
+
+// Scan, part 2: one block. True and padded group starts (moe.cu:413-419), tile -> expert table,
+// number of tiles in use, split table of the router weight-gradient product.
+__global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, const RouteBufs b, int splits) {
+    __shared__ int poff_s[257];
+    const int E = d.E;
     if (threadIdx.x == 0) {
         int tk = 0, ptk = 0;
         for (int e = 0; e < E; ++e) {
-            b.off[e] = tk; tk += cnt_s[e];
+            const int c = b.counts[e];
+            b.off[e] = tk; tk += c;
             poff_s[e] = ptk; b.poff[e] = ptk;
-            ptk += (cnt_s[e] + d.pad - 1) / d.pad * d.pad;
+            ptk += (c + d.pad - 1) / d.pad * d.pad;
         }
         b.off[E] = tk; poff_s[E] = ptk; b.poff[E] = ptk;
         if (ptk > d.cap) { report(b.status, kErrSlotRange); ptk = 0; }
@@ -284,8 +290,10 @@ __global__ void __launch_bounds__(1024) scan_kernel(const RouteDims d, const Rou
         int e = -1;
         if (i < used) {
             const int row = i * kPad;
-            for (int q = 0; q < E; ++q)
-                if (row >= poff_s[q] && row < poff_s[q + 1]) { e = q; break; }
+            int lo = 0, hi = E;                       // last e with poff[e] <= row
+            while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (poff_s[mid] <= row) lo = mid; else hi = mid; }
+            e = lo;
+            while (e < E && poff_s[e + 1] <= row) ++e;  // skip empty groups that share the start
         }
         b.tile_expert[i] = e;
     }
@@ -325,7 +333,8 @@ cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t
 
 cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s) {
     const int nb = (d.T + kTokBlock - 1) / kTokBlock;
-    scan_kernel<<<1, 1024, 0, s>>>(d, b, nb, splits);
+    scan_columns_kernel<<<(d.E + 7) / 8, 256, 0, s>>>(d, b, nb);
+    scan_finish_kernel<<<1, 256, 0, s>>>(d, b, splits);
     return cudaGetLastError();
 }
 
