@@ -104,9 +104,9 @@ class ClockSampler:
         inside = [p for ts, p in rows if ts is not None and t0 - 0.05 <= ts <= t1 + 0.05]
         if len(inside) >= 2:
             use = inside
-        else:       # region shorter than the sampling period: fall back to everything since warm-up began
-            use = [p for _, p in rows]
-            out["window"] = "warm-up and timed region (timed region shorter than two sampling periods)"
+        else:       # region shorter than two sampling periods: everything from one second before it to its end
+            use = [p for ts, p in rows if ts is not None and t0 - 1.0 <= ts <= t1 + 0.05] or [p for _, p in rows[-3:]]
+            out["window"] = "last second before and during the timed region (region shorter than two sampling periods)"
         if not use:
             return out
         out["samples"] = len(use)
@@ -253,6 +253,9 @@ def main():
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()                        # nvidia-smi needs about a second before its first sample
     local_experts = E // world
     work_stream = torch.cuda.Stream()          # a real stream (not the legacy default), so the decode loop can be graph-captured
     torch.cuda.set_stream(work_stream)
@@ -317,9 +320,6 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()

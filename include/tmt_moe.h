@@ -126,6 +126,12 @@ long long tmt_moe_launch_count(const tmt_moe* h);
  * out; otherwise the first code recorded. Synchronises. */
 int tmt_moe_device_status(tmt_moe* h);
 
+/* Failure-detection self-test (no counterpart in the reference): launches one block that waits on a
+ * barrier nothing arrives on, with the given limit in clock cycles, through the same bounded-wait
+ * routine the GEMM kernels use. Returns 2 (the time-out status code) when the wait ran out, the status
+ * word was set and the kernel returned in order; the context stays usable. -1 on a host error. */
+int tmt_moe_selftest_bounded_wait(tmt_moe* h, long long limit_cycles);
+
 /* ---- NVFP4 expert weights for sampling (no counterpart in the reference) ---------------
  * e2m1 values, one e4m3 scale per 16 consecutive input elements, one fp32 scale per tensor. */
 typedef struct tmt_nvfp4_weight {

@@ -129,6 +129,7 @@ cudaError_t launch_gemm_tcgen05(const GemmParams& p, int num_sms, cudaStream_t s
 cudaError_t launch_gemm_tcgen05_2cta(const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_simt(const GemmParams& p, int max_m_tiles, cudaStream_t stream);
 size_t gemm_tcgen05_smem_bytes();
+cudaError_t launch_bounded_wait_selftest(int* status, long long limit_cycles, int* reached_end, cudaStream_t stream);
 size_t gemm_tcgen05_2cta_smem_bytes();
 
 }  // namespace tmt

@@ -243,6 +243,29 @@ cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
 
 }  // namespace
 
+namespace {
+// One block waits on a barrier nobody arrives on, with a short limit: exercises the time-out path of
+// every bounded wait in the GEMM kernels (status word, abort flag, orderly return) without a real fault.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit, int* reached_end) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_s;
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait_limit(smem_u32(&bar), 0, &abort_s, status, limit);
+    __syncthreads();
+    if (threadIdx.x == 0) *reached_end = ok ? 2 : 1;
+}
+}  // namespace
+
+cudaError_t launch_bounded_wait_selftest(int* status, long long limit_cycles, int* reached_end, cudaStream_t stream) {
+    bounded_wait_selftest_kernel<<<1, 64, 0, stream>>>(status, limit_cycles, reached_end);
+    return cudaGetLastError();
+}
+
 size_t gemm_tcgen05_smem_bytes() { return (size_t)kStages * kStageBytes + 1024; }
 
 cudaError_t launch_gemm_tcgen05(const GemmParams& p, int num_sms, cudaStream_t stream) {

@@ -786,6 +786,23 @@ int tmt_moe_profile(tmt_moe* h, float* ms, long long* count, int reset) {
 int tmt_moe_num_phases(void) { return kNumPhases; }
 const char* tmt_moe_phase_name(int i) { return i >= 0 && i < kNumPhases ? kPhaseNames[i] : ""; }
 
+int tmt_moe_selftest_bounded_wait(tmt_moe* h, long long limit_cycles) {
+    if (!h) { set_error("null handle"); return -1; }
+    int out = -1;
+    try {
+        CK(cudaSetDevice(h->d.device));
+        if (limit_cycles < 1 || limit_cycles > 2000000000LL) throw std::runtime_error("limit_cycles outside [1, 2e9]");
+        int* words = dalloc<int>(h, 2);          // [0] status of this self-test, [1] where the kernel ended
+        CK(cudaMemsetAsync(words, 0, 2 * sizeof(int), h->stream));
+        CK(launch_bounded_wait_selftest(words, limit_cycles, words + 1, h->stream));
+        int host[2] = {-1, -1};
+        CK(cudaMemcpyAsync(host, words, sizeof host, cudaMemcpyDeviceToHost, h->stream));
+        CK(cudaStreamSynchronize(h->stream));
+        out = (host[0] == kErrWaitTimeout && host[1] == 1) ? kErrWaitTimeout : -2 - host[1];
+        return out;
+    } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
+}
+
 long long tmt_moe_launch_count(const tmt_moe* h) { return h ? h->launches : -1; }
 
 int tmt_moe_device_status(tmt_moe* h) {

@@ -25,7 +25,7 @@ EXPORTS = (
     "tmt_moe_launch_count", "tmt_moe_device_status", "tmt_moe_quantize_nvfp4",
     "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init", "tmt_moe_set_profile",
     "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name", "tmt_moe_ep_plan",
-    "tmt_moe_copy_stats",
+    "tmt_moe_copy_stats", "tmt_moe_selftest_bounded_wait", "tmt_moe_router_dw_noalloc",
 )
 
 

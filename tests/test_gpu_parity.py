@@ -3,6 +3,8 @@
 Tolerances (bf16 path, fp32 accumulation): routing (logits, indices, counts, offsets, slots)
 bit-exact; outputs relative L2 <= 1e-2 and max-abs <= 2e-2 * max|ref|; gradients relative L2
 <= 3e-2 per tensor (the reference's own bar, architecture_test.cu:254); aux / z relative 1e-4."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -237,6 +239,19 @@ def test_host_step_equals_device_path():
     np.testing.assert_array_equal(dWr.cpu().numpy(), g["dWr"])
     np.testing.assert_array_equal(dWup_all.cpu().numpy(), g["dWup"])
     np.testing.assert_array_equal(hstat.numpy(), stat)
+
+
+def test_bounded_wait_runs_out_and_context_survives():
+    """Failure detection without a fault: a wait on a barrier nothing signals runs out after its limit,
+    the kernel records the time-out status and returns, and the same handle keeps working."""
+    cfg = dict(T=256, D=128, H=128, E=4, K=2)
+    data = synth.make(cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"], seed=16)
+    layer = G.Layer(data, cfg["T"], cfg["D"], cfg["E"], cfg["K"], cfg["H"], training=False)
+    a = layer.forward().copy()
+    rc = layer.moe.lib.tmt_moe_selftest_bounded_wait(layer.moe.h, ctypes.c_longlong(2_000_000))   # about 1 ms
+    assert rc == 2, (rc, layer.moe.lib.tmt_moe_last_error())
+    assert layer.moe.device_status() == 0          # the handle's own status word is untouched
+    np.testing.assert_array_equal(layer.forward(), a)
 
 
 def test_argument_errors():
