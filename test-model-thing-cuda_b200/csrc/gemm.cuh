@@ -56,6 +56,7 @@ struct GemmParams {
     const uint16_t* P;            // kEpiDh
     float* sw_part; int sw_ld;    // kEpiDh: per-row partial sums, one per kEpiCols columns
     int* status;
+    int dbg;                      // measurement only: bit 0 = no TMA loads (stale operands), bit 1 = no MMAs, bit 2 = no epilogue stores
 };
 
 // One row, kChunk consecutive columns starting at col0 (col0 % 8 == 0). Stores only

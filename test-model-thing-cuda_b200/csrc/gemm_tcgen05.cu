@@ -124,15 +124,17 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
                 for (int kb = 0; kb < ti.nkb; ++kb) {
                     if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
                     const uint32_t fb = smem_u32(&full_bar[s]);
-                    mbar_expect_tx(fb, p.tx_bytes);
+                    mbar_expect_tx(fb, (p.dbg & 1) ? 0u : p.tx_bytes);
                     const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
                     const int k0 = (ti.kb0 + kb) * kBK;
-                    if (p.a_mn) {       // A[k rows][m contiguous]: boxes of 64 m x 64 k
+                    if (p.dbg & 1) {
+                    } else if (p.a_mn) {       // A[k rows][m contiguous]: boxes of 64 m x 64 k
                         for (int j = 0; j < p.a_boxes; ++j) tma_load_2d(sa + j * 8192, ma, fb, ti.row0 + j * p.a_box_step, k0);
                     } else {            // A[rows][k contiguous]: one box of 64 k x 128 rows
                         tma_load_2d(sa, ma, fb, k0, ti.row0);
                     }
-                    if (p.b_mn) {
+                    if (p.dbg & 1) {
+                    } else if (p.b_mn) {
                         for (int j = 0; j < p.b_boxes; ++j) tma_load_2d(sb + j * 8192, mb, fb, ti.col0 + j * p.b_box_step, k0);
                     } else {
                         tma_load_2d(sb, mb, fb, k0, ti.col0);
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
                     const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
-                        tc_mma(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                        if (!(p.dbg & 2)) tc_mma(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
                     tc_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs have read it
                     if (++s == kStages) { s = 0; ph ^= 1; }
                 }
@@ -215,7 +217,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
 #pragma unroll
                     for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
                 }
-                if (row_ok) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
+                if (row_ok && !(p.dbg & 4)) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
             }
             if (EPI == kEpiDh && row_ok && ti.col0 + half * kEpiCols < p.N) p.sw_part[row * p.sw_ld + (ti.col0 + half * kEpiCols) / kEpiCols] = sw;
             tc_fence_before();

@@ -172,15 +172,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                     if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
                     const uint32_t fb_local = smem_u32(&full_bar[s]);
                     const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
-                    if (leader) mbar_expect_tx(fb_local, 2 * p.tx_bytes);      // both CTAs' bytes
+                    if (leader) mbar_expect_tx(fb_local, (p.dbg & 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
                     const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
                     const int k0 = (ti.kb0 + kb) * kBK;
-                    if (p.a_mn) {
+                    if (p.dbg & 1) {
+                    } else if (p.a_mn) {
                         for (int j = 0; j < p.a_boxes; ++j) tma_load_2d_pair(sa + j * 8192, ma, fb, ti.row0 + j * p.a_box_step, k0);
                     } else {
                         tma_load_2d_pair(sa, ma, fb, k0, ti.row0);
                     }
-                    if (p.b_mn) {
+                    if (p.dbg & 1) {
+                    } else if (p.b_mn) {
                         for (int j = 0; j < p.b_boxes; ++j) tma_load_2d_pair(sb + j * 8192, mb, fb, bcol0 + j * p.b_box_step, k0);
                     } else {
                         tma_load_2d_pair(sb, mb, fb, k0, bcol0);
@@ -224,7 +226,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                     const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
-                        tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                        if (!(p.dbg & 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
                     tc_commit_pair(smem_u32(&empty_bar[s]));
                     if (++s == kStages2) { s = 0; ph ^= 1; }
                 }
@@ -265,7 +267,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
 #pragma unroll
                     for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
                 }
-                if (row_ok) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
+                if (row_ok && !(p.dbg & 4)) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
             }
             if (EPI == kEpiDh && row_ok && ti.col0 + half * kEpiCols < p.N) p.sw_part[row * p.sw_ld + (ti.col0 + half * kEpiCols) / kEpiCols] = sw;
             tc_fence_before();

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <stdexcept>
@@ -169,6 +170,7 @@ GemmParams base_params(tmt_moe* h) {
     p.poff = h->g_poff;
     p.status = h->rb.status;
     p.a_boxes = 1; p.b_boxes = 1; p.a_box_step = 64; p.b_box_step = 64;
+    p.dbg = h->gemm_dbg;
     return p;
 }
 
@@ -484,6 +486,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     if (d.gemm_impl < 0 || d.gemm_impl > 2) throw std::runtime_error("unknown gemm_impl");
     h->tensor_core = d.gemm_impl != TMT_MOE_GEMM_SIMT;
     h->two_cta = d.gemm_impl == TMT_MOE_GEMM_TCGEN05_2CTA;
+    if (const char* dbg = getenv("TMT_MOE_GEMM_DEBUG")) h->gemm_dbg = atoi(dbg);     // measurement only, results are then wrong
     h->pad = h->two_cta ? 2 * kPad : kPad;
     const int pad = h->pad;
     // rows of the grouped buffers: every assignment plus up to pad-1 pad rows per expert (moe.cu:331)

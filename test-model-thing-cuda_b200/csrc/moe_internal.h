@@ -41,7 +41,7 @@ struct tmt_moe {
     // layout tables the grouped GEMMs run on: the token-side tables on one GPU, the expert-side ones under EP
     const int* g_poff = nullptr; const int* g_num_m_tiles = nullptr; const int* g_tile_expert = nullptr; int g_max_tiles = 0;
     long gcap = 0;      // rows of the grouped GEMM buffers
-    bool two_cta = false; bool tensor_core = true;
+    bool two_cta = false; bool tensor_core = true; int gemm_dbg = 0;
     int pad = 128;      // group padding (rows)
     int x_cap = 0;
     float* bias = nullptr;
