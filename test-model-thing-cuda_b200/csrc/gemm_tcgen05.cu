@@ -24,7 +24,7 @@ constexpr int kStageBytes = kATile + kBTile;
 template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiDh ? 8 : 4; }
 template <int EPI> __host__ __device__ constexpr int block_threads() { return 64 + 32 * epi_warps<EPI>(); }
 constexpr uint32_t kTmemCols = 512;     // two fp32 accumulators of 256 columns
-constexpr int kPrefetch = 0;            // k blocks an L2 prefetch would run ahead of the loads: measured harmful (the TMA unit is the limiter), off
+constexpr int kStagingBytes = 128 * 128;  // one staged output chunk: 128 rows x 128 bytes (64 bf16 or 32 fp32 columns)
 
 using namespace tc;
 
@@ -58,7 +58,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int m_tiles
 template <int EPI>
 __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tfull_bar[2], tempty_bar[2];
+    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tfull_bar[2], tempty_bar[2], group_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; ++a) mbar_init(smem_u32(&group_bar[a]), 4);      // 4 epilogue warps meet here
         for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 1 * epi_warps<EPI>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -87,71 +88,56 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
     if (p.mode == kRowsRagged) m_tiles = *p.num_m_tiles; else m_tiles = (p.M + kBM - 1) / kBM;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---------------- TMA producer ----------------
-            int s = 0; uint32_t ph = 0;
-            uint32_t issued = 0;           // bit s set once stage s has received a load
-            uint32_t last_parity = 0;      // parity of the last load issued into stage s
-            bool ok = true;
-            // L2 prefetch cursor: runs kPrefetch k blocks ahead of the loads (across tile boundaries), so
-            // that a stage's boxes are L2 hits by the time they are fetched into shared memory
-            int pt = blockIdx.x, pkb = 0;
-            TileInfo pti;
-            bool pvalid = get_tile(p, pt, m_tiles, n_tiles, pti);
-            auto prefetch_next = [&]() {
-                while (pvalid && pkb >= pti.nkb) { pt += gridDim.x; pkb = 0; pvalid = get_tile(p, pt, m_tiles, n_tiles, pti); }
-                if (!pvalid) return;
-                const CUtensorMap* ma = p.mapA + (size_t)pti.expert * p.a_stride;
-                const CUtensorMap* mb = p.mapB + (size_t)pti.expert * p.b_stride;
-                const int k0 = (pti.kb0 + pkb) * kBK;
-                if (p.a_mn) { for (int j = 0; j < p.a_boxes; ++j) tma_prefetch_2d(ma, pti.row0 + j * p.a_box_step, k0); }
-                else tma_prefetch_2d(ma, k0, pti.row0);
-                if (p.b_mn) { for (int j = 0; j < p.b_boxes; ++j) tma_prefetch_2d(mb, pti.col0 + j * p.b_box_step, k0); }
-                else tma_prefetch_2d(mb, k0, pti.col0);
-                ++pkb;
-            };
-            for (int i = 0; i < kPrefetch; ++i) prefetch_next();
-            for (int t = blockIdx.x; ok; t += gridDim.x) {
-                TileInfo ti;
-                if (!get_tile(p, t, m_tiles, n_tiles, ti)) {
-                    if (p.mode == kRowsRagged && t < m_tiles * n_tiles) report(p.status, kErrSlotRange);
-                    break;
-                }
-                const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
-                const CUtensorMap* mb = p.mapB + (size_t)ti.expert * p.b_stride;
-                tensormap_acquire(ma);
-                tensormap_acquire(mb);
-                for (int kb = 0; kb < ti.nkb; ++kb) {
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-                    const uint32_t fb = smem_u32(&full_bar[s]);
-                    mbar_expect_tx(fb, (p.dbg & 1) ? 0u : p.tx_bytes);
-                    const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
-                    const int k0 = (ti.kb0 + kb) * kBK;
-                    if (p.dbg & 1) {
-                    } else if (p.a_mn) {       // A[k rows][m contiguous]: boxes of 64 m x 64 k
-                        for (int j = 0; j < p.a_boxes; ++j) tma_load_2d(sa + j * 8192, ma, fb, ti.row0 + j * p.a_box_step, k0);
-                    } else {            // A[rows][k contiguous]: one box of 64 k x 128 rows
-                        tma_load_2d(sa, ma, fb, k0, ti.row0);
-                    }
-                    if (p.dbg & 1) {
-                    } else if (p.b_mn) {
-                        for (int j = 0; j < p.b_boxes; ++j) tma_load_2d(sb + j * 8192, mb, fb, ti.col0 + j * p.b_box_step, k0);
-                    } else {
-                        tma_load_2d(sb, mb, fb, k0, ti.col0);
-                    }
-                    if (kPrefetch > 0) prefetch_next();
-                    issued |= 1u << s;
-                    last_parity = (last_parity & ~(1u << s)) | (ph << s);
-                    if (++s == kStages) { s = 0; ph ^= 1; }
-                }
+        // ---------------- TMA producer: lane 0 owns the barriers, lanes 0..n-1 each issue one box ----------------
+        // (a single thread issuing 6 boxes per k block was measured to be the slowest part of the launches with
+        // mn-major operands)
+        int s = 0; uint32_t ph = 0;
+        uint32_t issued = 0;           // bit s set once stage s has received a load
+        uint32_t last_parity = 0;      // parity of the last load issued into stage s
+        bool ok = true;
+        const int a_n = p.a_mn ? p.a_boxes : 1, b_n = p.b_mn ? p.b_boxes : 1;
+        for (int t = blockIdx.x; ok; t += gridDim.x) {
+            TileInfo ti;
+            if (!get_tile(p, t, m_tiles, n_tiles, ti)) {
+                if (lane == 0 && p.mode == kRowsRagged && t < m_tiles * n_tiles) report(p.status, kErrSlotRange);
+                break;
             }
-            if (!ok) {
-                // aborting: wait (bounded, no abort short-cut) until the copies already issued have landed
-                for (int q = 0; q < kStages; ++q) {
-                    if (!(issued >> q & 1)) continue;
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
+            const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
+            const CUtensorMap* mb = p.mapB + (size_t)ti.expert * p.b_stride;
+            if (lane == 0) { tensormap_acquire(ma); tensormap_acquire(mb); }
+            __syncwarp();
+            for (int kb = 0; kb < ti.nkb; ++kb) {
+                const uint32_t fb = smem_u32(&full_bar[s]);
+                if (lane == 0) {
+                    ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status);
+                    if (ok) mbar_expect_tx(fb, (p.dbg & 1) ? 0u : p.tx_bytes);
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
+                const int k0 = (ti.kb0 + kb) * kBK;
+                if (!(p.dbg & 1)) {
+                    if (lane < a_n) {
+                        if (p.a_mn) tma_load_2d(sa + lane * 8192, ma, fb, ti.row0 + lane * p.a_box_step, k0);   // 64 m x 64 k
+                        else tma_load_2d(sa, ma, fb, k0, ti.row0);                                              // 64 k x 128 rows
+                    } else if (lane < a_n + b_n) {
+                        const int j = lane - a_n;
+                        if (p.b_mn) tma_load_2d(sb + j * 8192, mb, fb, ti.col0 + j * p.b_box_step, k0);
+                        else tma_load_2d(sb, mb, fb, k0, ti.col0);
+                    }
+                }
+                __syncwarp();
+                issued |= 1u << s;
+                last_parity = (last_parity & ~(1u << s)) | (ph << s);
+                if (++s == kStages) { s = 0; ph ^= 1; }
+            }
+        }
+        if (!ok && lane == 0) {
+            // aborting: wait (bounded, no abort short-cut) until the copies already issued have landed
+            for (int q = 0; q < kStages; ++q) {
+                if (!(issued >> q & 1)) continue;
+                const long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
             }
         }
         __syncwarp();
@@ -190,12 +176,29 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        // ---------------- epilogue: TMEM -> registers -> (shared memory -> TMA store | global) ----------------
         const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
-        constexpr int kWarpCols = kBN / (epi_warps<EPI>() / 4);      // columns of the tile this warp drains
+        constexpr int kGroups = epi_warps<EPI>() / 4;                // 4 warps form a group with its own staging buffer(s)
+        constexpr int kWarpCols = kBN / kGroups;                     // columns of the tile one group drains
         const int half = (warp - 2) >> 2;
+        const bool staged = p.mapC0 != nullptr && !(p.dbg & 8);     // bit 3 of the measurement switches: per-thread-row global stores
+        const bool issuer = ((warp - 2) & 3) == 0 && lane == 0;      // one thread per group issues the TMA stores
+        const uint32_t cbuf = tiles_s + kStages * kStageBytes;       // two staging buffers of kStagingBytes
+        const uint32_t gbar = smem_u32(&group_bar[half]);
+        uint32_t gphase = 0;
+        int use = 0;
+        // group-wide meeting point with the same bounded wait as everything else (a hardware barrier could not
+        // be left if a warp of the group had given up)
+        auto group_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(gbar);
+            const bool ok = mbar_wait(gbar, gphase, abort_flag, p.status);
+            gphase ^= 1;
+            return __all_sync(0xffffffffu, ok);
+        };
         int acc = 0; uint32_t acc_ph = 0;
-        for (int t = blockIdx.x;; t += gridDim.x) {
+        bool alive = true;
+        for (int t = blockIdx.x; alive; t += gridDim.x) {
             TileInfo ti;
             if (!get_tile(p, t, m_tiles, n_tiles, ti)) break;
             bool ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);
@@ -205,19 +208,85 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
             const int r_in_tile = quarter * 32 + lane;
             const long row = (long)ti.row0 + r_in_tile;
             const bool row_ok = (p.mode == kRowsRagged) || (row < p.M);
+            const uint32_t tm = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kBN);
             float sw = 0.0f;
+            if (staged) {
+                constexpr bool kF32 = EPI == kEpiF32;
+                constexpr int kCols = kF32 ? 32 : 64;                 // columns per staged chunk: 128 bytes per row
+                const bool two = EPI == kEpiUp && p.mapC1 != nullptr;
+                const CUtensorMap* m0 = p.mapC0 + (size_t)ti.expert * p.c_stride;
+                const CUtensorMap* m1 = two ? p.mapC1 + (size_t)ti.expert * p.c_stride : nullptr;
+                const uint32_t rsw = (uint32_t)(r_in_tile & 7);
 #pragma unroll 1
-            for (int c = half * (kWarpCols / kChunk); c < (half + 1) * (kWarpCols / kChunk); ++c) {
-                const int col0 = ti.col0 + c * kChunk;
-                if (col0 >= p.N) break;
-                float v[kChunk];
-                if (ti.nkb > 0) {
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kBN + c * kChunk), v);
-                } else {
+                for (int cc = half * (kWarpCols / kCols); cc < (half + 1) * (kWarpCols / kCols); ++cc) {
+                    const int ccol0 = ti.col0 + cc * kCols;
+                    if (ccol0 >= p.N) break;
+                    // buffer choice: two outputs or two groups -> one buffer each, reused every chunk; else alternate
+                    const bool single = (EPI == kEpiUp) || kGroups == 2;
+                    const uint32_t b0 = cbuf + (uint32_t)((EPI == kEpiUp) ? 0 : (kGroups == 2 ? half : (use & 1))) * kStagingBytes;
+                    const uint32_t b1 = cbuf + kStagingBytes;
+                    if (issuer) { if (single) bulk_wait_read<0>(); else bulk_wait_read<1>(); }
+                    if (!group_sync()) { alive = false; break; }
+                    const uint32_t rbase = (uint32_t)r_in_tile * 128u;
+                    if constexpr (kF32) {
+                        float v[kChunk];
+                        if (ti.nkb > 0) tmem_ld32(tm + (uint32_t)(cc * kCols), v);
+                        else {
 #pragma unroll
-                    for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+                            for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+                        }
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            st_shared16(b0 + rbase + (((uint32_t)q ^ rsw) << 4), __float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
+                                        __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+                    } else {
+#pragma unroll
+                        for (int sub = 0; sub < 2; ++sub) {
+                            const int col0 = ccol0 + sub * kChunk;
+                            float v[kChunk];
+                            uint32_t w0[kChunk / 2], w1[kChunk / 2];
+                            if (ti.nkb > 0) tmem_ld32(tm + (uint32_t)(cc * kCols + sub * kChunk), v);
+                            else {
+#pragma unroll
+                                for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+                            }
+                            if (col0 < p.N && row_ok) epilogue_math<EPI>(p, ti.expert, row, col0, v, w0, w1, sw);
+                            else {
+#pragma unroll
+                                for (int i = 0; i < kChunk / 2; ++i) { w0[i] = 0; w1[i] = 0; }
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint32_t off = rbase + ((((uint32_t)(sub * 4 + q)) ^ rsw) << 4);
+                                st_shared16(b0 + off, w0[4 * q], w0[4 * q + 1], w0[4 * q + 2], w0[4 * q + 3]);
+                                if (two) st_shared16(b1 + off, w1[4 * q], w1[4 * q + 1], w1[4 * q + 2], w1[4 * q + 3]);
+                            }
+                        }
+                    }
+                    fence_async_smem();
+                    if (!group_sync()) { alive = false; break; }
+                    if (issuer && !(p.dbg & 4)) {
+                        tma_store_2d(m0, b0, ccol0, ti.row0);
+                        if (two) tma_store_2d(m1, b1, ccol0, ti.row0);
+                        bulk_commit();
+                    }
+                    ++use;
                 }
-                if (row_ok && !(p.dbg & 4)) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
+                if (!alive) break;
+            } else {
+#pragma unroll 1
+                for (int c = half * (kWarpCols / kChunk); c < (half + 1) * (kWarpCols / kChunk); ++c) {
+                    const int col0 = ti.col0 + c * kChunk;
+                    if (col0 >= p.N) break;
+                    float v[kChunk];
+                    if (ti.nkb > 0) {
+                        tmem_ld32(tm + (uint32_t)(c * kChunk), v);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
+                    }
+                    if (row_ok && !(p.dbg & 4)) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
+                }
             }
             if (EPI == kEpiDh && row_ok && ti.col0 + half * kEpiCols < p.N) p.sw_part[row * p.sw_ld + (ti.col0 + half * kEpiCols) / kEpiCols] = sw;
             tc_fence_before();
@@ -225,6 +294,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+        if (staged && issuer) bulk_wait_all();      // the shared-memory sources and the global writes of this CTA are done
     }
     tc_fence_before();
     __syncthreads();
@@ -268,7 +338,7 @@ cudaError_t launch_bounded_wait_selftest(int* status, long long limit_cycles, in
     return cudaGetLastError();
 }
 
-size_t gemm_tcgen05_smem_bytes() { return (size_t)kStages * kStageBytes + 1024; }
+size_t gemm_tcgen05_smem_bytes() { return (size_t)kStages * kStageBytes + 2 * kStagingBytes + 1024; }
 
 cudaError_t launch_gemm_tcgen05(const GemmParams& p, int num_sms, cudaStream_t stream) {
     // persistent: one CTA per SM (the shared-memory footprint allows no second one)

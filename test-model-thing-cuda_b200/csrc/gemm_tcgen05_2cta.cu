@@ -22,7 +22,6 @@ namespace {
 using namespace tc;
 
 constexpr int kStages2 = 7;
-constexpr int kPrefetch2 = 0;           // L2 prefetch distance in k blocks: measured harmful (the TMA unit is the limiter), off
 constexpr int kATile2 = kBM * kBK * 2;          // 16 KB: this CTA's 128 rows
 constexpr int kBTile2 = (kBN / 2) * kBK * 2;    // 16 KB: this CTA's 128 of the 256 columns
 constexpr int kStageBytes2 = kATile2 + kBTile2;
@@ -135,71 +134,55 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---------------- TMA producer (both CTAs) ----------------
-            int s = 0; uint32_t ph = 0;
-            uint32_t issued = 0, last_parity = 0;
-            bool ok = true;
-            // L2 prefetch cursor, kPrefetch2 k blocks ahead of the loads (across tile boundaries)
-            int pt = pair, pkb = 0;
-            Tile2 pti;
-            bool pvalid = get_tile2(p, pt, m_pairs, n_tiles, rank, pti);
-            auto prefetch_next = [&]() {
-                while (pvalid && pkb >= pti.nkb) { pt += npairs; pkb = 0; pvalid = get_tile2(p, pt, m_pairs, n_tiles, rank, pti); }
-                if (!pvalid) return;
-                const CUtensorMap* ma = p.mapA + (size_t)pti.expert * p.a_stride;
-                const CUtensorMap* mb = p.mapB + (size_t)pti.expert * p.b_stride;
-                const int k0 = (pti.kb0 + pkb) * kBK, bc = pti.col0 + rank * (kBN / 2);
-                if (p.a_mn) { for (int j = 0; j < p.a_boxes; ++j) tma_prefetch_2d(ma, pti.row0 + j * p.a_box_step, k0); }
-                else tma_prefetch_2d(ma, k0, pti.row0);
-                if (p.b_mn) { for (int j = 0; j < p.b_boxes; ++j) tma_prefetch_2d(mb, bc + j * p.b_box_step, k0); }
-                else tma_prefetch_2d(mb, k0, bc);
-                ++pkb;
-            };
-            for (int i = 0; i < kPrefetch2; ++i) prefetch_next();
-            for (int t = pair; ok; t += npairs) {
-                Tile2 ti;
-                if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) {
-                    if (p.mode == kRowsRagged && t < m_pairs * n_tiles) report(p.status, kErrSlotRange);
-                    break;
-                }
-                const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
-                const CUtensorMap* mb = p.mapB + (size_t)ti.expert * p.b_stride;
-                tensormap_acquire(ma);
-                tensormap_acquire(mb);
-                const int bcol0 = ti.col0 + rank * (kBN / 2);
-                for (int kb = 0; kb < ti.nkb; ++kb) {
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-                    const uint32_t fb_local = smem_u32(&full_bar[s]);
-                    const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
-                    if (leader) mbar_expect_tx(fb_local, (p.dbg & 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
-                    const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
-                    const int k0 = (ti.kb0 + kb) * kBK;
-                    if (p.dbg & 1) {
-                    } else if (p.a_mn) {
-                        for (int j = 0; j < p.a_boxes; ++j) tma_load_2d_pair(sa + j * 8192, ma, fb, ti.row0 + j * p.a_box_step, k0);
-                    } else {
-                        tma_load_2d_pair(sa, ma, fb, k0, ti.row0);
-                    }
-                    if (p.dbg & 1) {
-                    } else if (p.b_mn) {
-                        for (int j = 0; j < p.b_boxes; ++j) tma_load_2d_pair(sb + j * 8192, mb, fb, bcol0 + j * p.b_box_step, k0);
-                    } else {
-                        tma_load_2d_pair(sb, mb, fb, k0, bcol0);
-                    }
-                    if (kPrefetch2 > 0) prefetch_next();
-                    issued |= 1u << s;
-                    last_parity = (last_parity & ~(1u << s)) | (ph << s);
-                    if (++s == kStages2) { s = 0; ph ^= 1; }
-                }
+        // ---------------- TMA producer (both CTAs): lane 0 owns the barriers, lanes 0..n-1 each issue one box ----------------
+        int s = 0; uint32_t ph = 0;
+        uint32_t issued = 0, last_parity = 0;
+        bool ok = true;
+        const int a_n = p.a_mn ? p.a_boxes : 1, b_n = p.b_mn ? p.b_boxes : 1;
+        for (int t = pair; ok; t += npairs) {
+            Tile2 ti;
+            if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) {
+                if (lane == 0 && p.mode == kRowsRagged && t < m_pairs * n_tiles) report(p.status, kErrSlotRange);
+                break;
             }
-            if (!ok && leader) {
-                // aborting: the leader's barriers count both CTAs' copies; wait (bounded) for what was announced
-                for (int q = 0; q < kStages2; ++q) {
-                    if (!(issued >> q & 1)) continue;
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
+            const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
+            const CUtensorMap* mb = p.mapB + (size_t)ti.expert * p.b_stride;
+            if (lane == 0) { tensormap_acquire(ma); tensormap_acquire(mb); }
+            __syncwarp();
+            const int bcol0 = ti.col0 + rank * (kBN / 2);
+            for (int kb = 0; kb < ti.nkb; ++kb) {
+                const uint32_t fb_local = smem_u32(&full_bar[s]);
+                const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
+                if (lane == 0) {
+                    ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status);
+                    if (ok && leader) mbar_expect_tx(fb_local, (p.dbg & 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
+                const int k0 = (ti.kb0 + kb) * kBK;
+                if (!(p.dbg & 1)) {
+                    if (lane < a_n) {
+                        if (p.a_mn) tma_load_2d_pair(sa + lane * 8192, ma, fb, ti.row0 + lane * p.a_box_step, k0);
+                        else tma_load_2d_pair(sa, ma, fb, k0, ti.row0);
+                    } else if (lane < a_n + b_n) {
+                        const int j = lane - a_n;
+                        if (p.b_mn) tma_load_2d_pair(sb + j * 8192, mb, fb, bcol0 + j * p.b_box_step, k0);
+                        else tma_load_2d_pair(sb, mb, fb, k0, bcol0);
+                    }
+                }
+                __syncwarp();
+                issued |= 1u << s;
+                last_parity = (last_parity & ~(1u << s)) | (ph << s);
+                if (++s == kStages2) { s = 0; ph ^= 1; }
+            }
+        }
+        if (!ok && leader && lane == 0) {
+            // aborting: the leader's barriers count both CTAs' copies; wait (bounded) for what was announced
+            for (int q = 0; q < kStages2; ++q) {
+                if (!(issued >> q & 1)) continue;
+                const long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
             }
         }
         __syncwarp();

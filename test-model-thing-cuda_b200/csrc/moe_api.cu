@@ -52,6 +52,18 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// 2-D tensor of 2-byte (bf16) or 4-byte (fp32) elements, 128-byte swizzle: the output side of the GEMMs.
+void make_out_map(CUtensorMap* m, const void* base, bool f32, uint64_t inner, uint64_t rows) {
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {inner * (f32 ? 4u : 2u)};
+    cuuint32_t box[2] = {f32 ? 32u : 64u, 128u};         // 128 bytes x 128 rows
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed for an output map (" + std::to_string((int)r) + ")");
+}
+
 // 2-D bf16 tensor, `inner` contiguous elements per row, 128-byte swizzle, zero fill.
 void make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows) {
     cuuint64_t dims[2] = {inner, rows};
@@ -88,7 +100,8 @@ T* dalloc(tmt_moe* h, size_t n) {
     return reinterpret_cast<T*>(p);
 }
 
-enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kDlgMN, kDltK, kXsMN, kDltMN, kNumActMaps };
+enum ActMap { kXgK = 0, kHactK, kDYgK, kDPK, kDYgMN, kHactMN, kDPMN, kXgMN, kDlgMN, kDltK, kXsMN, kDltMN,
+              kOutP, kOutHact, kOutYg, kOutDP, kOutDXg, kOutDXr, kOutSplit0, kNumActMaps = kOutSplit0 + kMaxSplits };
 enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };   // one more map follows the 4*E weight maps: the router, mn-major
 
 void build_act_maps(tmt_moe* h) {
@@ -104,6 +117,17 @@ void build_act_maps(tmt_moe* h) {
         make_map(&m[kDPK], h->dP, H, cap, 64, 128);
         make_map(&m[kHactMN], h->Hact, H, cap, 64, 64);
         make_map(&m[kDPMN], h->dP, H, cap, 64, 64);
+    }
+    make_out_map(&m[kOutYg], h->Yg, false, D, cap);
+    if (h->dXg) make_out_map(&m[kOutDXg], h->dXg, false, D, cap);
+    if (H > 0) {
+        make_out_map(&m[kOutHact], h->Hact, false, H, cap);
+        if (h->P) make_out_map(&m[kOutP], h->P, false, H, cap);
+        if (h->d.training) make_out_map(&m[kOutDP], h->dP, false, H, cap);
+    }
+    if (h->dXr) {
+        make_out_map(&m[kOutDXr], h->dXr, false, D, (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad);
+        for (int i = 0; i < h->splits; ++i) make_out_map(&m[kOutSplit0 + i], h->dwr_partial + (size_t)i * h->mw * D, true, D, h->mw);
     }
     if (h->dl_g) {
         make_map(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, 64, 64);
@@ -155,6 +179,20 @@ void refresh_grads(tmt_moe* h, float* const* dWup, float* const* dWdown) {
         if (!dWup[e] || (two && !dWdown[e])) throw std::runtime_error("null expert gradient pointer");
     h->gup_seen.assign(dWup, dWup + E);
     CK(cudaMemcpyAsync(h->gup_ptrs, dWup, E * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
+    if (h->tensor_core) {
+        const uint64_t D = h->d.dim, H = h->d.hidden;
+        std::vector<CUtensorMap> m((size_t)2 * E);
+        memset(m.data(), 0, m.size() * sizeof(CUtensorMap));
+        for (int e = 0; e < E; ++e) {
+            if (two) {
+                make_out_map(&m[e], dWup[e], true, D, H);              // dWup[e]: H x D
+                make_out_map(&m[E + e], dWdown[e], true, H, D);        // dWdown[e]: D x H
+            } else {
+                make_out_map(&m[e], dWup[e], true, D, D);
+            }
+        }
+        CK(cudaMemcpyAsync(h->g_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+    }
     if (two) {
         h->gdown_seen.assign(dWdown, dWdown + E);
         CK(cudaMemcpyAsync(h->gdown_ptrs, dWdown, E * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
@@ -285,11 +323,13 @@ void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown
         GemmParams up = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, H, D, kEpiUp);
         up.out0 = h->d.training ? h->P : nullptr;
         up.out1 = h->Hact;
+        up.mapC0 = h->act_maps + kOutHact; up.mapC1 = h->d.training ? h->act_maps + kOutP : nullptr;
         if (h->q_expert_scales) up.expert_scale = h->q_scales;
         prof_mark(h, kPhGemmUp);
         run_gemm(h, up);
         GemmParams down = rows_gemm(h, kHactK, h->Hact, kDownK, h->down_ptrs, false, D, H, gate_in_epilogue ? kEpiDown : kEpiBf16);
         down.out0 = h->Yg;
+        down.mapC0 = h->act_maps + kOutYg;
         down.row_scale = h->rb.slotw;
         if (h->q_expert_scales) down.expert_scale = h->q_scales + h->d.experts;
         prof_mark(h, kPhGemmDown);
@@ -297,6 +337,7 @@ void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown
     } else {
         GemmParams g = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, D, D, kEpiBf16);
         g.out0 = h->Yg;
+        g.mapC0 = h->act_maps + kOutYg;
         prof_mark(h, kPhGemmUp);
         run_gemm(h, g);
     }
@@ -327,21 +368,30 @@ void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdow
     if (H > 0) {
         GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
         dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
+        dh.mapC0 = h->act_maps + kOutDP;
         prof_mark(h, kPhGemmDh);
         run_gemm(h, dh);
         prof_mark(h, kPhGemmDwDown);
-        run_gemm(h, red_gemm(h, kDYgMN, h->dYg, D, kHactMN, h->Hact, H, h->gdown_ptrs));
+        GemmParams gd = red_gemm(h, kDYgMN, h->dYg, D, kHactMN, h->Hact, H, h->gdown_ptrs);
+        gd.mapC0 = h->g_maps + h->local_experts; gd.c_stride = 1;
+        run_gemm(h, gd);
         prof_mark(h, kPhGemmDwUp);
-        run_gemm(h, red_gemm(h, kDPMN, h->dP, H, kXgMN, h->Xg, D, h->gup_ptrs));
+        GemmParams gu = red_gemm(h, kDPMN, h->dP, H, kXgMN, h->Xg, D, h->gup_ptrs);
+        gu.mapC0 = h->g_maps; gu.c_stride = 1;
+        run_gemm(h, gu);
         GemmParams dx = rows_gemm(h, kDPK, h->dP, kUpMN, h->up_ptrs, true, D, H, kEpiBf16);
         dx.out0 = h->dXg;
+        dx.mapC0 = h->act_maps + kOutDXg;
         prof_mark(h, kPhGemmDx);
         run_gemm(h, dx);
     } else {
         prof_mark(h, kPhGemmDwUp);
-        run_gemm(h, red_gemm(h, kDYgMN, h->dYg, D, kXgMN, h->Xg, D, h->gup_ptrs));
+        GemmParams gu = red_gemm(h, kDYgMN, h->dYg, D, kXgMN, h->Xg, D, h->gup_ptrs);
+        gu.mapC0 = h->g_maps; gu.c_stride = 1;
+        run_gemm(h, gu);
         GemmParams dx = rows_gemm(h, kDYgK, h->dYg, kUpMN, h->up_ptrs, true, D, D, kEpiBf16);
         dx.out0 = h->dXg;
+        dx.mapC0 = h->act_maps + kOutDXg;
         prof_mark(h, kPhGemmDx);
         run_gemm(h, dx);
     }
@@ -440,6 +490,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.tx_bytes = (p.a_boxes + p.b_boxes) * 8192;
         p.M = h->mw; p.N = D; p.experts = h->splits; p.poff = tok_order ? h->tok_split_poff : h->rb.split_poff;
         p.epi = kEpiF32; p.outF = h->dwr_part_ptrs; p.ldc = D;
+        p.mapC0 = h->act_maps + kOutSplit0; p.c_stride = 1;
         run_tc(h, p);
         CK(launch_reduce_parts(h->dwr_partial, h->splits, h->mw, E, D, dWr, h->stream));
         h->launches += 2;
@@ -456,6 +507,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.N = D; p.K = h->kw; p.experts = 1;
         p.tile_expert = h->plain_tiles; p.num_m_tiles = h->plain_num;
         p.epi = kEpiBf16; p.out0 = h->dXr; p.ldc = D;
+        p.mapC0 = h->act_maps + kOutDXr;
         run_tc(h, p);
         CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream, pm));
         h->launches += 2;
@@ -573,6 +625,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->down_ptrs = dalloc<const uint16_t*>(h, h->local_experts);
     h->gup_ptrs = dalloc<float*>(h, h->local_experts);
     h->gdown_ptrs = dalloc<float*>(h, h->local_experts);
+    h->g_maps = dalloc<CUtensorMap>(h, (size_t)2 * h->local_experts);
     h->g_poff = b.poff; h->g_num_m_tiles = b.num_m_tiles; h->g_tile_expert = b.tile_expert; h->g_max_tiles = h->dims.max_tiles;
     if (h->tensor_core) build_act_maps(h);
     if (d.host_io) {

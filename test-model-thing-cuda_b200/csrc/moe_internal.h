@@ -66,6 +66,7 @@ struct tmt_moe {
     CUtensorMap* w_maps = nullptr;
     const uint16_t** up_ptrs = nullptr; const uint16_t** down_ptrs = nullptr;
     float** gup_ptrs = nullptr; float** gdown_ptrs = nullptr;
+    CUtensorMap* g_maps = nullptr;      // [2][local experts] fp32 output maps of the weight gradients
     std::vector<const void*> up_seen, down_seen;
     std::vector<float*> gup_seen, gdown_seen;
     // staging for the host-buffer entry point
