@@ -255,7 +255,7 @@ void run_gemm(tmt_moe* h, const GemmParams& p) {
 
 const char* const kPhaseNames[kNumPhases] = {
     "router", "scan", "dispatch", "gemm_up", "gemm_down", "combine", "grad_dispatch", "gemm_dh", "gemm_dwdown",
-    "gemm_dwup", "gemm_dx", "router_bwd", "router_dw", "scatter", "exchange"};
+    "gemm_dwup", "gemm_dx", "router_bwd", "router_dw", "router_dx", "scatter", "exchange"};
 
 void prof_collect(tmt_moe* h) {
     Profiler& pr = h->prof;
@@ -495,7 +495,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         CK(launch_reduce_parts(h->dwr_partial, h->splits, h->mw, E, D, dWr, h->stream));
         h->launches += 2;
     }
-    prof_mark(h, kPhScatter);
+    prof_mark(h, kPhRouterDx);
     {   // dXr = dl_t * Wr (one k block per 64 experts), then dX = dXr + sum_j dXg[slot_j]
         GemmParams p = base_params(h);
         p.mode = kRowsRagged;
@@ -509,6 +509,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.epi = kEpiBf16; p.out0 = h->dXr; p.ldc = D;
         p.mapC0 = h->act_maps + kOutDXr;
         run_tc(h, p);
+        prof_mark(h, kPhScatter);
         CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream, pm));
         h->launches += 2;
     }

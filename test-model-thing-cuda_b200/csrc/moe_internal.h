@@ -18,7 +18,7 @@ namespace tmt {
 // (the reference's TMT_PROFILE phases, tmt-cuda/src/moe.cu:380-394, at kernel granularity).
 enum Phase : int {
     kPhRouter = 0, kPhScan, kPhDispatch, kPhGemmUp, kPhGemmDown, kPhCombine,
-    kPhGradDispatch, kPhGemmDh, kPhGemmDwDown, kPhGemmDwUp, kPhGemmDx, kPhRouterBwd, kPhRouterDw, kPhScatter,
+    kPhGradDispatch, kPhGemmDh, kPhGemmDwDown, kPhGemmDwUp, kPhGemmDx, kPhRouterBwd, kPhRouterDw, kPhRouterDx, kPhScatter,
     kPhExchange, kNumPhases
 };
 struct Profiler {

@@ -84,10 +84,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dispatch_kernel(const Rou
     }
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const RouteDims d, const RouteBufs b,
                                                                        const uint16_t* __restrict__ Yg,
                                                                        uint16_t* __restrict__ Y, float beta,
-                                                                       int mode, const PeerMap pm,
+                                                                       const PeerMap pm,
                                                                        uint16_t* __restrict__ y_keep) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long t = (long)blockIdx.x * kWarpsPerBlock + warp;
@@ -105,6 +106,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
     }
     const int nvec = d.D >> 3;
     uint16_t* dst = Y + t * d.D;
+#pragma unroll 2
     for (int v = lane; v < nvec; v += 32) {
         float acc[8];
         if (beta != 0.0f) {
@@ -122,10 +124,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
                 const uint4 raw = ldg16(rows[j] + v * 8);
                 if (y_keep) stg16(y_keep + (long)slots[j] * d.D + v * 8, raw);
                 unpack8(raw, y);
-                if (mode == 1) {
+                if constexpr (MODE == 1) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[i] += ws[j] * silu_f(y[i]);
-                } else if (mode == 2) {
+                } else if constexpr (MODE == 2) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[i] += ws[j] * y[i];
                 } else {
@@ -138,11 +140,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
     }
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(const RouteDims d, const RouteBufs b,
                                                                              const uint16_t* __restrict__ dY,
                                                                              const uint16_t* __restrict__ Yg,
                                                                              uint16_t* __restrict__ dYg,
-                                                                             float* __restrict__ s_j, int mode,
+                                                                             float* __restrict__ s_j,
                                                                              int tok_blocks, const PeerMap pm) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = d.D >> 3;
@@ -168,6 +171,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
         rows[j] = shfl_ptr(row, j);
     }
     const uint16_t* src = dY + t * d.D;
+#pragma unroll 2
     for (int v = lane; v < nvec; v += 32) {
         float g[8];
         unpack8(ldg16(src + v * 8), g);
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
         for (int j = 0; j < kMaxK; ++j) {
             if (j < d.K && slots[j] >= 0) {
                 float o[8];
-                if (mode == 1) {
+                if constexpr (MODE == 1) {
                     float pre[8];
                     unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), pre);
 #pragma unroll
@@ -185,7 +189,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
                         o[i] = (ws[j] * g[i]) * sg * (1.0f + pre[i] * (1.0f - sg));     // silu_bwd, common.h:21-24
                     }
                 } else {
-                    if (mode == 2) {
+                    if constexpr (MODE == 2) {
                         float y[8];
                         unpack8(ldg16(Yg + (long)slots[j] * d.D + v * 8), y);
 #pragma unroll
@@ -198,7 +202,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
             }
         }
     }
-    if (mode != 0) {
+    if constexpr (MODE != 0) {
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
             if (j < d.K) {
@@ -435,14 +439,20 @@ cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16
 
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
                            int mode, cudaStream_t s, PeerMap pm, uint16_t* y_keep) {
-    combine_kernel<<<tok_blocks_of(d.T), kWarpsPerBlock * 32, 0, s>>>(d, b, Yg, Y, beta, mode, pm, y_keep);
+    const dim3 grid(tok_blocks_of(d.T)), block(kWarpsPerBlock * 32);
+    if (mode == 1) combine_kernel<1><<<grid, block, 0, s>>>(d, b, Yg, Y, beta, pm, y_keep);
+    else if (mode == 2) combine_kernel<2><<<grid, block, 0, s>>>(d, b, Yg, Y, beta, pm, y_keep);
+    else combine_kernel<0><<<grid, block, 0, s>>>(d, b, Yg, Y, beta, pm, y_keep);
     return cudaGetLastError();
 }
 
 cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
                                  uint16_t* dYg, float* s_j, int mode, cudaStream_t s, PeerMap pm) {
     const int tb = tok_blocks_of(d.T);
-    grad_dispatch_kernel<<<tb + (pm.base ? 0 : d.E), kWarpsPerBlock * 32, 0, s>>>(d, b, dY, Yg, dYg, s_j, mode, tb, pm);
+    const dim3 grid(tb + (pm.base ? 0 : d.E)), block(kWarpsPerBlock * 32);
+    if (mode == 1) grad_dispatch_kernel<1><<<grid, block, 0, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
+    else if (mode == 2) grad_dispatch_kernel<2><<<grid, block, 0, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
+    else grad_dispatch_kernel<0><<<grid, block, 0, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
     return cudaGetLastError();
 }
 
