@@ -441,7 +441,7 @@ def main():
                     "bytes_per_decode_step": per_decode}
     hbm = {}
     bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12), "combine": (A * D * 2 + T * D * 2),
-                "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + T * D * 2)}
+                "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
     for n, nb in bytes_of.items():
         if n in phases and phases[n][0] > 0:
             gbs = nb / (phases[n][0] / phases[n][1] * 1e-3) / 1e9

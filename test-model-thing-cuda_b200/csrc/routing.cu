@@ -19,6 +19,13 @@ namespace {
 constexpr int kDC = 128;            // d elements staged per pipeline step (16 vectors of 8)
 constexpr int kTT = 4;              // tokens per thread
 
+// Compile-time loop: f(integral_constant<int, 0>) ... f(integral_constant<int, N-1>)
+template <int V> struct IntC { static constexpr int value = V; };
+template <int N, int I = 0, class F>
+__device__ __forceinline__ void static_for(F& f) {
+    if constexpr (I < N) { f(IntC<I>{}); static_for<N, I + 1>(f); }
+}
+
 struct RouterArgs {
     const uint16_t* X; const void* Wr; const float* bias;
     int T, D, E, K;
@@ -31,6 +38,14 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// 16-byte shared-memory load from a 32-bit shared address plus a compile-time offset (keeps the
+// address arithmetic of the unrolled expert loop in the instruction's immediate field)
+template <int OFF>
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4 + %5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+    return v;
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -98,38 +113,41 @@ __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a
             if (k + 1 < nchunks) { load_chunk(k + 1, stage[(k + 1) & 1]); cp_async_wait<1>(); }
             else cp_async_wait<0>();
             __syncthreads();
-            const uint8_t* xb = stage[k & 1];
-            const uint8_t* wb = xb + XS_BYTES;
+            const uint32_t xb = (uint32_t)__cvta_generic_to_shared(stage[k & 1]);
+            const uint32_t wb = xb + XS_BYTES;
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 const int v = c * 8 + s;                         // this chain's vector inside the chunk
                 if (k * (kDC / 8) + c * 8 < nvec) {              // uniform: nvec is a multiple of 8
                     float x[kTT][8];
-#pragma unroll
-                    for (int i = 0; i < kTT; ++i) {
-                        const int row = tslab * 16 + g * kTT + i;
-                        const uint4 xv = *reinterpret_cast<const uint4*>(xb + (row * (kDC / 8) + v) * 16);
-                        x[i][0] = bf_lo(xv.x); x[i][1] = bf_hi(xv.x); x[i][2] = bf_lo(xv.y); x[i][3] = bf_hi(xv.y);
-                        x[i][4] = bf_lo(xv.z); x[i][5] = bf_hi(xv.z); x[i][6] = bf_lo(xv.w); x[i][7] = bf_hi(xv.w);
-                    }
-#pragma unroll
-                    for (int e = 0; e < TE; ++e) {
-                        const int row = eslab * TE + e;
+                    const uint32_t xa = xb + (uint32_t)(((tslab * 16 + g * kTT) * (kDC / 8) + v) * 16);
+                    const uint32_t wa = wb + (uint32_t)(((eslab * TE) * (kDC / 8) + v) * 16);
+                    auto unpack = [&](const uint4 xv, float (&f)[8]) {
+                        f[0] = bf_lo(xv.x); f[1] = bf_hi(xv.x); f[2] = bf_lo(xv.y); f[3] = bf_hi(xv.y);
+                        f[4] = bf_lo(xv.z); f[5] = bf_hi(xv.z); f[6] = bf_lo(xv.w); f[7] = bf_hi(xv.w);
+                    };
+                    static_assert(kTT == 4, "token rows are unrolled by hand");
+                    unpack(lds16<0 * (kDC / 8) * 16>(xa), x[0]);
+                    unpack(lds16<1 * (kDC / 8) * 16>(xa), x[1]);
+                    unpack(lds16<2 * (kDC / 8) * 16>(xa), x[2]);
+                    unpack(lds16<3 * (kDC / 8) * 16>(xa), x[3]);
+                    auto expert = [&](auto E_) {
+                        constexpr int e = decltype(E_)::value;
                         float w[8];
                         if constexpr (WF32) {
-                            const float4 w0 = *reinterpret_cast<const float4*>(wb + ((0 * EP + row) * (kDC / 8) + v) * 16);
-                            const float4 w1 = *reinterpret_cast<const float4*>(wb + ((1 * EP + row) * (kDC / 8) + v) * 16);
-                            w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+                            const uint4 w0 = lds16<e * (kDC / 8) * 16>(wa);
+                            const uint4 w1 = lds16<(EP + e) * (kDC / 8) * 16>(wa);
+                            w[0] = __uint_as_float(w0.x); w[1] = __uint_as_float(w0.y); w[2] = __uint_as_float(w0.z); w[3] = __uint_as_float(w0.w);
+                            w[4] = __uint_as_float(w1.x); w[5] = __uint_as_float(w1.y); w[6] = __uint_as_float(w1.z); w[7] = __uint_as_float(w1.w);
                         } else {
-                            const uint4 wv = *reinterpret_cast<const uint4*>(wb + (row * (kDC / 8) + v) * 16);
-                            w[0] = bf_lo(wv.x); w[1] = bf_hi(wv.x); w[2] = bf_lo(wv.y); w[3] = bf_hi(wv.y);
-                            w[4] = bf_lo(wv.z); w[5] = bf_hi(wv.z); w[6] = bf_lo(wv.w); w[7] = bf_hi(wv.w);
+                            unpack(lds16<e * (kDC / 8) * 16>(wa), w);
                         }
 #pragma unroll
                         for (int i = 0; i < kTT; ++i)
 #pragma unroll
                             for (int q = 0; q < 8; ++q) acc[i][e] = __fmaf_rn(x[i][q], w[q], acc[i][e]);
-                    }
+                    };
+                    static_for<TE>(expert);
                 }
             }
             __syncthreads();
