@@ -203,6 +203,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gemm-cycles", action="store_true",
+                    help="measurement only: print (stderr) where the TMA, MMA and epilogue threads of the last GEMM launches spent their cycles")
     ap.add_argument("--gemm", default="1cta", choices=["2cta", "1cta"],
                     help="grouped GEMM kernel: one CTA per 128x256 tile (default, measured 1-2 %% faster) or CTA pairs on 256x256 tiles")
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
@@ -212,6 +214,8 @@ def main():
     if args.tokens:
         cfg["T"] = args.tokens
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.gemm_cycles:
+        os.environ["TMT_MOE_GEMM_CYCLES"] = "1"
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -340,6 +344,16 @@ def main():
     wall1 = time.time()
     phases = moe.profile(reset=True)
     moe.set_profile(False)
+    if args.gemm_cycles and rank == 0:
+        n, cyc = moe.gemm_cycles()
+        per_step = max(1, n // (args.warmup + args.steps))
+        names = ("mma_wait_full", "mma_issue", "mma_wait_acc", "tma_wait_empty", "tma_issue", "epi_wait_acc", "epi_work", "total")
+        for j in range(per_step):
+            c = cyc[(n - per_step + j) % cyc.shape[0]]
+            c = c[c[:, 7] > 0]
+            if len(c):
+                print("gemm launch %d of a step (mean cycles over %d CTAs): " % (j, len(c)) +
+                      ", ".join("%s %.0f" % (nm, v) for nm, v in zip(names, c.mean(axis=0))), file=sys.stderr)
     launches = moe.launch_count - launches0
     clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps

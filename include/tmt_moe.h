@@ -122,6 +122,12 @@ const char* tmt_moe_phase_name(int i);
 /* Number of kernel launches the handle has queued since creation (the reference counts
  * nothing; used by the benchmark to report its launch count). */
 long long tmt_moe_launch_count(const tmt_moe* h);
+/* Measurement only (no counterpart in the reference). With TMT_MOE_GEMM_CYCLES=1 in the environment at
+ * tmt_moe_create, every tcgen05 GEMM launch records, per CTA, the clock cycles its TMA, MMA and
+ * epilogue threads spent waiting and working. Copies the ring of the last *launches launches
+ * ([launch % *launches][cta < *ctas][slot < *slots] long long) to `out` (may be NULL to query the
+ * sizes) and returns the number of GEMM launches so far, -1 when the counters are off. Synchronises. */
+int tmt_moe_debug_gemm_cycles(tmt_moe* h, long long* out, int* launches, int* ctas, int* slots);
 /* Device-side status word: 0 when no kernel reported a bounds violation or a wait that ran
  * out; otherwise the first code recorded. Synchronises. */
 int tmt_moe_device_status(tmt_moe* h);

@@ -30,13 +30,16 @@ constexpr int kBK = 64;    // k per stage: 64 bf16 = one 128-byte swizzle span
 constexpr int kChunk = 32; // columns one epilogue step handles per row
 constexpr int kEpiCols = 128; // columns of a tile one epilogue warp drains; also the width of one gate-gradient partial
 
+// Cycle counters one CTA of a tcgen05 kernel records when GemmParams::cyc is set.
+enum CycSlot : int { kCycMmaWaitFull = 0, kCycMmaIssue, kCycMmaWaitAcc, kCycProdWaitEmpty, kCycProdIssue, kCycEpiWaitAcc, kCycEpiWork, kCycTotal, kCycSlots };
+
 struct GemmParams {
     // tensor maps in device memory; map index = expert * stride (stride 0: one shared map)
     const CUtensorMap* mapA; int a_stride;
     const CUtensorMap* mapB; int b_stride;
     uint32_t tx_bytes;            // bytes one pipeline stage receives
-    int a_boxes, b_boxes;         // TMA boxes per stage for A and B
-    int a_box_step, b_box_step;   // coordinate step between boxes along the tile's MN extent
+    int a_boxes, b_boxes;         // mn-major operands: 64-wide blocks (8 KB each) one CTA stages per k block; their maps are the
+                                  // 3-D views {64, k, block}, one box of a_boxes / b_boxes blocks per load
     // raw views of the same operands for the SIMT kernel
     const uint16_t* A; long lda;
     const uint16_t* B; long ldb;              // kRedRagged
@@ -60,6 +63,7 @@ struct GemmParams {
     // mapC1 = pre-activation (optional).
     const CUtensorMap* mapC0; const CUtensorMap* mapC1; int c_stride;
     int* status;
+    long long* cyc;               // measurement only: 8 cycle counters per CTA (see kCyc*), NULL = off
     int dbg;                      // measurement only: bit 0 = no TMA loads (stale operands), bit 1 = no MMAs, bit 2 = no epilogue stores, bit 3 = epilogue stores straight from registers
 };
 

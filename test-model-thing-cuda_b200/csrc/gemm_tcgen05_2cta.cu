@@ -4,32 +4,39 @@
 // a third against the single-CTA kernel, whose 128x256 tiles are bound by shared-memory
 // bandwidth (TMA fill + operand reads) rather than by the tensor pipe.
 //
-// Protocol. Both CTAs run a TMA producer (warp 0) for their own tiles and signal the LEADER's
+// Protocol. Both CTAs run two TMA producer warps (warp 0: even stages, last warp: odd stages; a TMA load
+// instruction keeps its warp busy for about 300 cycles) for their own tiles and signal the LEADER's
 // (cluster rank 0) "full" barrier; the leader's warp 1 issues the MMAs and commits to the
 // "empty" and "accumulator full" barriers of BOTH CTAs (one tcgen05.commit per CTA); the
 // epilogue warps of both CTAs drain their own 128 TMEM lanes and arrive on the leader's
 // "accumulator empty" barrier. Every TMA load has exactly one destination CTA. Waits are bounded as in the single-CTA
 // kernel; both CTAs always reach the closing cluster barrier before TMEM is freed.
 //
+// Pipeline stages are filled and released in PAIRS: one "full" and one "empty" barrier cover two
+// consecutive stages, so the MMA thread waits once and commits once (two instructions, one per
+// CTA) per 8 MMAs. Measured on a B200: any shared-memory read by the thread that issues tcgen05.mma
+// costs it about 370 cycles and a commit about 85, so with a wait and a commit pair per 4 MMAs (512
+// tensor-pipe cycles) the thread, not the pipe, sets the pace. The epilogue is the shared
+// one (staged in shared memory, written with TMA stores).
+//
 // Needs every group padded to 256 rows so that the two 128-row halves of a tile belong to one
 // expert (the handle pads accordingly when this kernel is selected).
-#include "gemm.cuh"
-#include "tc_util.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace tmt {
 namespace {
 
 using namespace tc;
 
-constexpr int kStages2 = 7;
+constexpr int kStages2 = 6;                     // three pairs
 constexpr int kATile2 = kBM * kBK * 2;          // 16 KB: this CTA's 128 rows
 constexpr int kBTile2 = (kBN / 2) * kBK * 2;    // 16 KB: this CTA's 128 of the 256 columns
 constexpr int kStageBytes2 = kATile2 + kBTile2;
 // Epilogue warps per CTA: 4 (one per TMEM lane quarter, 256 columns each) or, for the epilogue that
 // also reads the saved pre-activation (measured: that one is latency-bound), 8 (two per quarter, 128
-// columns each). Threads = TMA warp + MMA warp + epilogue warps.
+// columns each). Threads = TMA warp + MMA warp + epilogue warps + second TMA warp.
 template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiDh ? 8 : 4; }
-template <int EPI> __host__ __device__ constexpr int block_threads() { return 64 + 32 * epi_warps<EPI>(); }
+template <int EPI> __host__ __device__ constexpr int block_threads() { return 96 + 32 * epi_warps<EPI>(); }
 constexpr uint32_t kTmemCols2 = 512;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -54,6 +61,11 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -99,10 +111,23 @@ __device__ __forceinline__ bool get_tile2(const GemmParams& p, int t, int m_pair
     return true;
 }
 
+// The MMA thread's view of a tile: no expert lookup for row-ragged launches (a global load it would have to wait for).
+__device__ __forceinline__ bool get_tile2_nkb(const GemmParams& p, int t, int m_pairs, int n_tiles, int& nkb) {
+    if (p.mode == kRowsRagged) {
+        nkb = (p.K + kBK - 1) / kBK;
+        return t < m_pairs * n_tiles;
+    }
+    const int per = m_pairs * n_tiles;
+    if (t >= per * p.experts) return false;
+    const int e = t / per;
+    nkb = (p.poff[e + 1] - p.poff[e]) / kBK;
+    return true;
+}
+
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[kStages2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2];
+    __shared__ uint64_t full_bar[kStages2 / 2], empty_bar[kStages2 / 2], tfull_bar[2], tempty_bar[2], group_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -114,7 +139,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
 
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < kStages2; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int s = 0; s < kStages2 / 2; ++s) { mbar_init(smem_u32(&full_bar[s]), 2); mbar_init(smem_u32(&empty_bar[s]), 1); }   // full: one leader arrival per stage
+        for (int a = 0; a < 2; ++a) mbar_init(smem_u32(&group_bar[a]), 4);
         for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 2 * epi_warps<EPI>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -133,16 +159,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
     const int m_pairs = p.mode == kRowsRagged ? (*p.num_m_tiles + 1) / 2 : (p.M + 2 * kBM - 1) / (2 * kBM);
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
-    if (warp == 0) {
-        // ---------------- TMA producer (both CTAs): lane 0 owns the barriers, lanes 0..n-1 each issue one box ----------------
+    if (warp == 0 || warp == 2 + epi_warps<EPI>()) {
+        const int my = warp == 0 ? 0 : 1;
+        // ---------------- TMA producers (both CTAs): lane 0 owns the barriers and loads A, lane 1 loads B ----------------
         int s = 0; uint32_t ph = 0;
         uint32_t issued = 0, last_parity = 0;
         bool ok = true;
-        const int a_n = p.a_mn ? p.a_boxes : 1, b_n = p.b_mn ? p.b_boxes : 1;
+        const bool prof = p.cyc != nullptr && my == 0;
+        long long c_wait = 0, c_issue = 0, t0 = 0, t1 = 0;
         for (int t = pair; ok; t += npairs) {
             Tile2 ti;
             if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) {
-                if (lane == 0 && p.mode == kRowsRagged && t < m_pairs * n_tiles) report(p.status, kErrSlotRange);
+                if (lane == 0 && p.mode == kRowsRagged && t < m_pairs * n_tiles) { report(p.status, kErrSlotRange); *abort_flag = 1; }
                 break;
             }
             const CUtensorMap* ma = p.mapA + (size_t)ti.expert * p.a_stride;
@@ -151,10 +179,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
             __syncwarp();
             const int bcol0 = ti.col0 + rank * (kBN / 2);
             for (int kb = 0; kb < ti.nkb; ++kb) {
-                const uint32_t fb_local = smem_u32(&full_bar[s]);
+                if ((s & 1) != my) { if (++s == kStages2) { s = 0; ph ^= 1; } continue; }     // the other producer's stage
+                const uint32_t fb_local = smem_u32(&full_bar[s >> 1]);
                 const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
                 if (lane == 0) {
-                    ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status);
+                    if (prof) t0 = clock64();
+                    ok = mbar_wait(smem_u32(&empty_bar[s >> 1]), ph ^ 1, abort_flag, p.status);   // the pair (s, s+1) is free
+                    if (prof) t1 = clock64();
                     if (ok && leader) mbar_expect_tx(fb_local, (p.dbg & 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -162,24 +193,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                 const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
                 const int k0 = (ti.kb0 + kb) * kBK;
                 if (!(p.dbg & 1)) {
-                    if (lane < a_n) {
-                        if (p.a_mn) tma_load_2d_pair(sa + lane * 8192, ma, fb, ti.row0 + lane * p.a_box_step, k0);
+                    if (lane == 0) {
+                        if (p.a_mn) tma_load_3d_pair(sa, ma, fb, 0, k0, ti.row0 >> 6);
                         else tma_load_2d_pair(sa, ma, fb, k0, ti.row0);
-                    } else if (lane < a_n + b_n) {
-                        const int j = lane - a_n;
-                        if (p.b_mn) tma_load_2d_pair(sb + j * 8192, mb, fb, bcol0 + j * p.b_box_step, k0);
+                    } else if (lane == 1) {
+                        if (p.b_mn) tma_load_3d_pair(sb, mb, fb, 0, k0, bcol0 >> 6);
                         else tma_load_2d_pair(sb, mb, fb, k0, bcol0);
                     }
                 }
                 __syncwarp();
-                issued |= 1u << s;
-                last_parity = (last_parity & ~(1u << s)) | (ph << s);
+                if (prof && lane == 0) { c_wait += t1 - t0; c_issue += clock64() - t1; }
+                issued |= 1u << (s >> 1);
+                last_parity = (last_parity & ~(1u << (s >> 1))) | (ph << (s >> 1));
                 if (++s == kStages2) { s = 0; ph ^= 1; }
             }
         }
+        // An odd number of k blocks leaves the last pair's barrier one arrival short: the leader's odd producer supplies it,
+        // after the same wait a real load of that stage would make (the barrier must have left its previous phase first).
+        if (ok && leader && lane == 0 && (s & 1) && my == 1 && mbar_wait(smem_u32(&empty_bar[s >> 1]), ph ^ 1, abort_flag, p.status))
+            mbar_expect_tx(smem_u32(&full_bar[s >> 1]), 0);
+        if (prof && lane == 0) {
+            p.cyc[blockIdx.x * kCycSlots + kCycProdWaitEmpty] = c_wait;
+            p.cyc[blockIdx.x * kCycSlots + kCycProdIssue] = c_issue;
+        }
         if (!ok && leader && lane == 0) {
             // aborting: the leader's barriers count both CTAs' copies; wait (bounded) for what was announced
-            for (int q = 0; q < kStages2; ++q) {
+            for (int q = 0; q < kStages2 / 2; ++q) {
                 if (!(issued >> q & 1)) continue;
                 const long long t0 = clock64();
                 while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
@@ -196,21 +235,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
             int s = 0; uint32_t ph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool ok = true;
+            const bool prof = p.cyc != nullptr;
+            long long c_full = 0, c_issue = 0, c_acc = 0, t0 = 0, t1 = 0;
+            const long long t_start = prof ? clock64() : 0;
             for (int t = pair; ok; t += npairs) {
                 Tile2 ti;
-                if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) break;
+                if (!get_tile2_nkb(p, t, m_pairs, n_tiles, ti.nkb)) break;
+                if (prof) t0 = clock64();
                 if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status)) break;
+                if (prof) c_acc += clock64() - t0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int kb = 0; kb < ti.nkb; ++kb) {
-                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, p.status)) { ok = false; break; }
-                    tc_fence_after();
+                    if (prof) t0 = clock64();
+                    if (!(s & 1) && !(p.dbg & 64)) {          // both stages of the pair (s, s+1), in both CTAs, have landed once this barrier completes
+                        if (!mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status)) { ok = false; break; }
+                        tc_fence_after();
+                    }
+                    if (prof) t1 = clock64();
                     const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
                     const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
                         if (!(p.dbg & 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
-                    tc_commit_pair(smem_u32(&empty_bar[s]));
+                    if ((s & 1) && !(p.dbg & 128)) tc_commit_pair(smem_u32(&empty_bar[s >> 1]));    // releases stages s-1 and s in both CTAs
+                    if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
                     if (++s == kStages2) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
@@ -221,43 +270,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                 }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
+            if (prof) {
+                long long* c = p.cyc + blockIdx.x * kCycSlots;
+                c[kCycMmaWaitFull] = c_full; c[kCycMmaIssue] = c_issue; c[kCycMmaWaitAcc] = c_acc; c[kCycTotal] = clock64() - t_start;
+            }
         }
         __syncwarp();
     } else {
         // ---------------- epilogue (both CTAs): own 128 TMEM lanes ----------------
-        const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
-        constexpr int kWarpCols = kBN / (epi_warps<EPI>() / 4);      // columns of the tile this warp drains
-        const int half = (warp - 2) >> 2;
+        constexpr int kGroups = epi_warps<EPI>() / 4;
+        EpiState es;
+        es.quarter = warp & 3;                  // TMEM lanes [32*quarter, 32*quarter+32)
+        es.half = (warp - 2) >> 2;
+        es.lane = lane;
+        es.staged = p.mapC0 != nullptr && !(p.dbg & 8);
+        es.issuer = ((warp - 2) & 3) == 0 && lane == 0;
+        es.cbuf = tiles_s + kStages2 * kStageBytes2;
+        es.gbar = smem_u32(&group_bar[es.half]);
+        es.abort_flag = abort_flag;
+        const bool prof = p.cyc != nullptr && warp == 2 && lane == 0;
+        long long c_wait = 0, c_work = 0, t0 = 0, t1 = 0;
         int acc = 0; uint32_t acc_ph = 0;
         for (int t = pair;; t += npairs) {
             Tile2 ti;
             if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) break;
-            bool ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);
+            if (prof) t0 = clock64();
+            bool ok = true;
+            if (!(p.dbg & 32) || lane == 0) ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);   // bit 5: one lane per warp waits
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (prof) t1 = clock64();
             tc_fence_after();
-            const long row = (long)ti.row0 + quarter * 32 + lane;
+            const long row = (long)ti.row0 + es.quarter * 32 + lane;
             const bool row_ok = (p.mode == kRowsRagged) ? (row < (long)*p.num_m_tiles * kBM) : (row < p.M);
-            float sw = 0.0f;
-#pragma unroll 1
-            for (int c = half * (kWarpCols / kChunk); c < (half + 1) * (kWarpCols / kChunk); ++c) {
-                const int col0 = ti.col0 + c * kChunk;
-                if (col0 >= p.N) break;
-                float v[kChunk];
-                if (ti.nkb > 0) {
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kBN + c * kChunk), v);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
-                }
-                if (row_ok && !(p.dbg & 4)) epilogue_chunk<EPI>(p, ti.expert, row, col0, v, sw);
-            }
-            if (EPI == kEpiDh && row_ok && ti.col0 + half * kEpiCols < p.N) p.sw_part[row * p.sw_ld + (ti.col0 + half * kEpiCols) / kEpiCols] = sw;
+            const uint32_t tm = tmem_base + ((uint32_t)(es.quarter * 32) << 16) + (uint32_t)(acc * kBN);
+            if (!epi_drain_tile<EPI, kGroups>(p, es, ti.expert, ti.row0, ti.col0, ti.nkb, tm, row_ok)) break;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+            if (prof) { c_wait += t1 - t0; c_work += clock64() - t1; }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+        if (prof) { p.cyc[blockIdx.x * kCycSlots + kCycEpiWaitAcc] = c_wait; p.cyc[blockIdx.x * kCycSlots + kCycEpiWork] = c_work; }
+        if (es.staged && es.issuer) bulk_wait_all();
     }
     tc_fence_before();
     __syncthreads();
@@ -279,7 +334,7 @@ cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
 
 }  // namespace
 
-size_t gemm_tcgen05_2cta_smem_bytes() { return (size_t)kStages2 * kStageBytes2 + 1024; }
+size_t gemm_tcgen05_2cta_smem_bytes() { return (size_t)kStages2 * kStageBytes2 + 2 * kStagingBytes + 1024; }
 
 cudaError_t launch_gemm_tcgen05_2cta(const GemmParams& p, int num_sms, cudaStream_t stream) {
     const int grid = num_sms & ~1;      // whole CTA pairs

@@ -81,6 +81,26 @@ void make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, u
     }
 }
 
+// bf16 matrix [rows][inner] read with the `inner` extent as the MMA's M or N (mn-major operand): a 3-D view
+// {64 inner elements, rows, inner / 64 blocks} with the block stride (128 B) below the row stride, so ONE
+// box {64, 64, blocks} lands as `blocks` consecutive 8 KB swizzle blocks, the layout the shared-memory
+// descriptors of the GEMM kernels use (one TMA instruction per operand and k block instead of one per block).
+void make_map_mn(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint32_t blocks) {
+    cuuint64_t dims[3] = {64, rows, inner / 64};
+    cuuint64_t strides[2] = {inner * 2, 128};
+    cuuint32_t box[3] = {64, 64, blocks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS || inner % 64 != 0) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled failed (%d) for the mn-major view of %llux%llu, %u blocks", (int)r,
+                 (unsigned long long)inner, (unsigned long long)rows, blocks);
+        throw std::runtime_error(msg);
+    }
+}
+
 #define CK(call)                                                                              \
     do {                                                                                      \
         cudaError_t e__ = (call);                                                             \
@@ -106,17 +126,18 @@ enum WMap { kUpK = 0, kDownK, kDownMN, kUpMN, kNumWMaps };   // one more map fol
 
 void build_act_maps(tmt_moe* h) {
     const uint64_t D = h->d.dim, H = h->d.hidden, cap = h->gcap;
+    const uint32_t ablk = kBM / 64, bblk = (h->two_cta ? kBN / 2 : kBN) / 64;    // 64-wide blocks one CTA stages per k block
     std::vector<CUtensorMap> m(kNumActMaps);
     memset(m.data(), 0, m.size() * sizeof(CUtensorMap));
     make_map(&m[kXgK], h->Xg, D, cap, 64, 128);
     make_map(&m[kDYgK], h->dYg, D, cap, 64, 128);
-    make_map(&m[kDYgMN], h->dYg, D, cap, 64, 64);
-    make_map(&m[kXgMN], h->Xg, D, cap, 64, 64);
+    make_map_mn(&m[kDYgMN], h->dYg, D, cap, ablk);
+    make_map_mn(&m[kXgMN], h->Xg, D, cap, bblk);
     if (H > 0) {
         make_map(&m[kHactK], h->Hact, H, cap, 64, 128);
         make_map(&m[kDPK], h->dP, H, cap, 64, 128);
-        make_map(&m[kHactMN], h->Hact, H, cap, 64, 64);
-        make_map(&m[kDPMN], h->dP, H, cap, 64, 64);
+        make_map_mn(&m[kHactMN], h->Hact, H, cap, bblk);
+        make_map_mn(&m[kDPMN], h->dP, H, cap, ablk);
     }
     make_out_map(&m[kOutYg], h->Yg, false, D, cap);
     if (h->dXg) make_out_map(&m[kOutDXg], h->dXg, false, D, cap);
@@ -130,7 +151,7 @@ void build_act_maps(tmt_moe* h) {
         for (int i = 0; i < h->splits; ++i) make_out_map(&m[kOutSplit0 + i], h->dwr_partial + (size_t)i * h->mw * D, true, D, h->mw);
     }
     if (h->dl_g) {
-        make_map(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, 64, 64);
+        make_map_mn(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, ablk);
         make_map(&m[kDltK], h->dl_t, h->kw, (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad, 64, 128);
     }
     CK(cudaMemcpyAsync(h->act_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
@@ -156,11 +177,11 @@ void refresh_weights(tmt_moe* h, const void* const* Wup, const void* const* Wdow
             if (H > 0) {
                 make_map(&m[kUpK * E + e], Wup[e], D, H, 64, (uint32_t)std::min<uint64_t>(brows, H));     // [H][D], k = D
                 make_map(&m[kDownK * E + e], Wdown[e], H, D, 64, (uint32_t)std::min<uint64_t>(brows, D)); // [D][H], k = H
-                make_map(&m[kDownMN * E + e], Wdown[e], H, D, 64, 64);    // dH: k = rows (D), n = H contiguous
-                make_map(&m[kUpMN * E + e], Wup[e], D, H, 64, 64);        // dXg: k = rows (H), n = D contiguous
+                make_map_mn(&m[kDownMN * E + e], Wdown[e], H, D, (uint32_t)brows / 64);    // dH: k = rows (D), n = H contiguous
+                make_map_mn(&m[kUpMN * E + e], Wup[e], D, H, (uint32_t)brows / 64);        // dXg: k = rows (H), n = D contiguous
             } else {
                 make_map(&m[kUpK * E + e], Wup[e], D, D, 64, (uint32_t)std::min<uint64_t>(brows, D));
-                make_map(&m[kUpMN * E + e], Wup[e], D, D, 64, 64);
+                make_map_mn(&m[kUpMN * E + e], Wup[e], D, D, (uint32_t)brows / 64);
             }
         }
         CK(cudaMemcpyAsync(h->w_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
@@ -207,7 +228,7 @@ GemmParams base_params(tmt_moe* h) {
     p.num_m_tiles = h->g_num_m_tiles;
     p.poff = h->g_poff;
     p.status = h->rb.status;
-    p.a_boxes = 1; p.b_boxes = 1; p.a_box_step = 64; p.b_box_step = 64;
+    p.a_boxes = 1; p.b_boxes = 1;
     p.dbg = h->gemm_dbg;
     return p;
 }
@@ -247,7 +268,13 @@ void run_tc(tmt_moe* h, const GemmParams& p) {
     else CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
 }
 
-void run_gemm(tmt_moe* h, const GemmParams& p) {
+void run_gemm(tmt_moe* h, const GemmParams& p0) {
+    GemmParams p = p0;
+    if (h->gemm_cyc && h->tensor_core) {
+        p.cyc = h->gemm_cyc + (size_t)(h->cyc_slot % kGemmCycLaunches) * kGemmCycCtas * kCycSlots;
+        CK(cudaMemsetAsync(p.cyc, 0, sizeof(long long) * kGemmCycCtas * kCycSlots, h->stream));
+        h->cyc_slot += 1;
+    }
     if (h->tensor_core) run_tc(h, p);
     else CK(launch_gemm_simt(p, h->g_max_tiles, h->stream));
     h->launches += 1;
@@ -424,10 +451,10 @@ void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order) {
     const uint64_t tpad = (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
     CUtensorMap m[2];
     memset(m, 0, sizeof m);
-    make_map(&m[0], x_rows, h->d.dim, token_order ? tpad : (uint64_t)h->dims.cap, 64, 64);
+    make_map_mn(&m[0], x_rows, h->d.dim, token_order ? tpad : (uint64_t)h->dims.cap, (h->two_cta ? kBN / 2 : kBN) / 64);
     CK(cudaMemcpyAsync(h->act_maps + kXsMN, &m[0], sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
     if (token_order) {
-        make_map(&m[1], h->dl_t, h->kw, tpad, 64, 64);
+        make_map_mn(&m[1], h->dl_t, h->kw, tpad, kBM / 64);
         CK(cudaMemcpyAsync(h->act_maps + kDltMN, &m[1], sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
         std::vector<int> sp(kMaxSplits + 1, 0);
         const long tiles = (long)tpad / kPad;
@@ -475,7 +502,7 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
     if (h->wr_seen != wr16) {
         CUtensorMap m;
         memset(&m, 0, sizeof m);
-        make_map(&m, wr16, D, E, 64, 64);
+        make_map_mn(&m, wr16, D, E, (h->two_cta ? kBN / 2 : kBN) / 64);
         CK(cudaMemcpyAsync(h->w_maps + (size_t)kNumWMaps * h->local_experts, &m, sizeof m, cudaMemcpyHostToDevice, h->stream));
         h->wr_seen = wr16;
     }
@@ -540,6 +567,8 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->tensor_core = d.gemm_impl != TMT_MOE_GEMM_SIMT;
     h->two_cta = d.gemm_impl == TMT_MOE_GEMM_TCGEN05_2CTA;
     if (const char* dbg = getenv("TMT_MOE_GEMM_DEBUG")) h->gemm_dbg = atoi(dbg);     // measurement only, results are then wrong
+    if (const char* cyc = getenv("TMT_MOE_GEMM_CYCLES"))                               // measurement only: per-role cycle counters
+        if (atoi(cyc) && h->num_sms <= kGemmCycCtas) h->gemm_cyc = dalloc<long long>(h, (size_t)kGemmCycLaunches * kGemmCycCtas * kCycSlots);
     h->pad = h->two_cta ? 2 * kPad : kPad;
     const int pad = h->pad;
     // rows of the grouped buffers: every assignment plus up to pad-1 pad rows per expert (moe.cu:331)
@@ -861,6 +890,22 @@ int tmt_moe_selftest_bounded_wait(tmt_moe* h, long long limit_cycles) {
 }
 
 long long tmt_moe_launch_count(const tmt_moe* h) { return h ? h->launches : -1; }
+
+int tmt_moe_debug_gemm_cycles(tmt_moe* h, long long* out, int* launches, int* ctas, int* slots) {
+    if (!h) { set_error("null handle"); return -1; }
+    if (launches) *launches = kGemmCycLaunches;
+    if (ctas) *ctas = kGemmCycCtas;
+    if (slots) *slots = kCycSlots;
+    if (!h->gemm_cyc) { set_error("cycle counters are off (set TMT_MOE_GEMM_CYCLES=1 before tmt_moe_create)"); return -1; }
+    if (!out) return h->cyc_slot;
+    cudaSetDevice(h->d.device);
+    if (cudaMemcpyAsync(out, h->gemm_cyc, sizeof(long long) * kGemmCycLaunches * kGemmCycCtas * kCycSlots, cudaMemcpyDeviceToHost, h->stream) != cudaSuccess ||
+        cudaStreamSynchronize(h->stream) != cudaSuccess) {
+        set_error("reading the cycle counters failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return -1;
+    }
+    return h->cyc_slot;
+}
 
 int tmt_moe_device_status(tmt_moe* h) {
     if (!h) { set_error("null handle"); return -1; }

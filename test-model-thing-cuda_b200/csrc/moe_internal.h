@@ -31,6 +31,9 @@ struct Profiler {
 };
 }  // namespace tmt
 
+constexpr int kGemmCycLaunches = 16;   // GEMM launches whose cycle counters are kept (a ring)
+constexpr int kGemmCycCtas = 160;
+
 struct tmt_moe {
     tmt_moe_desc d{};
     cudaStream_t stream = nullptr;
@@ -42,6 +45,7 @@ struct tmt_moe {
     const int* g_poff = nullptr; const int* g_num_m_tiles = nullptr; const int* g_tile_expert = nullptr; int g_max_tiles = 0;
     long gcap = 0;      // rows of the grouped GEMM buffers
     bool two_cta = false; bool tensor_core = true; int gemm_dbg = 0;
+    long long* gemm_cyc = nullptr; int cyc_slot = 0;   // measurement only: cycle counters of the last kGemmCycLaunches GEMM launches
     int pad = 128;      // group padding (rows)
     int x_cap = 0;
     float* bias = nullptr;

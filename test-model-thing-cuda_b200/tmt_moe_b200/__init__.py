@@ -26,6 +26,7 @@ EXPORTS = (
     "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init", "tmt_moe_set_profile",
     "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name", "tmt_moe_ep_plan",
     "tmt_moe_copy_stats", "tmt_moe_selftest_bounded_wait", "tmt_moe_router_dw_noalloc",
+    "tmt_moe_debug_gemm_cycles",
 )
 
 
@@ -217,6 +218,18 @@ class MoE:
         cnt = (ctypes.c_longlong * n)()
         _check(self.lib.tmt_moe_profile(self.h, ms, cnt, int(reset)), self.lib)
         return {self.lib.tmt_moe_phase_name(i).decode(): (ms[i], cnt[i]) for i in range(n) if cnt[i]}
+
+    def gemm_cycles(self):
+        """Measurement only (TMT_MOE_GEMM_CYCLES=1 at creation): (launches so far, array
+        [ring slot][cta][counter]) of the per-role cycle counters of the last GEMM launches."""
+        import numpy as np
+        a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        self.lib.tmt_moe_debug_gemm_cycles(self.h, None, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+        out = np.zeros((a.value, b.value, c.value), np.int64)
+        n = self.lib.tmt_moe_debug_gemm_cycles(self.h, out.ctypes.data_as(ctypes.c_void_p), None, None, None)
+        if n < 0:
+            raise MoeError(self.lib.tmt_moe_last_error().decode())
+        return n, out
 
     @property
     def launch_count(self):
