@@ -3,7 +3,7 @@
 // persistent over 128x256 tiles.
 //
 // Warp roles: warp 0 and the last warp = TMA producers (even / odd pipeline stages), warp 1 = TMEM
-// allocator and MMA issuer (one lane), warps 2..5 (2..9) = epilogue (each owns the 32 TMEM lanes
+// allocator and MMA issuer (the whole warp runs the loop, one elected lane issues), warps 2..5 (2..9) = epilogue (each owns the 32 TMEM lanes
 // warp_id % 4). Two producers because a TMA load instruction keeps its warp busy for about 300
 // cycles (measured), so one warp could not start a 48 KB stage every 512 cycles.
 // Two 256-column accumulators in TMEM let the epilogue of tile i run under the MMAs of tile
@@ -174,51 +174,60 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---------------- MMA issuer ----------------
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
-                                   ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-            const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor units of 16 B per k = 16
-            const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
-            int s = 0; uint32_t ph = 0;
-            int acc = 0; uint32_t acc_ph = 0;
-            bool ok = true;
-            const bool prof = p.cyc != nullptr;
-            long long c_full = 0, c_issue = 0, c_acc = 0, t0 = 0, t1 = 0;
-            const long long t_start = prof ? clock64() : 0;
-            for (int t = blockIdx.x; ok; t += gridDim.x) {
-                TileInfo ti;
-                if (!get_tile_nkb(p, t, m_tiles, n_tiles, ti.nkb)) break;
+        // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop and one elected lane issues: with uniform control flow the descriptors and
+        // barrier addresses stay in uniform registers, and a barrier wait costs the warp about 110 cycles; the same
+        // loop run by a single lane inside a divergent branch was measured at about 370 cycles per wait.
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
+                               ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+        const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor units of 16 B per k = 16
+        const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+        int s = 0; uint32_t ph = 0;
+        int acc = 0; uint32_t acc_ph = 0;
+        bool ok = true;
+        const bool prof = p.cyc != nullptr;
+        long long c_full = 0, c_issue = 0, c_acc = 0, t0 = 0, t1 = 0;
+        const long long t_start = prof ? clock64() : 0;
+        for (int t = blockIdx.x; ok; t += gridDim.x) {
+            TileInfo ti;
+            if (!get_tile_nkb(p, t, m_tiles, n_tiles, ti.nkb)) break;
+            if (prof) t0 = clock64();
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status));
+            if (!ok) break;
+            if (prof) c_acc += clock64() - t0;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * kBN;
+            for (int kb = 0; kb < ti.nkb; ++kb) {
                 if (prof) t0 = clock64();
-                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status)) break;
-                if (prof) c_acc += clock64() - t0;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * kBN;
-                for (int kb = 0; kb < ti.nkb; ++kb) {
-                    if (prof) t0 = clock64();
-                    if (!(s & 1) && !(p.dbg & 64)) {          // both stages of the pair (s, s+1) have landed once this barrier completes
-                        if (!mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status)) { ok = false; break; }
-                        tc_fence_after();
-                    }
-                    if (prof) t1 = clock64();
-                    const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
-                    const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
+                if (!(s & 1) && !(p.dbg & 64)) {          // both stages of the pair (s, s+1) have landed once this barrier completes
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status));
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (prof) t1 = clock64();
+                const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
+                const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
+                if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
                         if (!(p.dbg & 2)) tc_mma(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
                     if (!(p.dbg & 128)) tc_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs have read it
-                    if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
-                    if (++s == kStages) { s = 0; ph ^= 1; }
                 }
-                if (!ok) break;
+                __syncwarp();
+                if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
+                if (++s == kStages) { s = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            if (elect_one()) {
                 if (ti.nkb > 0) tc_commit(smem_u32(&tfull_bar[acc]));   // accumulator complete
                 else mbar_arrive(smem_u32(&tfull_bar[acc]));            // empty group: nothing to wait for
-                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
-            if (prof) {
-                long long* c = p.cyc + blockIdx.x * kCycSlots;
-                c[kCycMmaWaitFull] = c_full; c[kCycMmaIssue] = c_issue; c[kCycMmaWaitAcc] = c_acc; c[kCycTotal] = clock64() - t_start;
-            }
+            __syncwarp();
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+        if (prof && lane == 0) {
+            long long* c = p.cyc + blockIdx.x * kCycSlots;
+            c[kCycMmaWaitFull] = c_full; c[kCycMmaIssue] = c_issue; c[kCycMmaWaitAcc] = c_acc; c[kCycTotal] = clock64() - t_start;
         }
         __syncwarp();
     } else {

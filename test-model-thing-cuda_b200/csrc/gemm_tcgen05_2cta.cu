@@ -226,8 +226,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0 && leader) {
-            // ---------------- MMA issuer (leader CTA only) ----------------
+        if (leader) {
+            // ---------------- MMA issuer (leader CTA only): the whole warp runs the loop, one elected lane issues ----------------
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
                                    ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
             const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
@@ -242,35 +242,43 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                 Tile2 ti;
                 if (!get_tile2_nkb(p, t, m_pairs, n_tiles, ti.nkb)) break;
                 if (prof) t0 = clock64();
-                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status)) break;
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1, abort_flag, p.status));
+                if (!ok) break;
                 if (prof) c_acc += clock64() - t0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int kb = 0; kb < ti.nkb; ++kb) {
                     if (prof) t0 = clock64();
                     if (!(s & 1) && !(p.dbg & 64)) {          // both stages of the pair (s, s+1), in both CTAs, have landed once this barrier completes
-                        if (!mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status)) { ok = false; break; }
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status));
+                        if (!ok) break;
                         tc_fence_after();
                     }
                     if (prof) t1 = clock64();
                     const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
                     const uint64_t da = make_desc(sa, p.a_mn, 8192), db = make_desc(sb, p.b_mn, 8192);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k)
-                        if (!(p.dbg & 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
-                    if ((s & 1) && !(p.dbg & 128)) tc_commit_pair(smem_u32(&empty_bar[s >> 1]));    // releases stages s-1 and s in both CTAs
+                        for (int k = 0; k < kBK / 16; ++k)
+                            if (!(p.dbg & 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                        if ((s & 1) && !(p.dbg & 128)) tc_commit_pair(smem_u32(&empty_bar[s >> 1]));    // releases stages s-1 and s in both CTAs
+                    }
+                    __syncwarp();
                     if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
                     if (++s == kStages2) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
-                if (ti.nkb > 0) tc_commit_pair(smem_u32(&tfull_bar[acc]));
-                else {                       // empty group: nothing to wait for, release both epilogues
-                    mbar_arrive(smem_u32(&tfull_bar[acc]));
-                    mbar_arrive_cluster(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+                if (elect_one()) {
+                    if (ti.nkb > 0) tc_commit_pair(smem_u32(&tfull_bar[acc]));
+                    else {                       // empty group: nothing to wait for, release both epilogues
+                        mbar_arrive(smem_u32(&tfull_bar[acc]));
+                        mbar_arrive_cluster(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+                    }
                 }
+                __syncwarp();
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
-            if (prof) {
+            if (prof && lane == 0) {
                 long long* c = p.cyc + blockIdx.x * kCycSlots;
                 c[kCycMmaWaitFull] = c_full; c[kCycMmaIssue] = c_issue; c[kCycMmaWaitAcc] = c_acc; c[kCycTotal] = clock64() - t_start;
             }
