@@ -206,7 +206,7 @@ def main():
     ap.add_argument("--gemm-cycles", action="store_true",
                     help="measurement only: print (stderr) where the TMA, MMA and epilogue threads of the last GEMM launches spent their cycles")
     ap.add_argument("--gemm", default="2cta", choices=["2cta", "1cta"],
-                    help="grouped GEMM kernel: one CTA per 128x256 tile (default, measured 1-2 %% faster) or CTA pairs on 256x256 tiles")
+                    help="grouped GEMM kernel: CTA pairs on 256x256 tiles (default) or one CTA per 128x256 tile")
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows move by peer loads/stores inside the gather/scatter kernels, or by NCCL send/recv")
     args = ap.parse_args()
