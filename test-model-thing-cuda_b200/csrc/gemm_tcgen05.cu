@@ -23,10 +23,11 @@ constexpr int kStages = 4;
 constexpr int kATile = kBM * kBK * 2;   // 16 KB
 constexpr int kBTile = kBN * kBK * 2;   // 32 KB
 constexpr int kStageBytes = kATile + kBTile;
-// Epilogue warps per CTA: 4 (one per TMEM lane quarter, 256 columns each) or, for the epilogue that
-// also reads the saved pre-activation (measured: that one is latency-bound), 8 (two per quarter, 128
-// columns each). Threads = TMA warp + MMA warp + epilogue warps + second TMA warp.
-template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiDh ? 8 : 4; }
+// Epilogue warps per CTA: 8 for the bf16 epilogues (two groups of four, one warp per TMEM lane quarter, 128 columns
+// per group: TMEM load -> math -> staging is latency-bound, and with four warps it took longer than the MMAs of a
+// K = 2048 tile), 4 for the fp32 one (its tiles have long reductions). Threads = TMA warp + MMA warp + epilogue
+// warps + second TMA warp.
+template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiF32 ? 4 : 8; }
 template <int EPI> __host__ __device__ constexpr int block_threads() { return 96 + 32 * epi_warps<EPI>(); }
 constexpr uint32_t kTmemCols = 512;     // two fp32 accumulators of 256 columns
 

@@ -7,16 +7,15 @@
 // Protocol. Both CTAs run two TMA producer warps (warp 0: even stages, last warp: odd stages; a TMA load
 // instruction keeps its warp busy for about 300 cycles) for their own tiles and signal the LEADER's
 // (cluster rank 0) "full" barrier; the leader's warp 1 issues the MMAs and commits to the
-// "empty" and "accumulator full" barriers of BOTH CTAs (one tcgen05.commit per CTA); the
+// "empty" and "accumulator full" barriers of BOTH CTAs; the
 // epilogue warps of both CTAs drain their own 128 TMEM lanes and arrive on the leader's
 // "accumulator empty" barrier. Every TMA load has exactly one destination CTA. Waits are bounded as in the single-CTA
 // kernel; both CTAs always reach the closing cluster barrier before TMEM is freed.
 //
-// Pipeline stages are filled and released in PAIRS: one "full" and one "empty" barrier cover two
-// consecutive stages, so the MMA thread waits once and commits once (two instructions, one per
-// CTA) per 8 MMAs. Measured on a B200: any shared-memory read by the thread that issues tcgen05.mma
-// costs it about 370 cycles and a commit about 85, so with a wait and a commit pair per 4 MMAs (512
-// tensor-pipe cycles) the thread, not the pipe, sets the pace. The epilogue is the shared
+// Pipeline stages are filled in PAIRS: one "full" barrier covers two consecutive stages, so the MMA
+// warp waits once per 8 MMAs (a wait costs it 110-370 cycles, measured, and with one per 4 MMAs the
+// issuing warp, not the tensor pipe, set the pace). Stages are released one by one: a single
+// tcgen05.commit whose mask names both CTAs arrives on the stage's "empty" barrier in each of them. The epilogue is the shared
 // one (staged in shared memory, written with TMA stores).
 //
 // Needs every group padded to 256 rows so that the two 128-row halves of a tile belong to one
@@ -32,10 +31,11 @@ constexpr int kStages2 = 6;                     // three pairs
 constexpr int kATile2 = kBM * kBK * 2;          // 16 KB: this CTA's 128 rows
 constexpr int kBTile2 = (kBN / 2) * kBK * 2;    // 16 KB: this CTA's 128 of the 256 columns
 constexpr int kStageBytes2 = kATile2 + kBTile2;
-// Epilogue warps per CTA: 4 (one per TMEM lane quarter, 256 columns each) or, for the epilogue that
-// also reads the saved pre-activation (measured: that one is latency-bound), 8 (two per quarter, 128
-// columns each). Threads = TMA warp + MMA warp + epilogue warps + second TMA warp.
-template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiDh ? 8 : 4; }
+// Epilogue warps per CTA: 8 for the bf16 epilogues (two groups of four, one warp per TMEM lane quarter, 128 columns
+// per group: TMEM load -> math -> staging is latency-bound, and with four warps it took longer than the MMAs of a
+// K = 2048 tile), 4 for the fp32 one (its tiles have long reductions). Threads = TMA warp + MMA warp + epilogue
+// warps + second TMA warp.
+template <int EPI> __host__ __device__ constexpr int epi_warps() { return EPI == kEpiF32 ? 4 : 8; }
 template <int EPI> __host__ __device__ constexpr int block_threads() { return 96 + 32 * epi_warps<EPI>(); }
 constexpr uint32_t kTmemCols2 = 512;
 
@@ -74,13 +74,11 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t da, uint64
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
-// Arrives on the barrier at the same shared-memory offset in both CTAs of the pair once the MMAs
-// issued so far are done: one commit on the leader's own barrier, one on the peer's (addressed
-// through the cluster window).
+// Arrives on the barrier at the same shared-memory offset in both CTAs of the pair once the MMAs issued so far are
+// done (one instruction; the mask names both CTAs of the cluster).
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    const uint32_t peer = map_to_cta(bar, 1);
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 
 struct Tile2 {
@@ -127,7 +125,7 @@ __device__ __forceinline__ bool get_tile2_nkb(const GemmParams& p, int t, int m_
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[kStages2 / 2], empty_bar[kStages2 / 2], tfull_bar[2], tempty_bar[2], group_bar[2];
+    __shared__ uint64_t full_bar[kStages2 / 2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2], group_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -139,7 +137,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
 
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < kStages2 / 2; ++s) { mbar_init(smem_u32(&full_bar[s]), 2); mbar_init(smem_u32(&empty_bar[s]), 1); }   // full: one leader arrival per stage
+        for (int s = 0; s < kStages2 / 2; ++s) mbar_init(smem_u32(&full_bar[s]), 2);    // one leader arrival per stage of the pair
+        for (int s = 0; s < kStages2; ++s) mbar_init(smem_u32(&empty_bar[s]), 1);
         for (int a = 0; a < 2; ++a) mbar_init(smem_u32(&group_bar[a]), 4);
         for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 2 * epi_warps<EPI>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -184,7 +183,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                 const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
                 if (lane == 0) {
                     if (prof) t0 = clock64();
-                    ok = mbar_wait(smem_u32(&empty_bar[s >> 1]), ph ^ 1, abort_flag, p.status);   // the pair (s, s+1) is free
+                    ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status);
                     if (prof) t1 = clock64();
                     if (ok && leader) mbar_expect_tx(fb_local, (p.dbg & 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
                 }
@@ -210,7 +209,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
         }
         // An odd number of k blocks leaves the last pair's barrier one arrival short: the leader's odd producer supplies it,
         // after the same wait a real load of that stage would make (the barrier must have left its previous phase first).
-        if (ok && leader && lane == 0 && (s & 1) && my == 1 && mbar_wait(smem_u32(&empty_bar[s >> 1]), ph ^ 1, abort_flag, p.status))
+        if (ok && leader && lane == 0 && (s & 1) && my == 1 && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status))
             mbar_expect_tx(smem_u32(&full_bar[s >> 1]), 0);
         if (prof && lane == 0) {
             p.cyc[blockIdx.x * kCycSlots + kCycProdWaitEmpty] = c_wait;
@@ -261,7 +260,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
 #pragma unroll
                         for (int k = 0; k < kBK / 16; ++k)
                             if (!(p.dbg & 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
-                        if ((s & 1) && !(p.dbg & 128)) tc_commit_pair(smem_u32(&empty_bar[s >> 1]));    // releases stages s-1 and s in both CTAs
+                        if (!(p.dbg & 128)) tc_commit_pair(smem_u32(&empty_bar[s]));    // releases stage s in both CTAs
                     }
                     __syncwarp();
                     if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }

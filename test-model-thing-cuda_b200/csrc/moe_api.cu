@@ -56,10 +56,10 @@ EncodeTiledFn encode_fn() {
 void make_out_map(CUtensorMap* m, const void* base, bool f32, uint64_t inner, uint64_t rows) {
     cuuint64_t dims[2] = {inner, rows};
     cuuint64_t strides[1] = {inner * (f32 ? 4u : 2u)};
-    cuuint32_t box[2] = {f32 ? 32u : 64u, 128u};         // 128 bytes x 128 rows
+    cuuint32_t box[2] = {32u, 128u};                     // fp32: 128 bytes x 128 rows (128-byte swizzle); bf16: 64 bytes x 128 rows (64-byte swizzle)
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode_fn()(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
-                             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed for an output map (" + std::to_string((int)r) + ")");
 }
