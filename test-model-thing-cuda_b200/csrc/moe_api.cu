@@ -447,7 +447,7 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
 // width read as zero) and the split table is fixed.
 void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order) {
     h->ep_x_token_order = token_order;
-    if (h->d.gemm_impl != TMT_MOE_GEMM_TCGEN05 || !h->dl_t) return;
+    if (!h->tensor_core || !h->dl_t) return;      // both tcgen05 kernels read these maps; the SIMT cross-check path does not
     const uint64_t tpad = (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
     CUtensorMap m[2];
     memset(m, 0, sizeof m);

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q, transport):
+def _worker(rank, world, port, q, transport, gemm_impl=0):
     try:
         sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -37,7 +37,7 @@ def _worker(rank, world, port, q, transport):
         mine = dict(base, X=data[rank]["X"], dY=data[rank]["dY"],
                     Wup=base["Wup"][rank * EL:(rank + 1) * EL], Wdown=base["Wdown"][rank * EL:(rank + 1) * EL])
         moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32, training=True, device=rank, ep_world=world, ep_rank=rank,
-                    ep_capacity_factor=2.0, ep_transport=transport)
+                    ep_capacity_factor=2.0, ep_transport=transport, gemm_impl=gemm_impl)
         moe.ep_init_torch(dist)
         X, dY, Wr = G.dev(mine["X"]), G.dev(mine["dY"]), G.dev(mine["Wr"])
         Wup_all, Wdown_all = G.dev(mine["Wup"]), G.dev(mine["Wdown"])
@@ -77,13 +77,14 @@ def _worker(rank, world, port, q, transport):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport", [pytest.param(0, id="peer"), pytest.param(1, id="nccl")])
-def test_expert_parallel_two_gpus(transport):
+@pytest.mark.parametrize("transport,gemm_impl", [pytest.param(0, 0, id="peer"), pytest.param(1, 0, id="nccl"),
+                                                 pytest.param(0, 2, id="peer-cta_pairs"), pytest.param(1, 2, id="nccl-cta_pairs")])
+def test_expert_parallel_two_gpus(transport, gemm_impl):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 200 + 7 * transport
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport)) for r in range(world)]
+    port = 29700 + os.getpid() % 200 + 7 * transport + 17 * gemm_impl
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport, gemm_impl)) for r in range(world)]
     for p in procs:
         p.start()
     res = []
