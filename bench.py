@@ -440,7 +440,7 @@ def main():
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 # dram read + write per launch, averaged over the six launches: ncu capture at 32768 tokens scaled to
                 # the full token count (activations x 4, weights fixed), profiles/step_kernels_config5_32k_tokens.md
-                "traffic": 5.8e9 if (args.config == "c5" and not args.tokens and world == 1) else None,
+                "traffic": 6.1e9 if (args.config == "c5" and not args.tokens and world == 1) else None,
                 "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
                 "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}
     if cfg.get("nvfp4"):
