@@ -100,6 +100,17 @@ int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const
                       const void* const* Wup, const void* const* Wdown, float* dWrouter,
                       float* const* dWup, float* const* dWdown, void* Y_host, void* dX_host,
                       float* stat_host, float beta, float aux, float zcoef, int tokens);
+/* The same step without the final synchronisation: the call returns once everything is queued. Uploads of
+ * the next step start as soon as this step has consumed the staging buffers (under its GEMMs) and downloads
+ * run under the following compute, so back-to-back calls keep PCIe busy in both directions while the GPU
+ * computes. The host buffers must stay valid (and Y_host / dX_host / stat_host unread) until
+ * tmt_moe_host_wait returns. No counterpart in the reference (its trainer keeps all data on the device). */
+int tmt_moe_step_host_async(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter,
+                      const void* const* Wup, const void* const* Wdown, float* dWrouter,
+                      float* const* dWup, float* const* dWdown, void* Y_host, void* dX_host,
+                      float* stat_host, float beta, float aux, float zcoef, int tokens);
+/* Waits for every host step queued so far (uploads, compute, downloads). */
+int tmt_moe_host_wait(tmt_moe* h);
 
 /* Copies saved routing state to HOST memory (synchronises). The reference exposes the same
  * tensors as MoeKeep fields (moe.cu:294-315). name is one of

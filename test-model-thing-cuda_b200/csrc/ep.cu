@@ -34,6 +34,9 @@
 struct tmt_ep_state {
     void* lib = nullptr;
     ncclComm_t comm = nullptr;
+    // second stream of the peer transport: rank barriers and row transfers that run under GEMMs of the main stream
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int G = 1, r = 0, EL = 0;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
@@ -182,6 +185,11 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         const int E = h->d.experts, D = h->d.dim;
         const size_t cap = h->dims.cap;
         ep->peer = h->d.ep_transport == TMT_MOE_EP_PEER;
+        if (ep->peer) {
+            CKE(cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking));
+            CKE(cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming));
+            CKE(cudaEventCreateWithFlags(&ep->ev_join, cudaEventDisableTiming));
+        }
         ep->Yr = ep_alloc<uint16_t>(h, cap * D);
         ep->bar_word = ep_alloc<int>(h, 1);
         CKE(cudaMemsetAsync(ep->bar_word, 0, sizeof(int), h->stream));
@@ -248,6 +256,9 @@ namespace tmt {
 void ep_teardown(tmt_moe* h) {
     if (!h->ep) return;
     for (void* p : h->ep->opened) cudaIpcCloseMemHandle(p);
+    if (h->ep->side) cudaStreamDestroy(h->ep->side);
+    if (h->ep->ev_fork) cudaEventDestroy(h->ep->ev_fork);
+    if (h->ep->ev_join) cudaEventDestroy(h->ep->ev_join);
     if (h->ep->comm && h->ep->CommDestroy) h->ep->CommDestroy(h->ep->comm);
     delete h->ep;
     h->ep = nullptr;
@@ -330,9 +341,9 @@ void exchange(tmt_moe* h, bool to_experts, const uint16_t* src, uint16_t* dst, i
 }
 
 // Stream-ordered meeting point of all ranks: when it completes here, every rank's stream has reached it.
-void rank_barrier(tmt_moe* h) {
+void rank_barrier(tmt_moe* h, cudaStream_t stream = nullptr) {
     tmt_ep_state* ep = h->ep;
-    NC(ep, ep->AllReduce(ep->bar_word, ep->bar_word, 1, ncclInt32, ncclSum, ep->comm, h->stream));
+    NC(ep, ep->AllReduce(ep->bar_word, ep->bar_word, 1, ncclInt32, ncclSum, ep->comm, stream ? stream : h->stream));
     h->launches += 1;
 }
 
@@ -416,11 +427,23 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
         h->launches += 1;
         prof_mark(h, kPhExchange);
         rank_barrier(h);
-        expert_backward(h, Wup, Wdown, dWup, dWdown);
-        prof_mark(h, kPhExchange);
-        rank_barrier(h);
+        // Input-gradient products first; then the rows of dXg travel back (rank barrier + scatter on the side stream)
+        // while the main stream computes the weight gradients, which need nothing from other ranks. Those two GEMM
+        // launches leave two SMs free so that the barrier's kernel can start while they run.
+        expert_backward(h, Wup, Wdown, dWup, dWdown, 1);
         router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
-                        (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg));
+                        (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg), /*defer_scatter=*/true);
+        CKE(cudaEventRecord(ep->ev_fork, h->stream));
+        CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+        rank_barrier(h, ep->side);          // every rank's dXg is complete
+        scatter_rows(h, Wr, h->dXg, static_cast<uint16_t*>(dX), ep->side, peer_map(h, ep->peer_dXg));
+        CKE(cudaEventRecord(ep->ev_join, ep->side));
+        struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
+        h->sm_limit = h->num_sms - 2;
+        expert_backward(h, Wup, Wdown, dWup, dWdown, 2);
+        h->sm_limit = 0;
+        prof_mark(h, kPhScatter);
+        CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
     } else {
         CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
         h->launches += 1;

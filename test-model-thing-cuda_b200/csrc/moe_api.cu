@@ -264,8 +264,9 @@ GemmParams red_gemm(tmt_moe* h, ActMap a, const uint16_t* A, int M, ActMap b, co
 }
 
 void run_tc(tmt_moe* h, const GemmParams& p) {
-    if (h->two_cta) CK(launch_gemm_tcgen05_2cta(p, h->num_sms, h->stream));
-    else CK(launch_gemm_tcgen05(p, h->num_sms, h->stream));
+    const int sms = h->sm_limit > 0 ? std::min(h->sm_limit, h->num_sms) : h->num_sms;
+    if (h->two_cta) CK(launch_gemm_tcgen05_2cta(p, sms, h->stream));
+    else CK(launch_gemm_tcgen05(p, sms, h->stream));
 }
 
 void run_gemm(tmt_moe* h, const GemmParams& p0) {
@@ -326,6 +327,7 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
     prof_mark(h, kPhDispatch);
     CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream));
     h->launches += 1;
+    if (h->host_hooks) CK(cudaEventRecord(h->host_ev[tmt_moe::kEvXFree], h->stream));      // X has been read for the last time
 }
 
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
@@ -388,39 +390,47 @@ void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* 
 
 // The four (reference mode: two) grouped gradient products over the rows in h->dYg.
 void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup,
-                     float* const* dWdown) {
+                     float* const* dWdown, int which) {
     const int D = h->d.dim, H = h->d.hidden;
     refresh_weights(h, Wup, Wdown);
     refresh_grads(h, dWup, dWdown);
     if (H > 0) {
-        GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
-        dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
-        dh.mapC0 = h->act_maps + kOutDP;
-        prof_mark(h, kPhGemmDh);
-        run_gemm(h, dh);
-        prof_mark(h, kPhGemmDwDown);
-        GemmParams gd = red_gemm(h, kDYgMN, h->dYg, D, kHactMN, h->Hact, H, h->gdown_ptrs);
-        gd.mapC0 = h->g_maps + h->local_experts; gd.c_stride = 1;
-        run_gemm(h, gd);
-        prof_mark(h, kPhGemmDwUp);
-        GemmParams gu = red_gemm(h, kDPMN, h->dP, H, kXgMN, h->Xg, D, h->gup_ptrs);
-        gu.mapC0 = h->g_maps; gu.c_stride = 1;
-        run_gemm(h, gu);
-        GemmParams dx = rows_gemm(h, kDPK, h->dP, kUpMN, h->up_ptrs, true, D, H, kEpiBf16);
-        dx.out0 = h->dXg;
-        dx.mapC0 = h->act_maps + kOutDXg;
-        prof_mark(h, kPhGemmDx);
-        run_gemm(h, dx);
+        if (which & 1) {
+            GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
+            dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
+            dh.mapC0 = h->act_maps + kOutDP;
+            prof_mark(h, kPhGemmDh);
+            run_gemm(h, dh);
+            GemmParams dx = rows_gemm(h, kDPK, h->dP, kUpMN, h->up_ptrs, true, D, H, kEpiBf16);
+            dx.out0 = h->dXg;
+            dx.mapC0 = h->act_maps + kOutDXg;
+            prof_mark(h, kPhGemmDx);
+            run_gemm(h, dx);
+        }
+        if (which & 2) {
+            prof_mark(h, kPhGemmDwDown);
+            GemmParams gd = red_gemm(h, kDYgMN, h->dYg, D, kHactMN, h->Hact, H, h->gdown_ptrs);
+            gd.mapC0 = h->g_maps + h->local_experts; gd.c_stride = 1;
+            run_gemm(h, gd);
+            prof_mark(h, kPhGemmDwUp);
+            GemmParams gu = red_gemm(h, kDPMN, h->dP, H, kXgMN, h->Xg, D, h->gup_ptrs);
+            gu.mapC0 = h->g_maps; gu.c_stride = 1;
+            run_gemm(h, gu);
+        }
     } else {
-        prof_mark(h, kPhGemmDwUp);
-        GemmParams gu = red_gemm(h, kDYgMN, h->dYg, D, kXgMN, h->Xg, D, h->gup_ptrs);
-        gu.mapC0 = h->g_maps; gu.c_stride = 1;
-        run_gemm(h, gu);
-        GemmParams dx = rows_gemm(h, kDYgK, h->dYg, kUpMN, h->up_ptrs, true, D, D, kEpiBf16);
-        dx.out0 = h->dXg;
-        dx.mapC0 = h->act_maps + kOutDXg;
-        prof_mark(h, kPhGemmDx);
-        run_gemm(h, dx);
+        if (which & 1) {
+            GemmParams dx = rows_gemm(h, kDYgK, h->dYg, kUpMN, h->up_ptrs, true, D, D, kEpiBf16);
+            dx.out0 = h->dXg;
+            dx.mapC0 = h->act_maps + kOutDXg;
+            prof_mark(h, kPhGemmDx);
+            run_gemm(h, dx);
+        }
+        if (which & 2) {
+            prof_mark(h, kPhGemmDwUp);
+            GemmParams gu = red_gemm(h, kDYgMN, h->dYg, D, kXgMN, h->Xg, D, h->gup_ptrs);
+            gu.mapC0 = h->g_maps; gu.c_stride = 1;
+            run_gemm(h, gu);
+        }
     }
 }
 
@@ -435,6 +445,7 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
     prof_mark(h, kPhGradDispatch);
     CK(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), h->Yg, h->dYg, h->s_j, H == 0 ? 1 : 0, h->stream));
     h->launches += 1;
+    if (h->host_hooks) CK(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], h->stream));     // dY has been read for the last time
     expert_backward(h, Wup, Wdown, dWup, dWdown);
     router_backward(h, Wr, H > 0 ? h->sw_part : nullptr, h->Xg, false, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef,
                     h->rb.counts, (long)h->dims.T);
@@ -467,7 +478,7 @@ void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order) {
 
 void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uint16_t* grouped_x, bool x_is_ep,
                      const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm,
-                     PeerMap pm) {
+                     PeerMap pm, bool defer_scatter) {
     const bool tok_order = x_is_ep && h->ep_x_token_order;
     const int D = h->d.dim, E = h->d.experts;
     if (E == 1) {      // dense shortcut: no router gradient (moe.cu:488-494)
@@ -536,10 +547,16 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
         p.epi = kEpiBf16; p.out0 = h->dXr; p.ldc = D;
         p.mapC0 = h->act_maps + kOutDXr;
         run_tc(h, p);
+        h->launches += 1;
+        if (defer_scatter) return;
         prof_mark(h, kPhScatter);
-        CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->dXr, dX, h->stream, pm));
-        h->launches += 2;
+        scatter_rows(h, Wr, dXg_rows, dX, h->stream, pm);
     }
+}
+
+void scatter_rows(tmt_moe* h, const void* Wr, const uint16_t* dXg_rows, uint16_t* dX, cudaStream_t stream, PeerMap pm) {
+    CK(launch_scatter(h->dims, h->rb, h->dlogits, Wr, dXg_rows, h->tensor_core ? h->dXr : nullptr, dX, stream, pm));
+    h->launches += 1;
 }
 
 tmt_moe* create_impl(const tmt_moe_desc* dsc) {
@@ -659,10 +676,9 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->g_poff = b.poff; h->g_num_m_tiles = b.num_m_tiles; h->g_tile_expert = b.tile_expert; h->g_max_tiles = h->dims.max_tiles;
     if (h->tensor_core) build_act_maps(h);
     if (d.host_io) {
-        CK(cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
-        CK(cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming));
-        CK(cudaEventCreateWithFlags(&h->ev_dy, cudaEventDisableTiming));
-        CK(cudaEventCreateWithFlags(&h->ev_fwd, cudaEventDisableTiming));
+        CK(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+        CK(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+        for (cudaEvent_t& e : h->host_ev) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         h->Xs = dalloc<uint16_t>(h, (size_t)T * D);
         h->Ys = dalloc<uint16_t>(h, (size_t)T * D);
         if (d.training) {
@@ -699,8 +715,8 @@ void tmt_moe_destroy(tmt_moe* h) {
     cudaStreamSynchronize(h->stream);
     ep_teardown(h);
     for (cudaEvent_t e : h->prof.pool) cudaEventDestroy(e);
-    if (h->copy_stream) { cudaStreamSynchronize(h->copy_stream); cudaStreamDestroy(h->copy_stream); }
-    for (cudaEvent_t e : {h->ev_start, h->ev_dy, h->ev_fwd}) if (e) cudaEventDestroy(e);
+    for (cudaStream_t st : {h->in_stream, h->out_stream}) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+    for (cudaEvent_t e : h->host_ev) if (e) cudaEventDestroy(e);
     for (void* p : h->allocs) cudaFree(p);
     delete h;
 }
@@ -767,9 +783,9 @@ int tmt_moe_copy_stats(tmt_moe* h, float* stat_device) {
     })
 }
 
-int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter, const void* const* Wup,
-                      const void* const* Wdown, float* dWrouter, float* const* dWup, float* const* dWdown, void* Y_host,
-                      void* dX_host, float* stat_host, float beta, float aux, float zcoef, int tokens) {
+int tmt_moe_step_host_async(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter, const void* const* Wup,
+                            const void* const* Wdown, float* dWrouter, float* const* dWup, float* const* dWdown, void* Y_host,
+                            void* dX_host, float* stat_host, float beta, float aux, float zcoef, int tokens) {
     if (!h) { set_error("null handle"); return -1; }
     GUARD({
         if (!h->Xs) throw std::runtime_error("handle was created with host_io = 0");
@@ -778,32 +794,63 @@ int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const
         check_tokens(h, tokens);
         CK(cudaSetDevice(h->d.device));
         const size_t bytes = (size_t)tokens * h->d.dim * 2;
-        // The gradient upload runs on a second stream under the forward pass and the output download under
-        // the backward pass (PCIe is full duplex); the compute stream only waits for what it consumes.
         const bool bwd = dY_host != nullptr;
         if (bwd && (!dX_host || !h->dYs)) throw std::runtime_error("backward needs dX_host and training = 1");
-        CK(cudaEventRecord(h->ev_start, h->stream));
+        // Three streams. Uploads wait only until the previous step has consumed the staging buffer (X: after its
+        // dispatch, dY: after its gradient dispatch), so they run under the previous step's GEMMs; downloads run under
+        // the next phase of compute; the compute stream waits for exactly what it consumes or overwrites. PCIe carries
+        // both directions at once. (Waiting on an event that was never recorded returns at once: first step.)
+        cudaEvent_t* ev = h->host_ev;
+        CK(cudaStreamWaitEvent(h->in_stream, ev[tmt_moe::kEvXFree], 0));
+        CK(cudaMemcpyAsync(h->Xs, X_host, bytes, cudaMemcpyHostToDevice, h->in_stream));
+        CK(cudaEventRecord(ev[tmt_moe::kEvXReady], h->in_stream));
         if (bwd) {
-            CK(cudaStreamWaitEvent(h->copy_stream, h->ev_start, 0));     // the previous step no longer reads dYs
-            CK(cudaMemcpyAsync(h->dYs, dY_host, bytes, cudaMemcpyHostToDevice, h->copy_stream));
-            CK(cudaEventRecord(h->ev_dy, h->copy_stream));
+            CK(cudaStreamWaitEvent(h->in_stream, ev[tmt_moe::kEvDyFree], 0));
+            CK(cudaMemcpyAsync(h->dYs, dY_host, bytes, cudaMemcpyHostToDevice, h->in_stream));
+            CK(cudaEventRecord(ev[tmt_moe::kEvDyReady], h->in_stream));
         }
-        CK(cudaMemcpyAsync(h->Xs, X_host, bytes, cudaMemcpyHostToDevice, h->stream));
+        CK(cudaStreamWaitEvent(h->stream, ev[tmt_moe::kEvXReady], 0));
+        CK(cudaStreamWaitEvent(h->stream, ev[tmt_moe::kEvYOut], 0));        // the previous Y has left Ys
         if (beta != 0.0f) CK(cudaMemcpyAsync(h->Ys, Y_host, bytes, cudaMemcpyHostToDevice, h->stream));
+        h->host_hooks = true;
+        struct Off { tmt_moe* h; ~Off() { h->host_hooks = false; } } off{h};
         forward_impl(h, h->Xs, Wrouter, Wup, Wdown, h->Ys, beta, tokens);
-        CK(cudaEventRecord(h->ev_fwd, h->stream));
-        CK(cudaStreamWaitEvent(h->copy_stream, h->ev_fwd, 0));
-        CK(cudaMemcpyAsync(Y_host, h->Ys, bytes, cudaMemcpyDeviceToHost, h->copy_stream));
+        CK(cudaEventRecord(ev[tmt_moe::kEvYWritten], h->stream));
+        CK(cudaStreamWaitEvent(h->out_stream, ev[tmt_moe::kEvYWritten], 0));
+        CK(cudaMemcpyAsync(Y_host, h->Ys, bytes, cudaMemcpyDeviceToHost, h->out_stream));
         if (stat_host)
-            CK(cudaMemcpyAsync(stat_host, h->rb.stat, (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->copy_stream));
+            CK(cudaMemcpyAsync(stat_host, h->rb.stat, (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->out_stream));
+        CK(cudaEventRecord(ev[tmt_moe::kEvYOut], h->out_stream));
         if (bwd) {
-            CK(cudaStreamWaitEvent(h->stream, h->ev_dy, 0));
+            CK(cudaStreamWaitEvent(h->stream, ev[tmt_moe::kEvDyReady], 0));
+            CK(cudaStreamWaitEvent(h->stream, ev[tmt_moe::kEvDxOut], 0));   // the previous dX has left dXs
             backward_impl(h, h->dYs, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, h->dXs, aux, zcoef);
-            CK(cudaMemcpyAsync(dX_host, h->dXs, bytes, cudaMemcpyDeviceToHost, h->stream));
+            CK(cudaEventRecord(ev[tmt_moe::kEvDxWritten], h->stream));
+            CK(cudaStreamWaitEvent(h->out_stream, ev[tmt_moe::kEvDxWritten], 0));
+            CK(cudaMemcpyAsync(dX_host, h->dXs, bytes, cudaMemcpyDeviceToHost, h->out_stream));
+            CK(cudaEventRecord(ev[tmt_moe::kEvDxOut], h->out_stream));
         }
-        CK(cudaStreamSynchronize(h->copy_stream));
-        CK(cudaStreamSynchronize(h->stream));
     })
+}
+
+int tmt_moe_host_wait(tmt_moe* h) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        if (!h->Xs) throw std::runtime_error("handle was created with host_io = 0");
+        CK(cudaSetDevice(h->d.device));
+        CK(cudaStreamSynchronize(h->in_stream));
+        CK(cudaStreamSynchronize(h->stream));
+        CK(cudaStreamSynchronize(h->out_stream));
+    })
+}
+
+int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter, const void* const* Wup,
+                      const void* const* Wdown, float* dWrouter, float* const* dWup, float* const* dWdown, void* Y_host,
+                      void* dX_host, float* stat_host, float beta, float aux, float zcoef, int tokens) {
+    if (tmt_moe_step_host_async(h, X_host, dY_host, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, Y_host, dX_host, stat_host, beta,
+                                aux, zcoef, tokens) != 0)
+        return -1;
+    return tmt_moe_host_wait(h);
 }
 
 long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes) {

@@ -45,6 +45,7 @@ struct tmt_moe {
     const int* g_poff = nullptr; const int* g_num_m_tiles = nullptr; const int* g_tile_expert = nullptr; int g_max_tiles = 0;
     long gcap = 0;      // rows of the grouped GEMM buffers
     bool two_cta = false; bool tensor_core = true; int gemm_dbg = 0;
+    int sm_limit = 0;       // > 0: GEMM launches use this many SMs (leaves room for kernels of another stream)
     long long* gemm_cyc = nullptr; int cyc_slot = 0;   // measurement only: cycle counters of the last kGemmCycLaunches GEMM launches
     int pad = 128;      // group padding (rows)
     int x_cap = 0;
@@ -75,8 +76,11 @@ struct tmt_moe {
     std::vector<float*> gup_seen, gdown_seen;
     // staging for the host-buffer entry point
     uint16_t *Xs = nullptr, *Ys = nullptr, *dYs = nullptr, *dXs = nullptr;
-    cudaStream_t copy_stream = nullptr;
-    cudaEvent_t ev_start = nullptr, ev_dy = nullptr, ev_fwd = nullptr;
+    // host_io: uploads on in_stream, downloads on out_stream, both under the compute of this and the next step
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    enum HostEvent { kEvXFree = 0, kEvDyFree, kEvXReady, kEvDyReady, kEvYWritten, kEvDxWritten, kEvYOut, kEvDxOut, kNumHostEvents };
+    cudaEvent_t host_ev[kNumHostEvents] = {};
+    bool host_hooks = false;     // forward / backward record kEvXFree / kEvDyFree once X / dY have been consumed
     // NVFP4 scratch: dequantised bf16 weights and per-expert tensor scales
     uint16_t* q_up = nullptr; uint16_t* q_down = nullptr; float* q_scales = nullptr;
     std::vector<const void*> q_ptrs_host;
@@ -108,13 +112,17 @@ const float* ep_stat(tmt_moe* h);
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr);
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped);
 void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue);
-void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown);
+// which: bit 0 = the products the input gradient needs (dH, dXg), bit 1 = the weight gradients (dWdown, dWup).
+void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown,
+                     int which = 3);
 // Router backward after the expert products: dlogits, dWr (local contribution) and dX.
 // grouped_x / x_is_ep: the token-side grouped copy of X (Xg, or the send buffer under expert parallelism).
 // pm: where the rows of dXg live (expert parallel with peer addressing); x_tokens: grouped_x is X in token order.
 void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uint16_t* grouped_x, bool x_is_ep,
                      const uint16_t* dXg_rows, float* dWr, uint16_t* dX, float aux, float zcoef, const int* counts, long n_norm,
-                     PeerMap pm = PeerMap());
+                     PeerMap pm = PeerMap(), bool defer_scatter = false);
+// The last step of the backward pass when router_backward was told to leave it out: dX = router term + sum_j dXg[slot_j], on `stream`.
+void scatter_rows(tmt_moe* h, const void* Wr, const uint16_t* dXg_rows, uint16_t* dX, cudaStream_t stream, PeerMap pm);
 void build_ep_maps(tmt_moe* h, const uint16_t* x_rows, bool token_order);
 void prof_mark(tmt_moe* h, int phase);
 }  // namespace tmt

@@ -491,7 +491,9 @@ cudaError_t launch_router_dw(const RouteDims& d, const RouteBufs& b, const float
 
 cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* dlogits, const void* Wr,
                            const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s, PeerMap pm) {
-    const size_t smem = (size_t)kWarpsPerBlock * d.E * sizeof(float);
+    // the staged router gradient is only read when the kernel computes the router term itself; without it a block
+    // needs no shared memory and fits beside a resident GEMM CTA
+    const size_t smem = dXr != nullptr ? 0 : (size_t)kWarpsPerBlock * d.E * sizeof(float);
     if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX, pm);
     else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX, pm);
     return cudaGetLastError();

@@ -26,7 +26,7 @@ EXPORTS = (
     "tmt_moe_forward_nvfp4", "tmt_moe_ep_unique_id", "tmt_moe_ep_init", "tmt_moe_set_profile",
     "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name", "tmt_moe_ep_plan",
     "tmt_moe_copy_stats", "tmt_moe_selftest_bounded_wait", "tmt_moe_router_dw_noalloc",
-    "tmt_moe_debug_gemm_cycles",
+    "tmt_moe_debug_gemm_cycles", "tmt_moe_step_host_async", "tmt_moe_host_wait",
 )
 
 
@@ -141,12 +141,17 @@ class MoE:
                                          ctypes.c_float(aux), ctypes.c_float(zcoef)), self.lib)
 
     def step_host(self, X_host, dY_host, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, Y_host, dX_host, stat_host,
-                  beta=0.0, aux=0.0, zcoef=0.0, tokens=None):
+                  beta=0.0, aux=0.0, zcoef=0.0, tokens=None, wait=True):
+        """wait=False queues the step and returns (tmt_moe_step_host_async); call host_wait() before reading results."""
         t = self.tokens if tokens is None else tokens
-        _check(self.lib.tmt_moe_step_host(self.h, _ptr(X_host), _ptr(dY_host), _ptr(Wrouter), _ptr_array(Wup),
+        fn = self.lib.tmt_moe_step_host if wait else self.lib.tmt_moe_step_host_async
+        _check(fn(self.h, _ptr(X_host), _ptr(dY_host), _ptr(Wrouter), _ptr_array(Wup),
                                           _ptr_array(Wdown), _ptr(dWrouter), _ptr_array(dWup), _ptr_array(dWdown),
                                           _ptr(Y_host), _ptr(dX_host), _ptr(stat_host), ctypes.c_float(beta),
                                           ctypes.c_float(aux), ctypes.c_float(zcoef), t), self.lib)
+
+    def host_wait(self):
+        _check(self.lib.tmt_moe_host_wait(self.h), self.lib)
 
     def stats(self):
         """Returns (stat[E+1], counts[E], aux) as numpy arrays / float (moe_aux_from, moe.cu:470-475)."""

@@ -241,6 +241,36 @@ def test_host_step_equals_device_path():
     np.testing.assert_array_equal(hstat.numpy(), stat)
 
 
+def test_host_steps_queued_back_to_back():
+    """Host steps queued without waiting (uploads of step n+1 under the GEMMs of step n, downloads under the
+    following compute): two different batches give exactly the results of the device-pointer calls."""
+    cfg = dict(T=3000, D=256, H=384, E=8, K=2)
+    E = cfg["E"]
+    batches = [synth.make(cfg["T"], cfg["D"], cfg["H"], E, cfg["K"], seed=15), synth.make(cfg["T"], cfg["D"], cfg["H"], E, cfg["K"], seed=16)]
+    layer = G.Layer(batches[0], cfg["T"], cfg["D"], E, cfg["K"], cfg["H"])
+    want = []
+    for b in batches:
+        layer.X = G.dev(b["X"])
+        Y = layer.forward(None, 0.0).copy()
+        g = layer.backward(b["dY"], 0.1, 0.001)
+        want.append((Y, g["dX"].copy()))
+    host = M.MoE(cfg["T"], cfg["D"], E, cfg["K"], hidden=cfg["H"], host_io=True)
+    pin = lambda a: torch.from_numpy(a.view(np.int16).copy()).pin_memory()
+    bufs = [(pin(b["X"]), pin(b["dY"]), torch.zeros(cfg["T"], cfg["D"], dtype=torch.int16).pin_memory(),
+             torch.zeros(cfg["T"], cfg["D"], dtype=torch.int16).pin_memory(), torch.zeros(E + 1).pin_memory()) for b in batches]
+    dWr = torch.zeros_like(layer.dWr)
+    dWup_all, dWdown_all = torch.zeros_like(layer.dWup_all), torch.zeros_like(layer.dWdown_all)
+    for rep in range(3):                      # six steps in flight order A B A B A B, one wait at the end
+        for hX, hdY, hY, hdX, hstat in bufs:
+            host.step_host(hX, hdY, layer.Wr, layer.Wup, layer.Wdown, dWr, [dWup_all[e] for e in range(E)],
+                           [dWdown_all[e] for e in range(E)], hY, hdX, hstat, 0.0, 0.1, 0.001, wait=False)
+    host.host_wait()
+    assert host.device_status() == 0
+    for (hX, hdY, hY, hdX, hstat), (Y, dX) in zip(bufs, want):
+        np.testing.assert_array_equal(hY.numpy().view(np.uint16), Y)
+        np.testing.assert_array_equal(hdX.numpy().view(np.uint16), dX)
+
+
 def test_bounded_wait_runs_out_and_context_survives():
     """Failure detection without a fault: a wait on a barrier nothing signals runs out after its limit,
     the kernel records the time-out status and returns, and the same handle keeps working."""
