@@ -37,6 +37,7 @@ struct tmt_ep_state {
     // second stream of the peer transport: rank barriers and row transfers that run under GEMMs of the main stream
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool overlap = true;              // TMT_MOE_EP_OVERLAP=0 switches the second stream off (measurement)
     int G = 1, r = 0, EL = 0;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
@@ -186,6 +187,7 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         const size_t cap = h->dims.cap;
         ep->peer = h->d.ep_transport == TMT_MOE_EP_PEER;
         if (ep->peer) {
+            if (const char* ov = getenv("TMT_MOE_EP_OVERLAP")) ep->overlap = atoi(ov) != 0;
             CKE(cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking));
             CKE(cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming));
             CKE(cudaEventCreateWithFlags(&ep->ev_join, cudaEventDisableTiming));
@@ -430,20 +432,28 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
         // Input-gradient products first; then the rows of dXg travel back (rank barrier + scatter on the side stream)
         // while the main stream computes the weight gradients, which need nothing from other ranks. Those two GEMM
         // launches leave two SMs free so that the barrier's kernel can start while they run.
-        expert_backward(h, Wup, Wdown, dWup, dWdown, 1);
-        router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
-                        (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg), /*defer_scatter=*/true);
-        CKE(cudaEventRecord(ep->ev_fork, h->stream));
-        CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
-        rank_barrier(h, ep->side);          // every rank's dXg is complete
-        scatter_rows(h, Wr, h->dXg, static_cast<uint16_t*>(dX), ep->side, peer_map(h, ep->peer_dXg));
-        CKE(cudaEventRecord(ep->ev_join, ep->side));
-        struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
-        h->sm_limit = h->num_sms - 2;
-        expert_backward(h, Wup, Wdown, dWup, dWdown, 2);
-        h->sm_limit = 0;
-        prof_mark(h, kPhScatter);
-        CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
+        if (!ep->overlap) {                 // measurement switch: everything on one stream, in dependency order
+            expert_backward(h, Wup, Wdown, dWup, dWdown);
+            prof_mark(h, kPhExchange);
+            rank_barrier(h);
+            router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+                            (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg));
+        } else {
+            expert_backward(h, Wup, Wdown, dWup, dWdown, 1);
+            router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+                            (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg), /*defer_scatter=*/true);
+            CKE(cudaEventRecord(ep->ev_fork, h->stream));
+            CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+            rank_barrier(h, ep->side);          // every rank's dXg is complete
+            scatter_rows(h, Wr, h->dXg, static_cast<uint16_t*>(dX), ep->side, peer_map(h, ep->peer_dXg));
+            CKE(cudaEventRecord(ep->ev_join, ep->side));
+            struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
+            h->sm_limit = h->num_sms - 2;
+            expert_backward(h, Wup, Wdown, dWup, dWdown, 2);
+            h->sm_limit = 0;
+            prof_mark(h, kPhScatter);
+            CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
+        }
     } else {
         CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
         h->launches += 1;
