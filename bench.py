@@ -193,12 +193,75 @@ def make_device_data(cfg, T, local_experts, rank, torch):
     return d
 
 
+def bench_adamw(args):
+    """Multi-tensor AdamW (include/tmt_adamw.h) over config 5's parameters: 64 experts x (2048x2048 up + 2048x2048 down)
+    and the 64x2048 router. One step = norm + clip + update + bf16 copies + gradient clearing. HBM-bound: 38 bytes per
+    parameter (norm pass: read grad 4; update pass: read master, m, v, grad 16, write master, m, v 12, bf16 copy 2, cleared
+    gradient 4)."""
+    import numpy as np
+    import torch
+    import tmt_moe_b200 as M
+    from oracle import oracle as O
+    c5 = CONFIGS["c5"]
+    sizes = [c5["H"] * c5["D"]] * c5["E"] + [c5["D"] * c5["H"]] * c5["E"] + [c5["E"] * c5["D"]]
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    mk = lambda n, std: torch.randn(n, generator=g, device="cuda", dtype=torch.float32) * std
+    w = [mk(n, 0.02) for n in sizes]
+    m = [mk(n, 1e-3) for n in sizes]
+    v = [mk(n, 1e-3) ** 2 for n in sizes]
+    gr = [mk(n, 1e-2) for n in sizes]
+    work = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+    opt = M.AdamW(sizes)
+    hyp = dict(clip=1.0, lr=3e-4, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, zero_grads=True)
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(max(args.warmup, 3)):
+        opt.step(w, m, v, gr, work, None, step=i + 1, **hyp)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    wall0 = time.time()
+    for i, (a, b) in enumerate(evs):
+        a.record()
+        opt.step(w, m, v, gr, work, None, step=10 + i, **hyp)
+        b.record()
+    torch.cuda.synchronize()
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1)
+    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    n = sum(sizes)
+    pk, kind = peaks()
+    gbs = 38.0 * n / (ms * 1e-3) / 1e9
+    line = dict(metric="adamw_parameters_per_s", unit="parameters/s", n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3),
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32 (bf16 working copies)", data="synthetic",
+                value=n / (ms * 1e-3), ms_per_step=ms,
+                config={"workload": "AdamW step over config 5's parameters: 128 expert matrices of 2048x2048 and the 64x2048 router "
+                                    "(%d parameters), global-norm clipping on" % n,
+                        "l2": "working set larger than L2 (no flush needed)"},
+                clocks=clocks, gpu_launches=3 * args.steps,
+                roofline={"bound": "hbm", "kernel": "adamw_kernel + sumsq_kernel", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                          "frac": gbs / pk["hbm_gbs"], "traffic": None, "peak_kind": kind, "bytes_per_parameter": 38})
+    if not args.no_cpu_baseline:
+        sample = 1 << 22
+        hw, hm, hv, hg = (x[0][:sample].cpu().numpy() for x in (w, m, v, gr))
+        t0 = time.perf_counter()
+        O.sumsq([hg])
+        O.adamw(hw, hm, hv, hg, 1.0, 3e-4, 0.9, 0.999, 1e-8, 0.01, 5)
+        sec = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": sample / sec, "unit": "parameters/s", "cores": 1, "kind": "port",
+                                "sample": "first %d parameters of one expert matrix, norm + update, one thread (%.2f s)" % (sample, sec)}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS) + ["adamw5"],
+                    help="c1..c5: the MoE layer workloads; adamw5: the optimizer step over config 5's expert and router parameters "
+                         "(the component after the layer's backward pass; its own metric, not the headline)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -210,6 +273,8 @@ def main():
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows move by peer loads/stores inside the gather/scatter kernels, or by NCCL send/recv")
     args = ap.parse_args()
+    if args.config == "adamw5":
+        return bench_adamw(args)
     cfg = dict(CONFIGS[args.config])
     if args.tokens:
         cfg["T"] = args.tokens

@@ -189,7 +189,7 @@ struct oracle_cfg {
     int pad;         // rows every expert group is padded to (0 = 128, the reference's padding)
 };
 
-int oracle_abi_version() { return 4; }
+int oracle_abi_version() { return 5; }
 
 // moe.cu:10-68 (+ optional per-expert logit bias, which the reference lacks).
 void oracle_router(const oracle_cfg* c, const uint16_t* X, const void* Wr, const float* bias,
@@ -576,6 +576,34 @@ void oracle_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, float
             float s = e4m3_to_f(scales[r * (cols / 16) + cidx / 16]) * tensor_scale;
             W[r * cols + cidx] = f2bf(v * s);
         }
+}
+
+
+// Multi-tensor AdamW, one tensor (adam.cu:84-99 with the roundings stated in include/tmt_adamw.h). `scale` is the
+// clipping factor (adam.cu:83); the squared norm it comes from is computed by oracle_sumsq in plain index order.
+double oracle_sumsq(const float* g, long n) {
+    double s = 0.0;
+    for (long i = 0; i < n; ++i) s += (double)g[i] * g[i];
+    return s;
+}
+float oracle_clip_scale(double sumsq, float clip) {
+    if (!(clip > 0.0f)) return 1.0f;
+    return std::fmin(1.0f, clip / std::fmax((float)std::sqrt(sumsq), 1e-12f));
+}
+void oracle_adamw(float* master, float* m, float* v, const float* grad, uint16_t* work, long n, float scale, float lr, float b1,
+                  float b2, float eps, float wd, int step) {
+    const float bc1 = 1.0f - std::pow(b1, (float)step), bc2 = 1.0f - std::pow(b2, (float)step);
+    const float omb1 = 1.0f - b1, omb2 = 1.0f - b2;
+    for (long i = 0; i < n; ++i) {
+        const float g = grad[i] * scale;
+        const float nm = std::fmaf(b1, m[i], omb1 * g);
+        const float t = omb2 * g;
+        const float nv = std::fmaf(b2, v[i], t * g);
+        const float u = (nm / bc1) / (std::sqrt(nv / bc2) + eps);
+        const float w = std::fmaf(-lr, std::fmaf(wd, master[i], u), master[i]);
+        m[i] = nm; v[i] = nv; master[i] = w;
+        if (work) work[i] = f2bf(w);
+    }
 }
 
 }  // extern "C"

@@ -36,7 +36,9 @@ def lib():
         _lib.oracle_stats.restype = ctypes.c_float
         _lib.oracle_layout.restype = ctypes.c_int
         _lib.oracle_abi_version.restype = ctypes.c_int
-        assert _lib.oracle_abi_version() == 4, "stale oracle library: run make -C oracle -B"
+        _lib.oracle_sumsq.restype = ctypes.c_double
+        _lib.oracle_clip_scale.restype = ctypes.c_float
+        assert _lib.oracle_abi_version() == 5, "stale oracle library: run make -C oracle -B"
     return _lib
 
 
@@ -199,3 +201,23 @@ def nvfp4_dequantize(packed, scales, tensor_scale=1.0):
                                   ctypes.c_float(tensor_scale), ctypes.c_long(rows), ctypes.c_long(cols),
                                   _p(W))
     return W
+
+
+def adamw(master, m, v, grad, scale, lr, b1, b2, eps, wd, step, want_work=True):
+    """One AdamW step on one tensor, in place on copies. Returns (master, m, v, work bf16 bits)."""
+    master, m, v = (np.array(a, dtype=np.float32, copy=True).ravel() for a in (master, m, v))
+    grad = np.ascontiguousarray(grad, np.float32).ravel()
+    work = np.zeros(master.size, np.uint16) if want_work else None
+    lib().oracle_adamw(_p(master), _p(m), _p(v), _p(grad), _p(work), ctypes.c_long(master.size), ctypes.c_float(scale),
+                       ctypes.c_float(lr), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(eps), ctypes.c_float(wd),
+                       ctypes.c_int(step))
+    return master, m, v, work
+
+
+def sumsq(grads):
+    """Squared norm of a list of gradient arrays, accumulated in double in list and index order."""
+    return float(sum(lib().oracle_sumsq(_p(np.ascontiguousarray(g, np.float32).ravel()), ctypes.c_long(g.size)) for g in grads))
+
+
+def clip_scale(ss, clip):
+    return float(lib().oracle_clip_scale(ctypes.c_double(ss), ctypes.c_float(clip)))

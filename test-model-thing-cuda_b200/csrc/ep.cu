@@ -37,7 +37,14 @@ struct tmt_ep_state {
     // second stream of the peer transport: rank barriers and row transfers that run under GEMMs of the main stream
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    static constexpr int kMaxWaves = 4;
+    cudaEvent_t ev_sent[kMaxWaves] = {}, ev_done[kMaxWaves] = {};     // a wave's rows have landed / its GEMMs are done
     bool overlap = true;              // TMT_MOE_EP_OVERLAP=0 switches the second stream off (measurement)
+    int waves = 1;                    // TMT_MOE_EP_WAVES: expert waves of the forward pass. Measured at 2 GPUs: 2 waves make the
+                                      // step 1.0-1.5 ms SLOWER (GEMMs beside the row kernels lose more than the transfers
+                                      // hide, with shared or with dedicated SMs), so the default is no waves.
+    int side_sms = 0;                 // TMT_MOE_EP_SMS: > 0 keeps that many SMs for the side stream's row kernels instead of
+                                      // letting their blocks share SMs with the GEMM CTAs
     int G = 1, r = 0, EL = 0;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
@@ -188,6 +195,13 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         ep->peer = h->d.ep_transport == TMT_MOE_EP_PEER;
         if (ep->peer) {
             if (const char* ov = getenv("TMT_MOE_EP_OVERLAP")) ep->overlap = atoi(ov) != 0;
+            if (const char* sm = getenv("TMT_MOE_EP_SMS")) ep->side_sms = std::max(0, std::min(atoi(sm), h->num_sms / 2));
+            if (const char* wv = getenv("TMT_MOE_EP_WAVES")) ep->waves = std::max(1, std::min(atoi(wv), (int)tmt_ep_state::kMaxWaves));
+            ep->waves = std::min(ep->waves, ep->EL);
+            for (int w = 0; w < tmt_ep_state::kMaxWaves; ++w) {
+                CKE(cudaEventCreateWithFlags(&ep->ev_sent[w], cudaEventDisableTiming));
+                CKE(cudaEventCreateWithFlags(&ep->ev_done[w], cudaEventDisableTiming));
+            }
             CKE(cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking));
             CKE(cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming));
             CKE(cudaEventCreateWithFlags(&ep->ev_join, cudaEventDisableTiming));
@@ -261,6 +275,8 @@ void ep_teardown(tmt_moe* h) {
     if (h->ep->side) cudaStreamDestroy(h->ep->side);
     if (h->ep->ev_fork) cudaEventDestroy(h->ep->ev_fork);
     if (h->ep->ev_join) cudaEventDestroy(h->ep->ev_join);
+    for (cudaEvent_t e : h->ep->ev_sent) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : h->ep->ev_done) if (e) cudaEventDestroy(e);
     if (h->ep->comm && h->ep->CommDestroy) h->ep->CommDestroy(h->ep->comm);
     delete h->ep;
     h->ep = nullptr;
@@ -349,11 +365,13 @@ void rank_barrier(tmt_moe* h, cudaStream_t stream = nullptr) {
     h->launches += 1;
 }
 
-PeerMap peer_map(tmt_moe* h, uint16_t** table) {
+PeerMap peer_map(tmt_moe* h, uint16_t** table, bool beside_gemm = false) {
     PeerMap pm;
     pm.base = table; pm.dest_row0 = h->ep->dest_row0; pm.experts_per_rank = h->ep->EL;
+    if (beside_gemm && h->ep->side_sms > 0) pm.pad_smem = 4096;
     return pm;
 }
+int gemm_sms_beside_rows(tmt_moe* h) { return h->num_sms - std::max(2, h->ep->side_sms); }
 
 void use_expert_layout(tmt_moe* h) {
     tmt_ep_state* ep = h->ep;
@@ -380,19 +398,63 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
         route_only(h, static_cast<const uint16_t*>(X), Wr);
         plan_step(h);                       // all-gather of counts: also separates this step from the previous one
         zero_pads(h, h->Xg, D);
-        prof_mark(h, kPhDispatch);
-        CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, h->stream, peer_map(h, ep->peer_Xg),
-                            h->d.training ? ep->Xc : nullptr));
-        h->launches += 1;
-        prof_mark(h, kPhExchange);
-        rank_barrier(h);                    // every rank's rows have landed
-        expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
-        prof_mark(h, kPhExchange);
-        rank_barrier(h);                    // every rank's expert outputs are complete
-        prof_mark(h, kPhCombine);
-        CKE(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream,
-                           peer_map(h, ep->peer_Yg), h->d.training ? ep->Yr : nullptr));
-        h->launches += 1;
+        if (!ep->overlap || ep->waves < 2) {
+            prof_mark(h, kPhDispatch);
+            CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, h->stream, peer_map(h, ep->peer_Xg),
+                                h->d.training ? ep->Xc : nullptr));
+            h->launches += 1;
+            prof_mark(h, kPhExchange);
+            rank_barrier(h);                    // every rank's rows have landed
+            expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
+            prof_mark(h, kPhExchange);
+            rank_barrier(h);                    // every rank's expert outputs are complete
+            prof_mark(h, kPhCombine);
+            CKE(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream,
+                               peer_map(h, ep->peer_Yg), h->d.training ? ep->Yr : nullptr));
+            h->launches += 1;
+        } else {
+            // Expert waves: wave w = the local experts [w*EL/W, (w+1)*EL/W) of EVERY rank. The side stream sends wave after
+            // wave (dispatch + rank barrier) and later fetches the finished waves' output rows; the main stream runs a
+            // wave's two GEMMs as soon as its rows have landed everywhere. So the transfer of wave w+1 runs under the GEMMs
+            // of wave w, and the fetch of wave w under the GEMMs of wave w+1. The GEMM launches leave two SMs free for the
+            // barriers' kernels; the row kernels fit beside the resident GEMM CTAs.
+            const int W = ep->waves, EL = ep->EL;
+            CKE(cudaEventRecord(ep->ev_fork, h->stream));
+            CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+            auto wave_map = [&](uint16_t** table, int w) {
+                PeerMap pm = peer_map(h, table, true);
+                pm.wave_lo = (int)((long)EL * w / W); pm.wave_hi = (int)((long)EL * (w + 1) / W);
+                return pm;
+            };
+            prof_mark(h, kPhDispatch);
+            for (int w = 0; w < W; ++w) {
+                CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, ep->side, wave_map(ep->peer_Xg, w),
+                                    (h->d.training && w == 0) ? ep->Xc : nullptr));
+                rank_barrier(h, ep->side);      // every rank's rows of this wave have landed
+                CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
+                h->launches += 1;
+            }
+            struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
+            h->sm_limit = gemm_sms_beside_rows(h);
+            for (int w = 0; w < W; ++w) {
+                const int lo = (int)((long)EL * w / W), hi = (int)((long)EL * (w + 1) / W);
+                CKE(cudaStreamWaitEvent(h->stream, ep->ev_sent[w], 0));
+                expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false, ep->x_poff[lo] / kPad, (ep->x_poff[hi] - ep->x_poff[lo]) / kPad);
+                CKE(cudaEventRecord(ep->ev_done[w], h->stream));
+            }
+            h->sm_limit = 0;
+            for (int w = 0; w < W; ++w) {
+                CKE(cudaStreamWaitEvent(ep->side, ep->ev_done[w], 0));
+                rank_barrier(h, ep->side);      // every rank's outputs of this wave are complete
+                CKE(launch_combine(h->dims, h->rb, h->Yg, nullptr, 0.0f, /*mode=*/3, ep->side, wave_map(ep->peer_Yg, w), ep->Yr));
+                h->launches += 1;
+            }
+            CKE(cudaEventRecord(ep->ev_join, ep->side));
+            CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
+            prof_mark(h, kPhCombine);           // every row is in Yr (token-side slots): a local weighted sum remains
+            CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
+            h->launches += 1;
+        }
     } else {
         route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
         plan_step(h);
@@ -445,10 +507,10 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
             CKE(cudaEventRecord(ep->ev_fork, h->stream));
             CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
             rank_barrier(h, ep->side);          // every rank's dXg is complete
-            scatter_rows(h, Wr, h->dXg, static_cast<uint16_t*>(dX), ep->side, peer_map(h, ep->peer_dXg));
+            scatter_rows(h, Wr, h->dXg, static_cast<uint16_t*>(dX), ep->side, peer_map(h, ep->peer_dXg, true));
             CKE(cudaEventRecord(ep->ev_join, ep->side));
             struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
-            h->sm_limit = h->num_sms - 2;
+            h->sm_limit = gemm_sms_beside_rows(h);
             expert_backward(h, Wup, Wdown, dWup, dWdown, 2);
             h->sm_limit = 0;
             prof_mark(h, kPhScatter);

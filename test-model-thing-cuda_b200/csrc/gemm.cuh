@@ -49,6 +49,8 @@ struct GemmParams {
     int experts;
     const int* tile_expert;       // kRowsRagged: expert of each 128-row tile
     const int* num_m_tiles;       // kRowsRagged: number of 128-row tiles in use (device scalar)
+    int tile_begin, tile_count;   // kRowsRagged: tile_count >= 0 restricts the launch to the 128-row tiles [tile_begin,
+                                  // tile_begin + tile_count) (host values; whole 256-row pairs for the CTA-pair kernel)
     const int* poff;              // E+1 padded group starts
     // epilogue
     int epi;

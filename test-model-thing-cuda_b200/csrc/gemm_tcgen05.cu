@@ -41,6 +41,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int m_tiles
     if (p.mode == kRowsRagged) {
         if (t >= m_tiles * n_tiles) return false;
         int mt = t / n_tiles, nt = t - mt * n_tiles;
+        mt += p.tile_begin;
         ti.expert = p.tile_expert[mt];
         ti.row0 = mt * kBM;
         ti.col0 = nt * kBN;
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
     const uint32_t tmem_base = tmem_base_s;
 
     int m_tiles, n_tiles = (p.N + kBN - 1) / kBN;
-    if (p.mode == kRowsRagged) m_tiles = *p.num_m_tiles; else m_tiles = (p.M + kBM - 1) / kBM;
+    if (p.mode == kRowsRagged) m_tiles = p.tile_count >= 0 ? p.tile_count : *p.num_m_tiles; else m_tiles = (p.M + kBM - 1) / kBM;
 
     if (warp == 0 || warp == 2 + epi_warps<EPI>()) {
         // ---------------- TMA producers: warp 0 fills the even stages, the last warp the odd ones; lane 0 owns the

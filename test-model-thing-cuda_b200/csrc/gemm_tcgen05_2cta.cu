@@ -90,8 +90,8 @@ __device__ __forceinline__ bool get_tile2(const GemmParams& p, int t, int m_pair
     if (p.mode == kRowsRagged) {
         if (t >= m_pairs * n_tiles) return false;
         const int mp = t / n_tiles, nt = t - mp * n_tiles;
-        ti.expert = p.tile_expert[2 * mp];
-        ti.row0 = mp * 2 * kBM + rank * kBM;
+        ti.expert = p.tile_expert[p.tile_begin + 2 * mp];
+        ti.row0 = (p.tile_begin + 2 * mp) * kBM + rank * kBM;
         ti.col0 = nt * kBN;
         ti.kb0 = 0;
         ti.nkb = (p.K + kBK - 1) / kBK;
@@ -155,7 +155,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
     const uint32_t tmem_base = tmem_base_s;
 
     const int n_tiles = (p.N + kBN - 1) / kBN;
-    const int m_pairs = p.mode == kRowsRagged ? (*p.num_m_tiles + 1) / 2 : (p.M + 2 * kBM - 1) / (2 * kBM);
+    const int m_tiles_in_use = p.mode == kRowsRagged ? (p.tile_count >= 0 ? p.tile_count : *p.num_m_tiles) : 0;
+    const int m_pairs = p.mode == kRowsRagged ? (m_tiles_in_use + 1) / 2 : (p.M + 2 * kBM - 1) / (2 * kBM);
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
     if (warp == 0 || warp == 2 + epi_warps<EPI>()) {
@@ -309,7 +310,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
             if (prof) t1 = clock64();
             tc_fence_after();
             const long row = (long)ti.row0 + es.quarter * 32 + lane;
-            const bool row_ok = (p.mode == kRowsRagged) ? (row < (long)*p.num_m_tiles * kBM) : (row < p.M);
+            const bool row_ok = (p.mode == kRowsRagged) ? (row < (long)(p.tile_begin + m_tiles_in_use) * kBM) : (row < p.M);
             const uint32_t tm = tmem_base + ((uint32_t)(es.quarter * 32) << 16) + (uint32_t)(acc * kBN);
             if (!epi_drain_tile<EPI, kGroups>(p, es, ti.expert, ti.row0, ti.col0, ti.nkb, tm, row_ok)) break;
             tc_fence_before();

@@ -45,6 +45,12 @@ struct PeerMap {
     uint16_t* const* base = nullptr;
     const int* dest_row0 = nullptr;
     int experts_per_rank = 1;
+    // Only assignments whose expert's index inside its owner rank lies in [wave_lo, wave_hi) move rows (the expert-
+    // parallel step sends the experts in waves so that a wave's transfer runs under the previous wave's GEMMs).
+    int wave_lo = 0, wave_hi = 1 << 30;
+    // Extra dynamic shared memory per block (unused by the kernel): with a few KB a block no longer fits beside a
+    // resident GEMM CTA, so a kernel launched next to a GEMM stays on the SMs that GEMM left free.
+    int pad_smem = 0;
 };
 
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
@@ -58,6 +64,7 @@ cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16
 // mode 0: Y = beta*Y + sum_j Yg[slot_j]               (two-matrix experts, gate applied by the GEMM)
 // mode 1: Y = beta*Y + sum_j w_j * silu(Yg[slot_j])   (reference mode, moe.cu:144-158)
 // mode 2: Y = beta*Y + sum_j w_j * Yg[slot_j]         (expert parallel: rows come back unscaled)
+// mode 3: no Y; only fetches the rows of pm's wave into y_keep (their token-side slots)
 // y_keep (may be NULL): stores every fetched row at its token-side slot (kept for the backward pass).
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
                            int mode, cudaStream_t s, PeerMap pm = PeerMap(), uint16_t* y_keep = nullptr);

@@ -229,6 +229,7 @@ GemmParams base_params(tmt_moe* h) {
     p.poff = h->g_poff;
     p.status = h->rb.status;
     p.a_boxes = 1; p.b_boxes = 1;
+    p.tile_begin = 0; p.tile_count = -1;
     p.dbg = h->gemm_dbg;
     return p;
 }
@@ -345,11 +346,13 @@ void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
 
 // Grouped expert products over the rows in h->Xg: Yg = expert(Xg). With gate_in_epilogue the
 // down-projection scales each row by its gate weight (single-GPU layout, where slotw is local).
-void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue) {
+void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue, int tile_begin,
+                    int tile_count) {
     const int D = h->d.dim, H = h->d.hidden;
     refresh_weights(h, Wup, Wdown);
     if (H > 0) {
         GemmParams up = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, H, D, kEpiUp);
+        up.tile_begin = tile_begin; up.tile_count = tile_count;
         up.out0 = h->d.training ? h->P : nullptr;
         up.out1 = h->Hact;
         up.mapC0 = h->act_maps + kOutHact; up.mapC1 = h->d.training ? h->act_maps + kOutP : nullptr;
@@ -358,6 +361,7 @@ void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown
         run_gemm(h, up);
         GemmParams down = rows_gemm(h, kHactK, h->Hact, kDownK, h->down_ptrs, false, D, H, gate_in_epilogue ? kEpiDown : kEpiBf16);
         down.out0 = h->Yg;
+        down.tile_begin = tile_begin; down.tile_count = tile_count;
         down.mapC0 = h->act_maps + kOutYg;
         down.row_scale = h->rb.slotw;
         if (h->q_expert_scales) down.expert_scale = h->q_scales + h->d.experts;
@@ -366,6 +370,7 @@ void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown
     } else {
         GemmParams g = rows_gemm(h, kXgK, h->Xg, kUpK, h->up_ptrs, false, D, D, kEpiBf16);
         g.out0 = h->Yg;
+        g.tile_begin = tile_begin; g.tile_count = tile_count;
         g.mapC0 = h->act_maps + kOutYg;
         prof_mark(h, kPhGemmUp);
         run_gemm(h, g);

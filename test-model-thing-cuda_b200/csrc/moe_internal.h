@@ -111,7 +111,9 @@ void ep_teardown(tmt_moe* h);
 const float* ep_stat(tmt_moe* h);
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr);
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped);
-void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue);
+// tile_count >= 0: only the 128-row tiles [tile_begin, tile_begin + tile_count) of the grouped buffers.
+void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue, int tile_begin = 0,
+                    int tile_count = -1);
 // which: bit 0 = the products the input gradient needs (dH, dXg), bit 1 = the weight gradients (dWdown, dWup).
 void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown,
                      int which = 3);

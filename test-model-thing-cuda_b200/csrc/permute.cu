@@ -25,6 +25,10 @@ __device__ __forceinline__ uint16_t* group_row(const PeerMap& pm, const uint16_t
     if (pm.base == nullptr) return const_cast<uint16_t*>(local) + (long)slot * D;
     return pm.base[e / pm.experts_per_rank] + (long)(pm.dest_row0[e] + slot - poff[e]) * D;
 }
+__device__ __forceinline__ bool in_wave(const PeerMap& pm, int e) {
+    const int le = e % pm.experts_per_rank;
+    return le >= pm.wave_lo && le < pm.wave_hi;
+}
 __device__ __forceinline__ uint16_t* shfl_ptr(uint16_t* p, int lane) {
     return reinterpret_cast<uint16_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(p), lane));
 }
@@ -67,7 +71,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dispatch_kernel(const Rou
                 b.slot_of[t * d.K + lane] = slot;
                 b.slotw[slot] = b.w[t * d.K + lane];
                 b.tok_of_slot[slot] = (int)t;
-                row = group_row(pm, Xg, b.poff, e, slot, d.D);
+                if (in_wave(pm, e)) row = group_row(pm, Xg, b.poff, e, slot, d.D);
             }
         }
     }
@@ -96,8 +100,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
     int slot = -1; float wj = 0.0f; uint16_t* row = nullptr;
     if (lane < d.K) {
         slot = b.slot_of[t * d.K + lane];
+        const int e = b.idx[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
-        else { wj = b.slotw[slot]; row = group_row(pm, Yg, b.poff, b.idx[t * d.K + lane], slot, d.D); }
+        else if (!in_wave(pm, e)) slot = -1;
+        else { wj = b.slotw[slot]; row = group_row(pm, Yg, b.poff, e, slot, d.D); }
     }
     int slots[kMaxK]; float ws[kMaxK]; const uint16_t* rows[kMaxK];
 #pragma unroll
@@ -105,6 +111,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
         slots[j] = __shfl_sync(0xffffffffu, slot, j); ws[j] = __shfl_sync(0xffffffffu, wj, j); rows[j] = shfl_ptr(row, j);
     }
     const int nvec = d.D >> 3;
+    if constexpr (MODE == 3) {
+#pragma unroll 2
+        for (int v = lane; v < nvec; v += 32) {
+#pragma unroll
+            for (int j = 0; j < kMaxK; ++j)
+                if (j < d.K && slots[j] >= 0) stg16(y_keep + (long)slots[j] * d.D + v * 8, ldg16(rows[j] + v * 8));
+        }
+        return;
+    }
     uint16_t* dst = Y + t * d.D;
 #pragma unroll 2
     for (int v = lane; v < nvec; v += 32) {
@@ -161,8 +176,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
     int slot = -1; float wj = 0.0f; uint16_t* row = nullptr;
     if (lane < d.K) {
         slot = b.slot_of[t * d.K + lane];
+        const int e = b.idx[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
-        else { wj = b.slotw[slot]; row = group_row(pm, dYg, b.poff, b.idx[t * d.K + lane], slot, d.D); }
+        else if (!in_wave(pm, e)) slot = -1;
+        else { wj = b.slotw[slot]; row = group_row(pm, dYg, b.poff, e, slot, d.D); }
     }
     int slots[kMaxK]; float ws[kMaxK]; float sdot[kMaxK]; uint16_t* rows[kMaxK];
 #pragma unroll
@@ -209,7 +226,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
                 float s = sdot[j];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == 0) s_j[t * d.K + j] = s;
+                if (lane == 0 && slots[j] >= 0) s_j[t * d.K + j] = s;
             }
         }
     }
@@ -433,16 +450,17 @@ cudaError_t launch_dispatch(const RouteDims& d, const RouteBufs& b, const uint16
                             PeerMap pm, uint16_t* x_copy) {
     const int tb = tok_blocks_of(d.T);
     // with peer addressing the pad rows belong to the owners, who zero their own
-    dispatch_kernel<<<tb + (pm.base ? 0 : d.E), kWarpsPerBlock * 32, d.E * sizeof(int), s>>>(d, b, X, Xg, tb, pm, x_copy);
+    dispatch_kernel<<<tb + (pm.base ? 0 : d.E), kWarpsPerBlock * 32, d.E * sizeof(int) + pm.pad_smem, s>>>(d, b, X, Xg, tb, pm, x_copy);
     return cudaGetLastError();
 }
 
 cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_t* Yg, uint16_t* Y, float beta,
                            int mode, cudaStream_t s, PeerMap pm, uint16_t* y_keep) {
     const dim3 grid(tok_blocks_of(d.T)), block(kWarpsPerBlock * 32);
-    if (mode == 1) combine_kernel<1><<<grid, block, 0, s>>>(d, b, Yg, Y, beta, pm, y_keep);
-    else if (mode == 2) combine_kernel<2><<<grid, block, 0, s>>>(d, b, Yg, Y, beta, pm, y_keep);
-    else combine_kernel<0><<<grid, block, 0, s>>>(d, b, Yg, Y, beta, pm, y_keep);
+    if (mode == 3) combine_kernel<3><<<grid, block, pm.pad_smem, s>>>(d, b, Yg, Y, beta, pm, y_keep);
+    else if (mode == 1) combine_kernel<1><<<grid, block, pm.pad_smem, s>>>(d, b, Yg, Y, beta, pm, y_keep);
+    else if (mode == 2) combine_kernel<2><<<grid, block, pm.pad_smem, s>>>(d, b, Yg, Y, beta, pm, y_keep);
+    else combine_kernel<0><<<grid, block, pm.pad_smem, s>>>(d, b, Yg, Y, beta, pm, y_keep);
     return cudaGetLastError();
 }
 
@@ -450,9 +468,9 @@ cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const u
                                  uint16_t* dYg, float* s_j, int mode, cudaStream_t s, PeerMap pm) {
     const int tb = tok_blocks_of(d.T);
     const dim3 grid(tb + (pm.base ? 0 : d.E)), block(kWarpsPerBlock * 32);
-    if (mode == 1) grad_dispatch_kernel<1><<<grid, block, 0, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
-    else if (mode == 2) grad_dispatch_kernel<2><<<grid, block, 0, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
-    else grad_dispatch_kernel<0><<<grid, block, 0, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
+    if (mode == 1) grad_dispatch_kernel<1><<<grid, block, pm.pad_smem, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
+    else if (mode == 2) grad_dispatch_kernel<2><<<grid, block, pm.pad_smem, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
+    else grad_dispatch_kernel<0><<<grid, block, pm.pad_smem, s>>>(d, b, dY, Yg, dYg, s_j, tb, pm);
     return cudaGetLastError();
 }
 
@@ -493,7 +511,7 @@ cudaError_t launch_scatter(const RouteDims& d, const RouteBufs& b, const float* 
                            const uint16_t* dXg, const uint16_t* dXr, uint16_t* dX, cudaStream_t s, PeerMap pm) {
     // the staged router gradient is only read when the kernel computes the router term itself; without it a block
     // needs no shared memory and fits beside a resident GEMM CTA
-    const size_t smem = dXr != nullptr ? 0 : (size_t)kWarpsPerBlock * d.E * sizeof(float);
+    const size_t smem = (dXr != nullptr ? 0 : (size_t)kWarpsPerBlock * d.E * sizeof(float)) + pm.pad_smem;
     if (d.router_f32) scatter_kernel<true><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX, pm);
     else scatter_kernel<false><<<tok_blocks_of(d.T), kWarpsPerBlock * 32, smem, s>>>(d, b, dlogits, Wr, dXg, dXr, dX, pm);
     return cudaGetLastError();

@@ -27,6 +27,7 @@ EXPORTS = (
     "tmt_moe_profile", "tmt_moe_num_phases", "tmt_moe_phase_name", "tmt_moe_ep_plan",
     "tmt_moe_copy_stats", "tmt_moe_selftest_bounded_wait", "tmt_moe_router_dw_noalloc",
     "tmt_moe_debug_gemm_cycles", "tmt_moe_step_host_async", "tmt_moe_host_wait",
+    "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
 )
 
 
@@ -88,7 +89,8 @@ def _ptr_array(xs):
         return None
     arr = (ctypes.c_void_p * len(xs))()
     for i, x in enumerate(xs):
-        arr[i] = _ptr(x).value
+        p = _ptr(x)
+        arr[i] = None if p is None else p.value
     return arr
 
 
@@ -242,6 +244,39 @@ class MoE:
 
     def device_status(self):
         return self.lib.tmt_moe_device_status(self.h)
+
+
+class AdamW:
+    """Multi-tensor AdamW over a fixed list of tensors (include/tmt_adamw.h; the reference's optimizer_step,
+    tmt-cuda/src/model.cu:716-729). Tensors are torch CUDA tensors (fp32 master / m / v / grad, bf16 work or None)."""
+
+    def __init__(self, sizes, device=0, stream=None):
+        self.lib = load()
+        self.n = len(sizes)
+        self.h = ctypes.c_void_p()
+        arr = (ctypes.c_longlong * self.n)(*[int(s) for s in sizes])
+        _check(self.lib.tmt_adamw_create(self.n, arr, int(device), _ptr(stream), ctypes.byref(self.h)), self.lib)
+
+    def step(self, master, m, v, grad, work, flags=None, clip=0.0, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, step=1,
+             zero_grads=True, want_norm=False):
+        fl = (ctypes.c_ubyte * self.n)(*([3] * self.n if flags is None else [int(f) for f in flags]))
+        ss = ctypes.c_double(0.0)
+        _check(self.lib.tmt_adamw_step(self.h, _ptr_array(master), _ptr_array(m), _ptr_array(v), _ptr_array(grad),
+                                       _ptr_array(work), fl, ctypes.c_float(clip), ctypes.c_float(lr), ctypes.c_float(b1),
+                                       ctypes.c_float(b2), ctypes.c_float(eps), ctypes.c_float(wd), int(step),
+                                       int(bool(zero_grads)), ctypes.byref(ss) if want_norm else None), self.lib)
+        return ss.value if want_norm else None
+
+    def close(self):
+        if self.h:
+            self.lib.tmt_adamw_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:   # noqa: BLE001
+            pass
 
 
 def quantize_nvfp4(W, rows, cols, packed, scales, stream=None):

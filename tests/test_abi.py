@@ -18,14 +18,25 @@ def lib():
 
 
 def test_every_declared_symbol_is_exported(lib):
-    text = open(os.path.join(ROOT, "include", "tmt_moe.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = set(re.findall(r"\b(tmt_moe_[a-z0-9_]+)\s*\(", text))
-    assert len(names) >= 20
+    names = set()
+    for header in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(tmt_(?:moe|adamw)_[a-z0-9_]+)\s*\(", text))
+    assert len(names) >= 23 and "tmt_adamw_step" in names
     for n in sorted(names):
         assert hasattr(lib, n), n
     import tmt_moe_b200 as M
     assert set(M.EXPORTS) <= names
+
+
+def test_adamw_fails_cleanly_on_bad_arguments(lib):
+    assert lib.tmt_adamw_create(0, None, 0, None, None) == -1
+    h = ctypes.c_void_p()
+    assert lib.tmt_adamw_create(0, None, 0, None, ctypes.byref(h)) == -1
+    assert b"tensor" in lib.tmt_moe_last_error()
+    assert lib.tmt_adamw_step(None, None, None, None, None, None, None, ctypes.c_float(0), ctypes.c_float(0), ctypes.c_float(0),
+                              ctypes.c_float(0), ctypes.c_float(0), ctypes.c_float(0), 1, 0, None) == -1
 
 
 def test_create_fails_cleanly_without_gpu_or_with_bad_arguments(lib):
