@@ -254,14 +254,82 @@ def bench_adamw(args):
     print(json.dumps(line), flush=True)
 
 
+def bench_ln(args):
+    """LayerNorm (include/tmt_norm.h) on config 5's activations (131072 x 2048 bf16), forward + backward per step.
+    HBM-bound: forward reads X and writes Y (4 bytes per element), backward reads X and dY and writes dX (6 bytes)."""
+    import numpy as np
+    import torch
+    import tmt_moe_b200 as M
+    from oracle import oracle as O
+    c5 = CONFIGS["c5"]
+    rows, D = c5["T"], c5["D"]
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(9)
+    X = (torch.randn((rows, D), generator=g, device="cuda") * 1.5 + 0.3).to(torch.bfloat16)
+    dY = (torch.randn((rows, D), generator=g, device="cuda") * 1e-2).to(torch.bfloat16)
+    gamma = 1 + 0.1 * torch.randn(D, generator=g, device="cuda")
+    beta = 0.1 * torch.randn(D, generator=g, device="cuda")
+    Y, dX = torch.empty_like(X), torch.empty_like(X)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    dG, dB = torch.empty(D, device="cuda"), torch.empty(D, device="cuda")
+    scratch = torch.empty(M.ln_backward_scratch_bytes(rows, D) // 4, device="cuda")
+
+    def step():
+        M.ln_forward(X, gamma, beta, Y, mean, rstd)
+        M.ln_backward(X, dY, gamma, mean, rstd, dX, dG, dB, scratch)
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ef = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps)]
+    wall0 = time.time()
+    for i in range(args.steps):
+        ef[3 * i].record()
+        M.ln_forward(X, gamma, beta, Y, mean, rstd)
+        ef[3 * i + 1].record()
+        M.ln_backward(X, dY, gamma, mean, rstd, dX, dG, dB, scratch)
+        ef[3 * i + 2].record()
+    torch.cuda.synchronize()
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1)
+    fwd = sum(ef[3 * i].elapsed_time(ef[3 * i + 1]) for i in range(args.steps)) / args.steps
+    bwd = sum(ef[3 * i + 1].elapsed_time(ef[3 * i + 2]) for i in range(args.steps)) / args.steps
+    pk, kind = peaks()
+    n = rows * D
+    gb_f, gb_b = 4.0 * n / (fwd * 1e-3) / 1e9, 6.0 * n / (bwd * 1e-3) / 1e9
+    line = dict(metric="layernorm_rows_per_s_fwd_bwd", unit="rows/s", n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3),
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16 (fp32 statistics)", data="synthetic",
+                value=rows / ((fwd + bwd) * 1e-3), ms_per_step=fwd + bwd,
+                config={"workload": "LayerNorm forward + backward on %d x %d bf16 activations (config 5's layer input)" % (rows, D),
+                        "l2": "working set larger than L2 (no flush needed)"},
+                clocks=clocks, gpu_launches=3 * args.steps,
+                roofline={"bound": "hbm", "kernel": "ln_bwd_kernel (forward beside it)", "achieved": gb_b, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                          "frac": gb_b / pk["hbm_gbs"], "traffic": None, "peak_kind": kind,
+                          "forward": {"ms": fwd, "achieved": gb_f, "frac": gb_f / pk["hbm_gbs"]}, "backward_ms": bwd})
+    if not args.no_cpu_baseline:
+        sample = 2048
+        hx, hdy = X[:sample].cpu().view(torch.int16).numpy().view(np.uint16), dY[:sample].cpu().view(torch.int16).numpy().view(np.uint16)
+        hg, hb = gamma.cpu().numpy(), beta.cpu().numpy()
+        t0 = time.perf_counter()
+        _, hm, hr = O.ln_forward(hx, hg, hb)
+        O.ln_backward(hx, hdy, hg, hm, hr)
+        sec = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": sample / sec, "unit": "rows/s", "cores": 1, "kind": "port",
+                                "sample": "first %d rows, forward + backward, one thread (%.2f s)" % (sample, sec)}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS) + ["adamw5"],
+    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS) + ["adamw5", "ln5"],
                     help="c1..c5: the MoE layer workloads; adamw5: the optimizer step over config 5's expert and router parameters "
-                         "(the component after the layer's backward pass; its own metric, not the headline)")
+                         "(the component after the layer's backward pass); ln5: the LayerNorm in front of the layer on config 5's "
+                         "activations, forward + backward. Both print their own metric, not the headline")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -275,6 +343,8 @@ def main():
     args = ap.parse_args()
     if args.config == "adamw5":
         return bench_adamw(args)
+    if args.config == "ln5":
+        return bench_ln(args)
     cfg = dict(CONFIGS[args.config])
     if args.tokens:
         cfg["T"] = args.tokens

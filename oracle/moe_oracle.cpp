@@ -189,7 +189,7 @@ struct oracle_cfg {
     int pad;         // rows every expert group is padded to (0 = 128, the reference's padding)
 };
 
-int oracle_abi_version() { return 5; }
+int oracle_abi_version() { return 6; }
 
 // moe.cu:10-68 (+ optional per-expert logit bias, which the reference lacks).
 void oracle_router(const oracle_cfg* c, const uint16_t* X, const void* Wr, const float* bias,
@@ -603,6 +603,76 @@ void oracle_adamw(float* master, float* m, float* v, const float* grad, uint16_t
         const float w = std::fmaf(-lr, std::fmaf(wd, master[i], u), master[i]);
         m[i] = nm; v[i] = nv; master[i] = w;
         if (work) work[i] = f2bf(w);
+    }
+}
+
+
+// LayerNorm (tmt-cuda/src/norm.cu:8-110) with the summation orders stated in include/tmt_norm.h.
+static float butterfly32(const float* lanes) {       // v += v[lane ^ 16], ^8, ^4, ^2, ^1; every lane ends with the same value
+    float a[32], b[32];
+    for (int i = 0; i < 32; ++i) a[i] = lanes[i];
+    for (int off = 16; off > 0; off >>= 1) {
+        for (int i = 0; i < 32; ++i) b[i] = a[i] + a[i ^ off];
+        for (int i = 0; i < 32; ++i) a[i] = b[i];
+    }
+    return a[0];
+}
+
+void oracle_ln_forward(const uint16_t* X, const float* gamma, const float* beta, uint16_t* Y, float* mean, float* rstd,
+                       long rows, int D) {
+    const int nvec = D / 8;
+    for (long r = 0; r < rows; ++r) {
+        const uint16_t* x = X + r * D;
+        float sum[32], sq[32];
+        for (int l = 0; l < 32; ++l) {
+            sum[l] = 0.0f; sq[l] = 0.0f;
+            for (int v = l; v < nvec; v += 32)
+                for (int q = 0; q < 8; ++q) {
+                    const float f = bf2f(x[v * 8 + q]);
+                    sum[l] = sum[l] + f;
+                    sq[l] = std::fmaf(f, f, sq[l]);
+                }
+        }
+        const float fd = (float)D;
+        const float m = butterfly32(sum) / fd;
+        const float var = butterfly32(sq) / fd - m * m;
+        const float rs = 1.0f / std::sqrt(var + 1e-5f);
+        mean[r] = m; rstd[r] = rs;
+        for (int d = 0; d < D; ++d) Y[r * D + d] = f2bf(std::fmaf((bf2f(x[d]) - m) * rs, gamma[d], beta[d]));
+    }
+}
+
+void oracle_ln_backward(const uint16_t* X, const uint16_t* dY, const float* gamma, const float* mean, const float* rstd,
+                        uint16_t* dX, float* dGamma, float* dBeta, long rows, int D) {
+    const int nvec = D / 8, kThreads = 256, kRows = 128;
+    const float fd = (float)D;
+    std::vector<float> g(D), xh(D), bg(D), bb(D);
+    for (int d = 0; d < D; ++d) { dGamma[d] = 0.0f; dBeta[d] = 0.0f; }
+    for (long r0 = 0; r0 < rows; r0 += kRows) {
+        for (int d = 0; d < D; ++d) { bg[d] = 0.0f; bb[d] = 0.0f; }
+        for (long r = r0; r < r0 + kRows && r < rows; ++r) {
+            const float m = mean[r], rs = rstd[r];
+            float s1[256], s2[256];
+            for (int t = 0; t < kThreads; ++t) {
+                s1[t] = 0.0f; s2[t] = 0.0f;
+                for (int v = t; v < nvec; v += kThreads)
+                    for (int q = 0; q < 8; ++q) {
+                        const int d = v * 8 + q;
+                        const float dy = bf2f(dY[r * D + d]);
+                        xh[d] = (bf2f(X[r * D + d]) - m) * rs;
+                        g[d] = dy * gamma[d];
+                        s1[t] = s1[t] + g[d];
+                        s2[t] = std::fmaf(g[d], xh[d], s2[t]);
+                        bg[d] = std::fmaf(dy, xh[d], bg[d]);
+                        bb[d] = bb[d] + dy;
+                    }
+            }
+            float t1 = 0.0f, t2 = 0.0f;
+            for (int w = 0; w < kThreads / 32; ++w) { t1 = t1 + butterfly32(s1 + 32 * w); t2 = t2 + butterfly32(s2 + 32 * w); }
+            const float a = t1 / fd, b = t2 / fd;
+            for (int d = 0; d < D; ++d) dX[r * D + d] = f2bf(rs * ((g[d] - a) - xh[d] * b));
+        }
+        for (int d = 0; d < D; ++d) { dGamma[d] = dGamma[d] + bg[d]; dBeta[d] = dBeta[d] + bb[d]; }
     }
 }
 

@@ -38,7 +38,7 @@ def lib():
         _lib.oracle_abi_version.restype = ctypes.c_int
         _lib.oracle_sumsq.restype = ctypes.c_double
         _lib.oracle_clip_scale.restype = ctypes.c_float
-        assert _lib.oracle_abi_version() == 5, "stale oracle library: run make -C oracle -B"
+        assert _lib.oracle_abi_version() == 6, "stale oracle library: run make -C oracle -B"
     return _lib
 
 
@@ -221,3 +221,25 @@ def sumsq(grads):
 
 def clip_scale(ss, clip):
     return float(lib().oracle_clip_scale(ctypes.c_double(ss), ctypes.c_float(clip)))
+
+
+def ln_forward(X, gamma, beta):
+    """LayerNorm forward (norm.cu:8-50). X (rows, D) bf16 bits. Returns Y (bf16 bits), mean, rstd."""
+    rows, D = X.shape
+    X = np.ascontiguousarray(X, np.uint16)
+    Y = np.empty((rows, D), np.uint16)
+    mean, rstd = np.empty(rows, np.float32), np.empty(rows, np.float32)
+    lib().oracle_ln_forward(_p(X), _p(np.ascontiguousarray(gamma, np.float32)), _p(np.ascontiguousarray(beta, np.float32)), _p(Y),
+                            _p(mean), _p(rstd), ctypes.c_long(rows), ctypes.c_int(D))
+    return Y, mean, rstd
+
+
+def ln_backward(X, dY, gamma, mean, rstd):
+    """LayerNorm backward (norm.cu:54-94). Returns dX (bf16 bits), dGamma, dBeta."""
+    rows, D = X.shape
+    dX = np.empty((rows, D), np.uint16)
+    dG, dB = np.empty(D, np.float32), np.empty(D, np.float32)
+    lib().oracle_ln_backward(_p(np.ascontiguousarray(X, np.uint16)), _p(np.ascontiguousarray(dY, np.uint16)),
+                             _p(np.ascontiguousarray(gamma, np.float32)), _p(np.ascontiguousarray(mean, np.float32)),
+                             _p(np.ascontiguousarray(rstd, np.float32)), _p(dX), _p(dG), _p(dB), ctypes.c_long(rows), ctypes.c_int(D))
+    return dX, dG, dB

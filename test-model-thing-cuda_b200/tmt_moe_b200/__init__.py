@@ -28,6 +28,7 @@ EXPORTS = (
     "tmt_moe_copy_stats", "tmt_moe_selftest_bounded_wait", "tmt_moe_router_dw_noalloc",
     "tmt_moe_debug_gemm_cycles", "tmt_moe_step_host_async", "tmt_moe_host_wait",
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
+    "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes",
 )
 
 
@@ -244,6 +245,27 @@ class MoE:
 
     def device_status(self):
         return self.lib.tmt_moe_device_status(self.h)
+
+
+def ln_forward(X, gamma, beta, Y, mean, rstd, stream=None):
+    """LayerNorm forward (include/tmt_norm.h; layernorm_fwd, tmt-cuda/src/norm.cu:96-100). Torch CUDA tensors."""
+    lib = load()
+    rows, dim = X.shape
+    _check(lib.tmt_ln_forward(_ptr(X), _ptr(gamma), _ptr(beta), _ptr(Y), _ptr(mean), _ptr(rstd), int(rows), int(dim), _ptr(stream)), lib)
+
+
+def ln_backward_scratch_bytes(rows, dim):
+    lib = load()
+    lib.tmt_ln_backward_scratch_bytes.restype = ctypes.c_size_t
+    return int(lib.tmt_ln_backward_scratch_bytes(int(rows), int(dim)))
+
+
+def ln_backward(X, dY, gamma, mean, rstd, dX, dGamma, dBeta, scratch, stream=None):
+    """LayerNorm backward (layernorm_bwd, norm.cu:102-110); scratch: ln_backward_scratch_bytes(rows, dim) bytes."""
+    lib = load()
+    rows, dim = X.shape
+    _check(lib.tmt_ln_backward(_ptr(X), _ptr(dY), _ptr(gamma), _ptr(mean), _ptr(rstd), _ptr(dX), _ptr(dGamma), _ptr(dBeta),
+                               int(rows), int(dim), _ptr(scratch), _ptr(stream)), lib)
 
 
 class AdamW:

@@ -14,10 +14,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q, transport, gemm_impl=0):
+def _worker(rank, world, port, q, transport, gemm_impl=0, waves=1):
     try:
         sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TMT_MOE_EP_WAVES=str(waves))
         import torch.distributed as dist
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -77,14 +77,15 @@ def _worker(rank, world, port, q, transport, gemm_impl=0):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport,gemm_impl", [pytest.param(0, 0, id="peer"), pytest.param(1, 0, id="nccl"),
-                                                 pytest.param(0, 2, id="peer-cta_pairs"), pytest.param(1, 2, id="nccl-cta_pairs")])
-def test_expert_parallel_two_gpus(transport, gemm_impl):
+@pytest.mark.parametrize("transport,gemm_impl,waves", [pytest.param(0, 0, 1, id="peer"), pytest.param(1, 0, 1, id="nccl"),
+                                                       pytest.param(0, 2, 1, id="peer-cta_pairs"), pytest.param(1, 2, 1, id="nccl-cta_pairs"),
+                                                       pytest.param(0, 2, 2, id="peer-cta_pairs-two_expert_waves")])
+def test_expert_parallel_two_gpus(transport, gemm_impl, waves):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 200 + 7 * transport + 17 * gemm_impl
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport, gemm_impl)) for r in range(world)]
+    port = 29700 + os.getpid() % 200 + 7 * transport + 17 * gemm_impl + 3 * waves
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport, gemm_impl, waves)) for r in range(world)]
     for p in procs:
         p.start()
     res = []
