@@ -135,49 +135,6 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int e, long 
     }
 }
 
-// The same epilogues without the stores: 32 accumulator columns of one row -> packed bf16 words
-// (w0: the main output, w1: the pre-activation of kEpiUp). Used by the shared-memory staged path.
-template <int EPI>
-__device__ __forceinline__ void epilogue_math(const GemmParams& p, int e, long row, int col0, float (&v)[kChunk],
-                                              uint32_t (&w0)[kChunk / 2], uint32_t (&w1)[kChunk / 2], float& sw) {
-    const float es = p.expert_scale ? p.expert_scale[e] : 1.0f;
-    if constexpr (EPI == kEpiDown) {
-        const float rs = p.row_scale[row];
-#pragma unroll
-        for (int i = 0; i < kChunk; ++i) v[i] = rs * (es * v[i]);
-    }
-    if constexpr (EPI == kEpiUp) {
-#pragma unroll
-        for (int i = 0; i < kChunk / 2; ++i) {
-            const float a = round_bf(es * v[2 * i]), b = round_bf(es * v[2 * i + 1]);
-            w1[i] = pack_bf2(a, b);
-            w0[i] = pack_bf2(a * sigmoid_fast(a), b * sigmoid_fast(b));
-        }
-        return;
-    }
-    if constexpr (EPI == kEpiDh) {
-        const uint16_t* pp = p.P + row * p.ldc + col0;
-#pragma unroll
-        for (int q = 0; q < kChunk / 8; ++q) {
-            if (col0 + q * 8 >= p.N) break;
-            const uint4 pv = ldg16(pp + q * 8);
-            const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float x0 = bf_lo(pw[i]), x1 = bf_hi(pw[i]);
-                const float s0 = sigmoid_fast(x0), s1 = sigmoid_fast(x1);
-                const float a0 = v[q * 8 + 2 * i], a1 = v[q * 8 + 2 * i + 1];
-                sw += a0 * (x0 * s0);
-                sw += a1 * (x1 * s1);
-                v[q * 8 + 2 * i] = a0 * (s0 * (1.0f + x0 * (1.0f - s0)));
-                v[q * 8 + 2 * i + 1] = a1 * (s1 * (1.0f + x1 * (1.0f - s1)));
-            }
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < kChunk / 2; ++i) w0[i] = pack_bf2(v[2 * i], v[2 * i + 1]);
-}
-
 // Launchers (gemm_tcgen05.cu / gemm_simt.cu). Both return the cudaError of the launch.
 cudaError_t launch_gemm_tcgen05(const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_tcgen05_2cta(const GemmParams& p, int num_sms, cudaStream_t stream);

@@ -69,8 +69,10 @@ __device__ __forceinline__ void epi_math32(float (&v)[kChunk], float es, float r
             }
         }
     }
+    if constexpr (EPI != kEpiUp) {
 #pragma unroll
-    for (int i = 0; i < kChunk / 2; ++i) w0[i] = pack_bf2(v[2 * i], v[2 * i + 1]);
+        for (int i = 0; i < kChunk / 2; ++i) w0[i] = pack_bf2(v[2 * i], v[2 * i + 1]);
+    }
 }
 
 // Staged bf16 epilogue: 8 warps in two groups, each group drains 128 of the tile's 256 columns in chunks of 32
@@ -167,66 +169,37 @@ __device__ __forceinline__ bool epi_drain_tile(const GemmParams& p, EpiState& s,
     const long row = (long)row0 + r_in_tile;
     float sw = 0.0f;
     if (s.staged && EPI != kEpiF32) {
-        static_assert(EPI == kEpiF32 || GROUPS == 2, "the staged bf16 epilogue runs with two groups of four warps");
-        if (!epi_drain_bf16<EPI>(p, s, expert, row0, tcol0, nkb, tm, row_ok, sw)) return false;
+        if constexpr (EPI != kEpiF32) {
+            static_assert(GROUPS == 2, "the staged bf16 epilogue runs with two groups of four warps");
+            if (!epi_drain_bf16<EPI>(p, s, expert, row0, tcol0, nkb, tm, row_ok, sw)) return false;
+        }
     } else if (s.staged) {
-        constexpr bool kF32 = EPI == kEpiF32;
-        constexpr int kCols = kF32 ? 32 : 64;                 // columns per staged chunk: 128 bytes per row
-        const bool two = EPI == kEpiUp && p.mapC1 != nullptr;
+        // fp32 output (one group of four warps): 32-column chunks, 128 bytes per row, two 16 KB buffers in turn
+        constexpr int kCols = 32;
         const CUtensorMap* m0 = p.mapC0 + (size_t)expert * p.c_stride;
-        const CUtensorMap* m1 = two ? p.mapC1 + (size_t)expert * p.c_stride : nullptr;
         const uint32_t rsw = (uint32_t)(r_in_tile & 7);
         const uint32_t rbase = (uint32_t)r_in_tile * 128u;
 #pragma unroll 1
         for (int cc = s.half * (kWarpCols / kCols); cc < (s.half + 1) * (kWarpCols / kCols); ++cc) {
             const int ccol0 = tcol0 + cc * kCols;
             if (ccol0 >= p.N) break;
-            // buffer choice: two outputs or two groups -> one buffer each, reused every chunk; else alternate
-            constexpr bool single = (EPI == kEpiUp) || GROUPS == 2;
-            const uint32_t b0 = s.cbuf + (uint32_t)((EPI == kEpiUp) ? 0 : (GROUPS == 2 ? s.half : (s.use & 1))) * kStagingBytes;
-            const uint32_t b1 = s.cbuf + kStagingBytes;
-            if (s.issuer) { if (single) bulk_wait_read<0>(); else bulk_wait_read<1>(); }
+            const uint32_t b0 = s.cbuf + (uint32_t)(s.use & 1) * kStagingBytes;
+            if (s.issuer) bulk_wait_read<1>();         // the store that read this buffer two chunks ago is done
             if (!epi_group_sync(s, p.status)) return false;
-            if constexpr (kF32) {
-                float v[kChunk];
-                if (nkb > 0) tmem_ld32(tm + (uint32_t)(cc * kCols), v);
-                else {
+            float v[kChunk];
+            if (nkb > 0) tmem_ld32(tm + (uint32_t)(cc * kCols), v);
+            else {
 #pragma unroll
-                    for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
-                }
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    st_shared16(b0 + rbase + (((uint32_t)q ^ rsw) << 4), __float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
-                                __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
-            } else {
-#pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
-                    const int col0 = ccol0 + sub * kChunk;
-                    float v[kChunk];
-                    uint32_t w0[kChunk / 2], w1[kChunk / 2];
-                    if (nkb > 0) tmem_ld32(tm + (uint32_t)(cc * kCols + sub * kChunk), v);
-                    else {
-#pragma unroll
-                        for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
-                    }
-                    if (col0 < p.N && row_ok) epilogue_math<EPI>(p, expert, row, col0, v, w0, w1, sw);
-                    else {
-#pragma unroll
-                        for (int i = 0; i < kChunk / 2; ++i) { w0[i] = 0; w1[i] = 0; }
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint32_t off = rbase + ((((uint32_t)(sub * 4 + q)) ^ rsw) << 4);
-                        st_shared16(b0 + off, w0[4 * q], w0[4 * q + 1], w0[4 * q + 2], w0[4 * q + 3]);
-                        if (two) st_shared16(b1 + off, w1[4 * q], w1[4 * q + 1], w1[4 * q + 2], w1[4 * q + 3]);
-                    }
-                }
+                for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
             }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                st_shared16(b0 + rbase + (((uint32_t)q ^ rsw) << 4), __float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
+                            __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
             fence_async_smem();
             if (!epi_group_sync(s, p.status)) return false;
             if (s.issuer && !(p.dbg & 4)) {
                 tma_store_2d(m0, b0, ccol0, row0);
-                if (two) tma_store_2d(m1, b1, ccol0, row0);
                 bulk_commit();
             }
             ++s.use;
