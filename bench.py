@@ -334,6 +334,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="config c3: run the decode loop eagerly (per-phase times become available)")
     ap.add_argument("--gemm-cycles", action="store_true",
                     help="measurement only: print (stderr) where the TMA, MMA and epilogue threads of the last GEMM launches spent their cycles")
     ap.add_argument("--gemm", default="2cta", choices=["2cta", "1cta"],
@@ -431,6 +432,8 @@ def main():
         launches0_per_loop = moe.launch_count - lc      # kernels one replay of the captured loop launches
         step = decode_loop
         try:                                 # the launch-bound loop as one CUDA graph on the handle's stream
+            if args.no_graph:
+                raise RuntimeError("eager loop requested (--no-graph)")
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=work_stream):
                 decode_loop()
