@@ -133,6 +133,14 @@ const char* tmt_moe_phase_name(int i);
 /* Number of kernel launches the handle has queued since creation (the reference counts
  * nothing; used by the benchmark to report its launch count). */
 long long tmt_moe_launch_count(const tmt_moe* h);
+/* Router-balance telemetry (train_main.cu:204-209, 232-248; capi.cu:131-136 tmt_model_expert_counts): tokens routed
+ * to each expert, accumulated ON THE DEVICE over every forward pass since the last reset (the reference adds the
+ * host-side hcnt of every window). Returns the reference's summary: min_share / max_share = smallest / largest
+ * expert share with 1.0 = uniform, dead = experts with a share below 0.01, passes = forward passes counted, totals
+ * (may be NULL) = the E accumulated counts. reset != 0 clears the accumulators. Synchronises. Under expert parallelism
+ * the counts are those of this rank's tokens (over all experts). */
+int tmt_moe_usage(tmt_moe* h, double* min_share, double* max_share, long long* dead, long long* passes,
+                  long long* totals, int reset);
 /* Measurement only (no counterpart in the reference). With TMT_MOE_GEMM_CYCLES=1 in the environment at
  * tmt_moe_create, every tcgen05 GEMM launch records, per CTA, the clock cycles its TMA, MMA and
  * epilogue threads spent waiting and working. Copies the ring of the last *launches launches

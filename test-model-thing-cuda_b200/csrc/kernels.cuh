@@ -27,6 +27,7 @@ struct RouteBufs {
     int* tok_of_slot;     // cap   token of each grouped row (-1 on pad rows)
     int* split_poff;      // kMaxSplits+1 row ranges (multiples of kPad) the router weight-gradient GEMM splits its reduction into
     int* status;
+    long long* use_acc;   // E+1  tokens routed to each expert since the last reset, [E] = forward passes counted (train_main.cu:204-209)
 };
 
 struct RouteDims {

@@ -630,6 +630,8 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     b.split_poff = dalloc<int>(h, kMaxSplits + 1);
     b.status = dalloc<int>(h, 1);
     CK(cudaMemsetAsync(b.status, 0, sizeof(int), h->stream));
+    b.use_acc = dalloc<long long>(h, E + 1);
+    CK(cudaMemsetAsync(b.use_acc, 0, sizeof(long long) * (E + 1), h->stream));
     h->bias = dalloc<float>(h, E);
     h->Xg = dalloc<uint16_t>(h, (size_t)gcap * D);
     h->Yg = dalloc<uint16_t>(h, (size_t)gcap * D);
@@ -942,6 +944,33 @@ int tmt_moe_selftest_bounded_wait(tmt_moe* h, long long limit_cycles) {
 }
 
 long long tmt_moe_launch_count(const tmt_moe* h) { return h ? h->launches : -1; }
+
+int tmt_moe_usage(tmt_moe* h, double* min_share, double* max_share, long long* dead, long long* passes, long long* totals,
+                  int reset) {
+    if (!h) { set_error("null handle"); return -1; }
+    GUARD({
+        CK(cudaSetDevice(h->d.device));
+        const int E = h->d.experts;
+        std::vector<long long> acc(E + 1);
+        CK(cudaMemcpyAsync(acc.data(), h->rb.use_acc, sizeof(long long) * (E + 1), cudaMemcpyDeviceToHost, h->stream));
+        if (reset) CK(cudaMemsetAsync(h->rb.use_acc, 0, sizeof(long long) * (E + 1), h->stream));
+        CK(cudaStreamSynchronize(h->stream));
+        long long tot = 0;
+        for (int e = 0; e < E; ++e) tot += acc[e];
+        double mn = 1, mx = 0;                     // train_main.cu:235-243: share 1.0 = uniform, dead below 0.01
+        long long nd = 0;
+        for (int e = 0; e < E; ++e) {
+            const double s = tot ? (double)acc[e] / (double)tot * E : 0;
+            mn = std::min(mn, s); mx = std::max(mx, s);
+            if (s < 0.01) ++nd;
+        }
+        if (min_share) *min_share = mn;
+        if (max_share) *max_share = mx;
+        if (dead) *dead = nd;
+        if (passes) *passes = acc[E];
+        if (totals) for (int e = 0; e < E; ++e) totals[e] = acc[e];
+    })
+}
 
 int tmt_moe_debug_gemm_cycles(tmt_moe* h, long long* out, int* launches, int* ctas, int* slots) {
     if (!h) { set_error("null handle"); return -1; }

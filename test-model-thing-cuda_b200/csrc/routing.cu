@@ -301,7 +301,10 @@ __global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, con
         b.off[E] = tk; poff_s[E] = ptk; b.poff[E] = ptk;
         if (ptk > d.cap) { report(b.status, kErrSlotRange); ptk = 0; }
         *b.num_m_tiles = ptk / kPad;
+        if (b.use_acc) b.use_acc[E] += 1;
     }
+    if (b.use_acc)      // router-balance telemetry: usage accumulated on the device, read when the host asks
+        for (int e = threadIdx.x; e < E; e += blockDim.x) b.use_acc[e] += b.counts[e];
     __syncthreads();
     const int used = poff_s[E] <= d.cap ? poff_s[E] / kPad : 0;
     for (int i = threadIdx.x; i < d.max_tiles; i += blockDim.x) {

@@ -28,7 +28,7 @@ EXPORTS = (
     "tmt_moe_copy_stats", "tmt_moe_selftest_bounded_wait", "tmt_moe_router_dw_noalloc",
     "tmt_moe_debug_gemm_cycles", "tmt_moe_step_host_async", "tmt_moe_host_wait",
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
-    "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes",
+    "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes", "tmt_moe_usage",
 )
 
 
@@ -152,6 +152,16 @@ class MoE:
                                           _ptr_array(Wdown), _ptr(dWrouter), _ptr_array(dWup), _ptr_array(dWdown),
                                           _ptr(Y_host), _ptr(dX_host), _ptr(stat_host), ctypes.c_float(beta),
                                           ctypes.c_float(aux), ctypes.c_float(zcoef), t), self.lib)
+
+    def usage(self, reset=False):
+        """Router-balance telemetry since the last reset: dict(min_share, max_share, dead, passes, totals[E])."""
+        import numpy as np
+        mn, mx = ctypes.c_double(), ctypes.c_double()
+        dead, passes = ctypes.c_longlong(), ctypes.c_longlong()
+        totals = np.zeros(self.experts, np.int64)
+        _check(self.lib.tmt_moe_usage(self.h, ctypes.byref(mn), ctypes.byref(mx), ctypes.byref(dead), ctypes.byref(passes),
+                                      totals.ctypes.data_as(ctypes.c_void_p), int(reset)), self.lib)
+        return dict(min_share=mn.value, max_share=mx.value, dead=dead.value, passes=passes.value, totals=totals)
 
     def host_wait(self):
         _check(self.lib.tmt_moe_host_wait(self.h), self.lib)

@@ -295,3 +295,27 @@ def test_argument_errors():
         m.forward(x, x, [x] * 4, [x] * 4, x, tokens=65)
     with pytest.raises(M.MoeError):
         m.backward(x, x, [x] * 4, [x] * 4, x, [x] * 4, [x] * 4, x)
+
+
+def test_router_usage_telemetry_accumulates_on_the_device():
+    """tmt_moe_usage: counts of every forward pass since the last reset, and the reference's summary of them
+    (train_main.cu:232-248: share 1.0 = uniform, dead below 0.01)."""
+    T, D, H, E, K = 700, 128, 128, 8, 2
+    bias = np.array([0, 0, 0, 0, 0, 0, 0, -60.0], np.float32)          # expert 7 never wins
+    total = np.zeros(E, np.int64)
+    layer = None
+    for seed in (31, 32, 33):
+        data = synth.make(T, D, H, E, K, seed=seed)
+        if layer is None:
+            layer = G.Layer(data, T, D, E, K, H, bias=bias)
+            assert layer.moe.usage(reset=True)["passes"] == 0
+        layer.X = G.dev(data["X"])
+        layer.forward()
+        total += layer.moe.read("counts").astype(np.int64)
+    u = layer.moe.usage()
+    np.testing.assert_array_equal(u["totals"], total)
+    assert u["passes"] == 3 and total[7] == 0 and u["dead"] == 1
+    share = total / total.sum() * E
+    assert abs(u["min_share"] - share.min()) < 1e-12 and abs(u["max_share"] - share.max()) < 1e-12
+    assert layer.moe.usage(reset=True)["passes"] == 3
+    assert layer.moe.usage()["passes"] == 0 and layer.moe.usage()["totals"].sum() == 0
