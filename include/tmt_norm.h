@@ -13,9 +13,10 @@
  * in index order (sq = fma(x, x, sq)); lanes combine by the butterfly v += v[lane ^ 16], ^8, ^4, ^2, ^1.
  *   mean = sum / D;  var = sumsq / D - mean * mean;  rstd = 1 / sqrt(var + 1e-5)   (IEEE division and square root)
  *   y = bf16(fma((x - mean) * rstd, gamma, beta))
- * Backward, per row with g = bf16 dy * gamma and xh = (x - mean) * rstd: thread t of 256 owns vectors t, t + 256, ...;
- * s1 = sum g, s2 = sum g * xh (fma) over its elements, warp butterfly as above, the 8 warp sums added in warp order;
- * a = s1 / D, b = s2 / D, dx = bf16(rstd * ((g - a) - xh * b)); dGamma[d] += dy * xh and dBeta[d] += dy run over the
+ * Backward, per row with g = dy * gamma and xh = fma(x, rstd, -(mean * rstd)): thread t of 256 owns vectors t, t + 256,
+ * ...; s1 = sum g, s2 = sum g * xh (fma) over its elements, warp butterfly as above, the 8 warp sums added in warp
+ * order; a = s1 / D, b = s2 / D, dx = bf16(fma(xh, -(rstd * b), fma(g, rstd, -(rstd * a)))), i.e. the reference's
+ * rstd * (g - a - xh * b) with fused multiply-adds; dGamma[d] = fma(dy, xh, dGamma[d]) and dBeta[d] += dy run over the
  * rows of a 128-row block in row order, and the block sums are added in block order. */
 #ifndef TMT_NORM_H
 #define TMT_NORM_H

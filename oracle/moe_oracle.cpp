@@ -652,6 +652,7 @@ void oracle_ln_backward(const uint16_t* X, const uint16_t* dY, const float* gamm
         for (int d = 0; d < D; ++d) { bg[d] = 0.0f; bb[d] = 0.0f; }
         for (long r = r0; r < r0 + kRows && r < rows; ++r) {
             const float m = mean[r], rs = rstd[r];
+            const float nmr = -(m * rs);
             float s1[256], s2[256];
             for (int t = 0; t < kThreads; ++t) {
                 s1[t] = 0.0f; s2[t] = 0.0f;
@@ -659,7 +660,7 @@ void oracle_ln_backward(const uint16_t* X, const uint16_t* dY, const float* gamm
                     for (int q = 0; q < 8; ++q) {
                         const int d = v * 8 + q;
                         const float dy = bf2f(dY[r * D + d]);
-                        xh[d] = (bf2f(X[r * D + d]) - m) * rs;
+                        xh[d] = std::fmaf(bf2f(X[r * D + d]), rs, nmr);
                         g[d] = dy * gamma[d];
                         s1[t] = s1[t] + g[d];
                         s2[t] = std::fmaf(g[d], xh[d], s2[t]);
@@ -670,7 +671,8 @@ void oracle_ln_backward(const uint16_t* X, const uint16_t* dY, const float* gamm
             float t1 = 0.0f, t2 = 0.0f;
             for (int w = 0; w < kThreads / 32; ++w) { t1 = t1 + butterfly32(s1 + 32 * w); t2 = t2 + butterfly32(s2 + 32 * w); }
             const float a = t1 / fd, b = t2 / fd;
-            for (int d = 0; d < D; ++d) dX[r * D + d] = f2bf(rs * ((g[d] - a) - xh[d] * b));
+            const float c0 = -(rs * a), c1 = -(rs * b);
+            for (int d = 0; d < D; ++d) dX[r * D + d] = f2bf(std::fmaf(xh[d], c1, std::fmaf(g[d], rs, c0)));
         }
         for (int d = 0; d < D; ++d) { dGamma[d] = dGamma[d] + bg[d]; dBeta[d] = dBeta[d] + bb[d]; }
     }

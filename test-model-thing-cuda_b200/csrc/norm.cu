@@ -171,7 +171,9 @@ __global__ void __launch_bounds__(kBwdThreads) ln_bwd_kernel(const uint16_t* __r
         cp_async_wait<P - RI>();                   // the RI oldest rows have landed (each thread waits for its own copies)
         uint4 cdy[RI][NV], cx[RI][NV];
         float kg[KEEP ? RI : 1][NV][8], kxh[KEEP ? RI : 1][NV][8];     // KEEP: g and xh stay in registers for the second half
-        float s1[RI], s2[RI];
+        float s1[RI], s2[RI], nmr[RI];
+#pragma unroll
+        for (int j = 0; j < RI; ++j) nmr[j] = -__fmul_rn(cm[j], crs[j]);      // xh = fma(x, rstd, -mean * rstd)
 #pragma unroll
         for (int j = 0; j < RI; ++j) {
             s1[j] = 0.0f; s2[j] = 0.0f;
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(kBwdThreads) ln_bwd_kernel(const uint16_t* __r
                         unpack8(cx[j][i], x);
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
-                            const float xh = __fmul_rn(__fsub_rn(x[q], cm[j]), crs[j]);
+                            const float xh = __fmaf_rn(x[q], crs[j], nmr[j]);
                             const float g = __fmul_rn(dy[q], gam[i][q]);
                             if constexpr (KEEP) { kg[j][i][q] = g; kxh[j][i][q] = xh; }
                             s1[j] = __fadd_rn(s1[j], g);
@@ -222,6 +224,7 @@ __global__ void __launch_bounds__(kBwdThreads) ln_bwd_kernel(const uint16_t* __r
 #pragma unroll
                 for (int w = 0; w < 8; ++w) { t1 = __fadd_rn(t1, p1[w]); t2 = __fadd_rn(t2, p2[w]); }
                 const float a = __fdiv_rn(t1, fd), b = __fdiv_rn(t2, fd);
+                const float c0 = -__fmul_rn(crs[j], a), c1 = -__fmul_rn(crs[j], b);     // dx = fma(xh, -rstd*b, fma(g, rstd, -rstd*a))
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
                     const int v = threadIdx.x + i * kBwdThreads;
@@ -229,16 +232,16 @@ __global__ void __launch_bounds__(kBwdThreads) ln_bwd_kernel(const uint16_t* __r
                         float o[8];
                         if constexpr (KEEP) {
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) o[q] = __fmul_rn(crs[j], __fsub_rn(__fsub_rn(kg[j][i][q], a), __fmul_rn(kxh[j][i][q], b)));
+                            for (int q = 0; q < 8; ++q) o[q] = __fmaf_rn(kxh[j][i][q], c1, __fmaf_rn(kg[j][i][q], crs[j], c0));
                         } else {
                             float dy[8], x[8];
                             unpack8(cdy[j][i], dy);
                             unpack8(cx[j][i], x);
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {        // g and xh again, by the same operations
-                                const float xh = __fmul_rn(__fsub_rn(x[q], cm[j]), crs[j]);
+                                const float xh = __fmaf_rn(x[q], crs[j], nmr[j]);
                                 const float g = __fmul_rn(dy[q], gam[i][q]);
-                                o[q] = __fmul_rn(crs[j], __fsub_rn(__fsub_rn(g, a), __fmul_rn(xh, b)));
+                                o[q] = __fmaf_rn(xh, c1, __fmaf_rn(g, crs[j], c0));
                             }
                         }
                         stg16(dX + r * D + v * 8, make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7])));
