@@ -593,7 +593,8 @@ def main():
                     "peak_kind": pk_kind + " copy bandwidth; algorithmic bytes are the PACKED weights, this path reads a bf16 expansion",
                     "bytes_per_decode_step": per_decode}
     hbm = {}
-    bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12), "combine": (A * D * 2 + T * D * 2),
+    # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)
+    bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12 + (T * D * 2 if cfg["backward"] else 0)), "combine": (A * D * 2 + T * D * 2),
                 "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
     for n, nb in bytes_of.items():
         if n in phases and phases[n][0] > 0:

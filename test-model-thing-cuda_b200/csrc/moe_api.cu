@@ -150,10 +150,8 @@ void build_act_maps(tmt_moe* h) {
         make_out_map(&m[kOutDXr], h->dXr, false, D, (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad);
         for (int i = 0; i < h->splits; ++i) make_out_map(&m[kOutSplit0 + i], h->dwr_partial + (size_t)i * h->mw * D, true, D, h->mw);
     }
-    if (h->dl_g) {
-        make_map_mn(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, ablk);
-        make_map(&m[kDltK], h->dl_t, h->kw, (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad, 64, 128);
-    }
+    if (h->dl_g) make_map_mn(&m[kDlgMN], h->dl_g, h->mw, h->dims.cap, ablk);
+    if (h->dl_t) make_map(&m[kDltK], h->dl_t, h->kw, (uint64_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad, 64, 128);
     CK(cudaMemcpyAsync(h->act_maps, m.data(), m.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
 }
 
@@ -326,7 +324,7 @@ void prof_mark(tmt_moe* h, int phase) {
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped) {
     route_only(h, X, Wr);
     prof_mark(h, kPhDispatch);
-    CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream));
+    CK(launch_dispatch(h->dims, h->rb, X, grouped, h->stream, PeerMap(), h->Xc));
     h->launches += 1;
     if (h->host_hooks) CK(cudaEventRecord(h->host_ev[tmt_moe::kEvXFree], h->stream));      // X has been read for the last time
 }
@@ -452,8 +450,8 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
     h->launches += 1;
     if (h->host_hooks) CK(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], h->stream));     // dY has been read for the last time
     expert_backward(h, Wup, Wdown, dWup, dWdown);
-    router_backward(h, Wr, H > 0 ? h->sw_part : nullptr, h->Xg, false, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef,
-                    h->rb.counts, (long)h->dims.T);
+    router_backward(h, Wr, H > 0 ? h->sw_part : nullptr, h->Xc ? h->Xc : h->Xg, h->Xc != nullptr, h->dXg, dWr,
+                    static_cast<uint16_t*>(dX), aux, zcoef, h->rb.counts, (long)h->dims.T);
     prof_mark(h, -1);
 }
 
@@ -495,6 +493,11 @@ void router_backward(tmt_moe* h, const void* Wr, const float* sw_part, const uin
     }
     const bool tc = h->tensor_core;
     prof_mark(h, kPhRouterBwd);
+    if (tc && tok_order) {      // rows of an earlier, longer call must not reach the token-order reduction
+        if (h->dims.T < h->dl_t_rows)
+            CK(cudaMemsetAsync(h->dl_t + (size_t)h->dims.T * h->kw, 0, (size_t)(h->dl_t_rows - h->dims.T) * h->kw * 2, h->stream));
+        h->dl_t_rows = h->dims.T;
+    }
     if (tc && !tok_order) CK(cudaMemsetAsync(h->dl_g, 0, (size_t)h->dims.cap * h->mw * 2, h->stream));
     CK(launch_router_bwd(h->dims, h->rb, sw_part, h->sw_ld, h->s_j, h->dlogits, aux, zcoef, counts, n_norm,
                          tc ? h->dl_t : nullptr, h->kw, tc && !tok_order ? h->dl_g : nullptr, h->mw, h->stream));
@@ -649,7 +652,15 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
             const size_t tpad = (size_t)(T + pad - 1) / pad * pad;
             h->dl_t = dalloc<uint16_t>(h, tpad * h->kw);
             CK(cudaMemsetAsync(h->dl_t, 0, tpad * h->kw * 2, h->stream));
-            h->dl_g = dalloc<uint16_t>(h, (size_t)cap * h->mw);
+            // The router weight gradient reduces over the tokens themselves: X is kept in token order by the dispatch
+            // kernel (tokens*D*2 bytes) instead of being read back from the grouped copy (topk times as many rows) through
+            // a zero-padded grouped gradient. Expert-parallel handles get their token-order copy in tmt_moe_ep_init.
+            if (d.ep_world == 1) {
+                h->Xc = dalloc<uint16_t>(h, tpad * D);
+                CK(cudaMemsetAsync(h->Xc, 0, tpad * D * 2, h->stream));
+            } else {
+                h->dl_g = dalloc<uint16_t>(h, (size_t)cap * h->mw);
+            }
             h->dXr = dalloc<uint16_t>(h, tpad * D);
             h->wr_bf16 = dalloc<uint16_t>(h, (size_t)E * D);
             h->dwr_partial = dalloc<float>(h, (size_t)h->splits * h->mw * D);
@@ -682,6 +693,7 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->g_maps = dalloc<CUtensorMap>(h, (size_t)2 * h->local_experts);
     h->g_poff = b.poff; h->g_num_m_tiles = b.num_m_tiles; h->g_tile_expert = b.tile_expert; h->g_max_tiles = h->dims.max_tiles;
     if (h->tensor_core) build_act_maps(h);
+    if (h->Xc) build_ep_maps(h, h->Xc, true);
     if (d.host_io) {
         CK(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
         CK(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));

@@ -65,7 +65,9 @@ struct tmt_moe {
     float** dwr_part_ptrs = nullptr;
     int* plain_tiles = nullptr; int* plain_num = nullptr; int plain_num_host = -1;
     const void* wr_seen = nullptr;
-    bool ep_x_token_order = false;     // expert parallel, peer transport: the router dW product reads X in token order
+    bool ep_x_token_order = false;     // the router dW product reads X in token order (one GPU, and the peer transport)
+    uint16_t* Xc = nullptr;            // one GPU, training: X kept in token order by the dispatch kernel for that product
+    int dl_t_rows = 0;                 // rows of dl_t that may hold values of an earlier, longer call
     int* tok_split_poff = nullptr;
     CUtensorMap* act_maps = nullptr;
     CUtensorMap* w_maps = nullptr;
