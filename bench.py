@@ -5,7 +5,7 @@
 
 One step = one forward + backward pass of the MoE layer over one batch of seeded synthetic
 tokens (N(0,1) activations, N(0,0.02^2) weights, N(0,1e-2^2) upstream gradient), through the
-C ABI of include/tmt_moe.h. Default workload: config 5 of BASELINE.json (131072 tokens per
+C ABI of include/tmt_moe.h. Default workload: config 5, the largest one (131072 tokens per
 GPU, dim 2048, 64 experts, top-4, expert FFN 2048->2048->2048, fp32 router), the one the
 1/2/4/8-GPU metric is quoted on; at N > 1 the experts are partitioned over the ranks (expert
 parallel, weak scaling: tokens per GPU fixed). Rank 0 prints ONE JSON line.
