@@ -588,9 +588,10 @@ def main():
         # 16 experts all experts are hit (P(miss) < 1e-3), plus the 64 input and output rows
         per_decode = E * 2.0 * D * H * (0.5 + 1.0 / 16) + 2 * T * D * 2
         gbs = per_decode * cfg["decode_steps"] / (ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "decode step (router, dispatch, 2 grouped GEMMs, combine)", "achieved": gbs,
+        roofline = {"bound": "hbm", "kernel": "decode step (router, fp4_rows_kernel up and down on the packed weights, combine)", "achieved": gbs,
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
-                    "peak_kind": pk_kind + " copy bandwidth; algorithmic bytes are the PACKED weights, this path reads a bf16 expansion",
+                    "peak_kind": pk_kind + " copy bandwidth; algorithmic bytes are the packed weights of every expert hit, once per decode "
+                                 "step (36 MB: they stay in the 126 MB L2 between decode steps, so this bounds the kernels' load path, not DRAM)",
                     "bytes_per_decode_step": per_decode}
     hbm = {}
     # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)

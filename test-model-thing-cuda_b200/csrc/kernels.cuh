@@ -54,8 +54,10 @@ struct PeerMap {
     int pad_smem = 0;
 };
 
+// scan_splits > 0 and scanned != NULL: a batch of at most kTokBlock tokens also runs the scan (launch_scan) inside the
+// router's last kernel; *scanned tells whether it did.
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
-                          const float* bias, cudaStream_t s);
+                          const float* bias, cudaStream_t s, int scan_splits = 0, bool* scanned = nullptr);
 // splits: number of reduction ranges written to split_poff (1..kMaxSplits).
 cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s);
 // Xg[slot] = X[token]; pad rows zeroed; fills slot_of / slotw / tok_of_slot (moe.cu:103-140).

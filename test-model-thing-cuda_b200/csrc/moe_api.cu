@@ -331,9 +331,10 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
 
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
     prof_mark(h, kPhRouter);
-    CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream));
+    bool scanned = false;
+    CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream, h->splits, &scanned));
     prof_mark(h, kPhScan);
-    CK(launch_scan(h->dims, h->rb, h->splits, h->stream));
+    if (!scanned) CK(launch_scan(h->dims, h->rb, h->splits, h->stream));
     const int plain = (h->dims.T + h->pad - 1) / h->pad * (h->pad / kPad);     // 128-row tiles, whole pairs for the CTA-pair kernel
     if (h->plain_num && plain != h->plain_num_host) {
         CK(cudaMemcpyAsync(h->plain_num, &plain, sizeof(int), cudaMemcpyHostToDevice, h->stream));

@@ -88,6 +88,9 @@ struct tmt_moe {
     std::vector<const void*> q_ptrs_host;
     std::vector<const void*> q_key; std::vector<float> q_scales_host;   // what the scratch was expanded from
     bool q_expert_scales = false;   // forward applies q_scales[e] / q_scales[E+e] to the accumulators
+    // small-batch NVFP4 route: device table of the packed weights ([4][E] pointers, then [2][E] scales) and what it was built from
+    void* q_table = nullptr;
+    std::vector<const void*> q_table_key; std::vector<float> q_table_scales;
     // expert parallelism
     tmt_ep_state* ep = nullptr;
     int* ep_world_counts = nullptr;

@@ -6,7 +6,10 @@
 //   q            = e2m1_rn(x / (float(block scale) * tensor_scale)), ties to the even code
 // Not compiled with fast-math: the divisions must be IEEE.
 #include <stdexcept>
+#include <cstdlib>
+
 #include "moe_internal.h"
+#include "nvfp4_decode.h"
 
 namespace tmt {
 namespace {
@@ -118,6 +121,69 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ packed, const uint
         if (e__ != cudaSuccess) throw std::runtime_error(std::string(#call) + " failed: " + cudaGetErrorString(e__)); \
     } while (0)
 
+
+// Steps of at most this many tokens take the small-batch route (TMT_MOE_DECODE_MAX_TOKENS overrides; 0 turns it off).
+int small_batch_limit() {
+    const char* s = getenv("TMT_MOE_DECODE_MAX_TOKENS");      // read per call: tests switch routes inside one process
+    return s && *s ? atoi(s) : 256;
+}
+
+bool small_batch_route(tmt_moe* h, const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, int tokens) {
+    const int E = h->d.experts, D = h->d.dim, H = h->d.hidden;
+    if (tokens > small_batch_limit() || (long)tokens * h->d.topk > kDecodeMaxAsg) return false;
+    if (!fp4_rows_shape_ok(H, D) || !fp4_rows_shape_ok(D, H)) return false;
+    for (int e = 0; e < E; ++e)
+        if (((uintptr_t)Wup[e].packed | (uintptr_t)Wup[e].scales | (uintptr_t)Wdown[e].packed | (uintptr_t)Wdown[e].scales) & 15)
+            return false;
+    return true;
+}
+
+// Router and scan as in every forward pass; then the two expert products read the packed weights and the token rows
+// directly (no grouped copy of X), one output row per assignment, and a small kernel sums the top-k rows of a token.
+void forward_small(tmt_moe* h, const uint16_t* X, const void* Wr, const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown,
+                   uint16_t* Y, float beta, int tokens) {
+    const int E = h->d.experts, D = h->d.dim, H = h->d.hidden, K = h->d.topk;
+    if (!h->q_table) {
+        void* p = nullptr;
+        CKQ(cudaMalloc(&p, (size_t)E * (4 * sizeof(void*) + 2 * sizeof(float)))); h->allocs.push_back(p); h->q_table = p;
+    }
+    std::vector<const void*> key(4 * E);
+    std::vector<float> sc(2 * E);
+    for (int e = 0; e < E; ++e) {
+        key[e] = Wup[e].packed; key[E + e] = Wup[e].scales; key[2 * E + e] = Wdown[e].packed; key[3 * E + e] = Wdown[e].scales;
+        sc[e] = Wup[e].tensor_scale * 16384.0f; sc[E + e] = Wdown[e].tensor_scale * 16384.0f;     // the kernels carry 2^-14
+    }
+    const uint8_t* const* tab = static_cast<const uint8_t* const*>(h->q_table);
+    float* es = reinterpret_cast<float*>(static_cast<char*>(h->q_table) + (size_t)4 * E * sizeof(void*));
+    if (key != h->q_table_key || sc != h->q_table_scales) {
+        CKQ(cudaMemcpyAsync(h->q_table, key.data(), key.size() * sizeof(void*), cudaMemcpyHostToDevice, h->stream));
+        CKQ(cudaMemcpyAsync(es, sc.data(), sc.size() * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+        CKQ(cudaStreamSynchronize(h->stream));      // the host vectors are about to be replaced
+        h->q_table_key = key; h->q_table_scales = sc;
+    }
+    h->dims.T = tokens;
+    h->last_tokens = tokens;
+    route_only(h, X, Wr);
+    Fp4RowsArgs up{};
+    up.packed = tab; up.scales = tab + E; up.es = es;
+    up.src = X; up.src_ld = D; up.src_div = K;
+    up.out = h->Hact; up.out_ld = H;
+    up.idx = h->rb.idx; up.gate = h->rb.w; up.n_asg = tokens * K; up.rows = H; up.kdim = D;
+    prof_mark(h, kPhGemmUp);
+    CKQ(launch_fp4_rows(up, E, 0, h->stream));
+    Fp4RowsArgs down = up;
+    down.packed = tab + 2 * E; down.scales = tab + 3 * E; down.es = es + E;
+    down.src = h->Hact; down.src_ld = H; down.src_div = 1;
+    down.out = h->Yg; down.out_ld = D; down.rows = D; down.kdim = H;
+    prof_mark(h, kPhGemmDown);
+    CKQ(launch_fp4_rows(down, E, 1, h->stream));
+    prof_mark(h, kPhCombine);
+    CKQ(launch_decode_combine(h->Yg, Y, beta, tokens, D, K, h->stream));
+    prof_mark(h, -1);
+    h->launches += 3;
+    h->have_forward = true;
+}
+
 }  // namespace
 }  // namespace tmt
 
@@ -158,6 +224,18 @@ int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter, const 
             throw std::runtime_error("NVFP4 forward needs hidden > 0, training = 0 and a single rank");
         if (!Wup || !Wdown) throw std::runtime_error("null argument");
         CKQ(cudaSetDevice(h->d.device));
+        if (!X || !Wrouter || !Y) throw std::runtime_error("null argument");
+        if (tokens < 1 || tokens > h->d.tokens) throw std::runtime_error("tokens outside [1, desc.tokens]");
+        for (int e = 0; e < E; ++e) {
+            if (Wup[e].rows != H || Wup[e].cols != D || Wdown[e].rows != D || Wdown[e].cols != H)
+                throw std::runtime_error("NVFP4 weight shape does not match the handle");
+            if (!Wup[e].packed || !Wup[e].scales || !Wdown[e].packed || !Wdown[e].scales)
+                throw std::runtime_error("null NVFP4 weight pointer");
+        }
+        if (small_batch_route(h, Wup, Wdown, tokens)) {
+            forward_small(h, static_cast<const uint16_t*>(X), Wrouter, Wup, Wdown, static_cast<uint16_t*>(Y), beta, tokens);
+            return 0;
+        }
         if (!h->q_up) {
             // scratch for the dequantised tiles: allocated on first use, kept for the handle's lifetime
             void* p = nullptr;
@@ -177,10 +255,6 @@ int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter, const 
         std::vector<float> sc(2 * E);
         const long blocks = (long)H * D / 16;
         for (int e = 0; e < E; ++e) {
-            if (Wup[e].rows != H || Wup[e].cols != D || Wdown[e].rows != D || Wdown[e].cols != H)
-                throw std::runtime_error("NVFP4 weight shape does not match the handle");
-            if (!Wup[e].packed || !Wup[e].scales || !Wdown[e].packed || !Wdown[e].scales)
-                throw std::runtime_error("null NVFP4 weight pointer");
             sc[e] = Wup[e].tensor_scale; sc[E + e] = Wdown[e].tensor_scale;
             key.push_back(Wup[e].packed); key.push_back(Wup[e].scales); key.push_back(Wdown[e].packed); key.push_back(Wdown[e].scales);
         }

@@ -11,6 +11,8 @@
 // the xor-butterfly 1, 2, 4 (fp32 addition is commutative, so every lane ends equal).
 // The products themselves run as a register-tiled fp32 FMA GEMM on the CUDA cores (tensor
 // cores would fix their own accumulation order, which the CPU statement could not mirror).
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace tmt {
@@ -48,6 +50,92 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
 }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Second half of the router, on the logits of one block of kTokBlock tokens in shared memory (lg, [kTokBlock][E]):
+// softmax, top-k, gate weights, then the block's stable ranks, counts and statistics partials.
+template <int NTHR>
+__device__ __forceinline__ void route_block_finish(const RouterArgs& a, float* lg, int* sidx, float* zs, long tok0) {
+    const int E = a.E, K = a.K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int s = lane & 7, g = lane >> 3;
+    const unsigned full = 0xffffffffu;
+    // ---- softmax, top-k (on logits, lowest index wins ties), gate weights: 8 lanes per token ----
+    for (int tb = warp * 4 + g; tb < kTokBlock; tb += (NTHR / 32) * 4) {
+        const long t = tok0 + tb;
+        const bool valid = t < a.T;
+        float* L = lg + tb * E;
+        float mx = -INFINITY;
+        for (int e = s; e < E; e += 8) mx = fmaxf(mx, L[e]);
+        mx = fmaxf(mx, __shfl_xor_sync(full, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(full, mx, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(full, mx, 4));
+        float se = 0.0f;
+        for (int e = s; e < E; e += 8) se += expf(L[e] - mx);
+        se += __shfl_xor_sync(full, se, 1);
+        se += __shfl_xor_sync(full, se, 2);
+        se += __shfl_xor_sync(full, se, 4);
+        unsigned used = 0;
+        for (int j = 0; j < K; ++j) {
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int e = s, i = 0; e < E; e += 8, ++i)
+                if (!(used >> i & 1) && (bi == 0x7fffffff || L[e] > bv)) { bv = L[e]; bi = e; }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                const float ov = __shfl_xor_sync(full, bv, o);
+                const int oi = __shfl_xor_sync(full, bi, o);
+                const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
+                if (take) { bv = ov; bi = oi; }
+            }
+            if ((bi & 7) == s) used |= 1u << (bi >> 3);
+            if (s == 0) sidx[tb * K + j] = valid ? bi : -1;
+        }
+        for (int e = s; e < E; e += 8) {
+            const float l = L[e];
+            const float pr = expf(l - mx) / se;
+            if (valid) { a.b.logits[t * E + e] = l; a.b.probs[t * E + e] = pr; }
+            L[e] = valid ? pr : 0.0f;
+        }
+        __syncwarp();
+        if (s == 0) {
+            const float lse = mx + logf(se);
+            zs[tb] = valid ? lse * lse : 0.0f;
+            if (valid) {
+                a.b.lse[t] = lse;
+                float z = 0.0f;
+                for (int j = 0; j < K; ++j) z += L[sidx[tb * K + j]];
+                for (int j = 0; j < K; ++j) {
+                    a.b.idx[t * K + j] = sidx[tb * K + j];
+                    a.b.w[t * K + j] = L[sidx[tb * K + j]] / z;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // ---- block level: stable ranks, counts, statistics partials ----
+    // rank of an assignment = number of earlier assignments of the block to the same expert: a warp walks the
+    // block's assignments 32 at a time for one expert (invalid tokens carry -1 and never match)
+    const int n_asg = kTokBlock * K;            // a multiple of 32
+    for (int e = warp; e < E; e += NTHR / 32) {
+        int running = 0;
+        for (int c0 = 0; c0 < n_asg; c0 += 32) {
+            const bool hit = sidx[c0 + lane] == e;
+            const unsigned m = __ballot_sync(full, hit);
+            if (hit) a.b.rank[(long)blockIdx.x * n_asg + c0 + lane] = running + __popc(m & ((1u << lane) - 1));
+            running += __popc(m);
+        }
+        if (lane == 0) a.b.block_counts[(long)blockIdx.x * E + e] = running;
+    }
+    for (int e = threadIdx.x; e < E; e += NTHR) {
+        float sp = 0.0f;
+        for (int tb = 0; tb < kTokBlock; ++tb) sp += lg[tb * E + e];
+        a.b.block_sump[(long)blockIdx.x * E + e] = sp;
+    }
+    if (threadIdx.x == NTHR - 1) {
+        float z = 0.0f;
+        for (int tb = 0; tb < kTokBlock; ++tb) z += zs[tb];
+        a.b.block_z[blockIdx.x] = z;
+    }
+}
 
 // Block = 64 tokens x (TE * ESLABS) experts per expert pass; 4 * ESLABS warps. Warp = one slab of 16
 // tokens x TE experts; lane = (chain s = lane & 7, token group g = lane >> 3); a thread keeps
@@ -169,91 +257,19 @@ __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a
             }
     }
     __syncthreads();
-    // ---- softmax, top-k (on logits, lowest index wins ties), gate weights: 8 lanes per token ----
-    for (int tb = warp * 4 + g; tb < kTokBlock; tb += (NTHR / 32) * 4) {
-        const long t = tok0 + tb;
-        const bool valid = t < a.T;
-        float* L = lg + tb * E;
-        float mx = -INFINITY;
-        for (int e = s; e < E; e += 8) mx = fmaxf(mx, L[e]);
-        mx = fmaxf(mx, __shfl_xor_sync(full, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(full, mx, 2));
-        mx = fmaxf(mx, __shfl_xor_sync(full, mx, 4));
-        float se = 0.0f;
-        for (int e = s; e < E; e += 8) se += expf(L[e] - mx);
-        se += __shfl_xor_sync(full, se, 1);
-        se += __shfl_xor_sync(full, se, 2);
-        se += __shfl_xor_sync(full, se, 4);
-        unsigned used = 0;
-        for (int j = 0; j < K; ++j) {
-            float bv = -INFINITY; int bi = 0x7fffffff;
-            for (int e = s, i = 0; e < E; e += 8, ++i)
-                if (!(used >> i & 1) && (bi == 0x7fffffff || L[e] > bv)) { bv = L[e]; bi = e; }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                const float ov = __shfl_xor_sync(full, bv, o);
-                const int oi = __shfl_xor_sync(full, bi, o);
-                const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
-                if (take) { bv = ov; bi = oi; }
-            }
-            if ((bi & 7) == s) used |= 1u << (bi >> 3);
-            if (s == 0) sidx[tb * K + j] = valid ? bi : -1;
-        }
-        for (int e = s; e < E; e += 8) {
-            const float l = L[e];
-            const float pr = expf(l - mx) / se;
-            if (valid) { a.b.logits[t * E + e] = l; a.b.probs[t * E + e] = pr; }
-            L[e] = valid ? pr : 0.0f;
-        }
-        __syncwarp();
-        if (s == 0) {
-            const float lse = mx + logf(se);
-            zs[tb] = valid ? lse * lse : 0.0f;
-            if (valid) {
-                a.b.lse[t] = lse;
-                float z = 0.0f;
-                for (int j = 0; j < K; ++j) z += L[sidx[tb * K + j]];
-                for (int j = 0; j < K; ++j) {
-                    a.b.idx[t * K + j] = sidx[tb * K + j];
-                    a.b.w[t * K + j] = L[sidx[tb * K + j]] / z;
-                }
-            }
-        }
-    }
-    __syncthreads();
-    // ---- block level: stable ranks, counts, statistics partials ----
-    const int n_asg = kTokBlock * K;
-    for (int i = threadIdx.x; i < n_asg; i += NTHR) {
-        const int e = sidx[i];
-        if (e < 0) continue;
-        int r = 0;
-        for (int q = 0; q < i; ++q) r += (sidx[q] == e);
-        a.b.rank[(long)blockIdx.x * n_asg + i] = r;
-    }
-    for (int e = threadIdx.x; e < E; e += NTHR) {
-        int c = 0;
-        for (int q = 0; q < n_asg; ++q) c += (sidx[q] == e);
-        float sp = 0.0f;
-        for (int tb = 0; tb < kTokBlock; ++tb) sp += lg[tb * E + e];
-        a.b.block_counts[(long)blockIdx.x * E + e] = c;
-        a.b.block_sump[(long)blockIdx.x * E + e] = sp;
-    }
-    if (threadIdx.x == 0) {
-        float z = 0.0f;
-        for (int tb = 0; tb < kTokBlock; ++tb) z += zs[tb];
-        a.b.block_z[blockIdx.x] = z;
-    }
+    route_block_finish<NTHR>(a, lg, sidx, zs, tok0);
 }
 
 // Scan, part 1: one warp per expert. Exclusive scan of that expert's per-block counts (the base of
 // every router block inside the group), the expert's total and its probability sum; warp 0 of
 // block 0 also reduces the z-loss partials. Fixed orders throughout: results are deterministic.
-__global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, const RouteBufs b, int NB) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// This warp handles experts e_first, e_first + e_stride, ...; `with_z`: it also reduces the z-loss partials.
+__device__ __forceinline__ void scan_columns_dev(const RouteDims& d, const RouteBufs& b, int NB, int e_first, int e_stride,
+                                                 bool with_z) {
+    const int lane = threadIdx.x & 31;
     const unsigned full = 0xffffffffu;
     const int E = d.E;
-    const int e = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (e < E) {
+    for (int e = e_first; e < E; e += e_stride) {
         int running = 0;
         float fs = 0.0f;
         for (int b0 = 0; b0 < NB; b0 += 32) {
@@ -276,7 +292,7 @@ __global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, co
             b.stat[e] = E == 1 ? 0.0f : fs;     // dense shortcut reports no statistics (moe.cu:397-403)
         }
     }
-    if (blockIdx.x == 0 && warp == 0) {
+    if (with_z) {
         float z = 0.0f;
         for (int blk = lane; blk < NB; blk += 32) z += b.block_z[blk];
 #pragma unroll
@@ -284,11 +300,14 @@ __global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, co
         if (lane == 0) b.stat[E] = E == 1 ? 0.0f : z / (float)d.T;
     }
 }
+__global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, const RouteBufs b, int NB) {
+    const int warp = threadIdx.x >> 5;
+    scan_columns_dev(d, b, NB, blockIdx.x * (blockDim.x >> 5) + warp, 1 << 30, blockIdx.x == 0 && warp == 0);
+}
 
 // Scan, part 2: one block. True and padded group starts (moe.cu:413-419), tile -> expert table,
 // number of tiles in use, split table of the router weight-gradient product.
-__global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, const RouteBufs b, int splits) {
-    __shared__ int poff_s[257];
+__device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteBufs& b, int splits, int* poff_s) {
     const int E = d.E;
     if (threadIdx.x == 0) {
         int tk = 0, ptk = 0;
@@ -321,6 +340,93 @@ __global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, con
     // even split of the rows in use into `splits` ranges of whole tiles
     for (int i = threadIdx.x; i <= splits; i += blockDim.x) b.split_poff[i] = (int)((long)used * i / splits) * kPad;
 }
+__global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, const RouteBufs b, int splits) {
+    __shared__ int poff_s[257];
+    scan_finish_dev(d, b, splits, poff_s);
+}
+
+// Few tokens (sampler steps, short sequences): the 64-token block above would leave all but a handful of SMs idle.
+// Here one block computes the logits of ONE token: 16 groups of 8 lanes, lane s = chain s, group q = experts q, q + 16,
+// ...; the same chains, in the same order, added by the same butterfly, so the logits are bit-identical. The second
+// half then runs per 64-token block on the stored logits (router_finish_kernel).
+template <bool WF32>
+__global__ void __launch_bounds__(128) router_logits_small_kernel(const RouterArgs a) {
+    const int s = threadIdx.x & 7, grp = threadIdx.x >> 3;
+    const long t = blockIdx.x;
+    const int nvec = a.D >> 3;
+    const unsigned full = 0xffffffffu;
+    const uint16_t* xrow = a.X + t * a.D;
+    for (int e0 = 0; e0 < a.E; e0 += 16) {
+        const int e = e0 + grp;
+        const bool valid = e < a.E;
+        const int er = valid ? e : 0;
+        float acc = 0.0f;
+        constexpr int kB = 4;                   // vectors in flight per lane (the chain itself stays sequential)
+        for (int v0 = s; v0 < nvec; v0 += 8 * kB) {
+            uint4 xv[kB], wa[kB], wb[kB];
+#pragma unroll
+            for (int u = 0; u < kB; ++u) {
+                const int v = min(v0 + 8 * u, nvec - 8 + s);       // past the end: a valid address, value unused
+                xv[u] = ldg16(xrow + v * 8);
+                if constexpr (WF32) {
+                    const float* wr = reinterpret_cast<const float*>(a.Wr) + (long)er * a.D + v * 8;
+                    wa[u] = ldg16(wr); wb[u] = ldg16(wr + 4);
+                } else {
+                    wa[u] = ldg16(reinterpret_cast<const uint16_t*>(a.Wr) + (long)er * a.D + v * 8);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kB; ++u) {
+                if (v0 + 8 * u < nvec) {
+                    const float x[8] = {bf_lo(xv[u].x), bf_hi(xv[u].x), bf_lo(xv[u].y), bf_hi(xv[u].y),
+                                        bf_lo(xv[u].z), bf_hi(xv[u].z), bf_lo(xv[u].w), bf_hi(xv[u].w)};
+                    float w[8];
+                    if constexpr (WF32) {
+                        w[0] = __uint_as_float(wa[u].x); w[1] = __uint_as_float(wa[u].y); w[2] = __uint_as_float(wa[u].z); w[3] = __uint_as_float(wa[u].w);
+                        w[4] = __uint_as_float(wb[u].x); w[5] = __uint_as_float(wb[u].y); w[6] = __uint_as_float(wb[u].z); w[7] = __uint_as_float(wb[u].w);
+                    } else {
+                        w[0] = bf_lo(wa[u].x); w[1] = bf_hi(wa[u].x); w[2] = bf_lo(wa[u].y); w[3] = bf_hi(wa[u].y);
+                        w[4] = bf_lo(wa[u].z); w[5] = bf_hi(wa[u].z); w[6] = bf_lo(wa[u].w); w[7] = bf_hi(wa[u].w);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) acc = __fmaf_rn(x[q], w[q], acc);
+                }
+            }
+        }
+        acc = __fadd_rn(acc, __shfl_xor_sync(full, acc, 1));
+        acc = __fadd_rn(acc, __shfl_xor_sync(full, acc, 2));
+        acc = __fadd_rn(acc, __shfl_xor_sync(full, acc, 4));
+        if (valid && s == 0) {
+            if (a.bias) acc = __fadd_rn(acc, a.bias[e]);
+            a.b.logits[t * a.E + e] = acc;
+        }
+    }
+}
+
+constexpr int kFinishThreads = 512;     // 64 groups of 8 lanes: every token of the block at once
+
+// splits > 0 (only with a single block, i.e. at most kTokBlock tokens): the block also does both parts of the scan.
+__global__ void __launch_bounds__(kFinishThreads) router_finish_kernel(const RouterArgs a, const RouteDims d, int splits) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* lg = reinterpret_cast<float*>(smem);          // [kTokBlock][E]
+    __shared__ int sidx[kTokBlock * 8];
+    __shared__ float zs[kTokBlock];
+    __shared__ int poff_s[257];
+    const long tok0 = (long)blockIdx.x * kTokBlock;
+    for (int i = threadIdx.x; i < kTokBlock * a.E; i += kFinishThreads) {
+        const long t = tok0 + i / a.E;
+        lg[i] = t < a.T ? a.b.logits[tok0 * a.E + i] : 0.0f;
+    }
+    __syncthreads();
+    route_block_finish<kFinishThreads>(a, lg, sidx, zs, tok0);
+    if (splits > 0) {
+        __syncthreads();        // the block's counts and partials are in global memory, written by this block
+        const int warp = threadIdx.x >> 5;
+        scan_columns_dev(d, a.b, 1, warp, kFinishThreads / 32, warp == kFinishThreads / 32 - 1);
+        __syncthreads();
+        scan_finish_dev(d, a.b, splits, poff_s);
+    }
+}
 
 template <int TE, int ESLABS, bool WF32>
 cudaError_t launch_router_t(const RouterArgs& a, int nb, cudaStream_t s) {
@@ -348,10 +454,30 @@ cudaError_t launch_router_w(const RouterArgs& a, int nb, cudaStream_t s) {
 
 }  // namespace
 
+// Up to this many logits the per-token kernel is used (TMT_MOE_ROUTER_SMALL = 0 / 1 forces one of the two; both give
+// the same bits): beyond it, re-reading the router rows per token costs more than the idle SMs of the tiled kernel.
+constexpr long kSmallRouterLogits = 16384;
+
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
-                          const float* bias, cudaStream_t s) {
+                          const float* bias, cudaStream_t s, int scan_splits, bool* scanned) {
+    if (scanned) *scanned = false;
     RouterArgs a{X, Wr, bias, d.T, d.D, d.E, d.K, b};
     const int nb = (d.T + kTokBlock - 1) / kTokBlock;
+    bool small = (long)d.T * d.E <= kSmallRouterLogits;
+    if (const char* f = getenv("TMT_MOE_ROUTER_SMALL")) if (*f) small = *f != '0';
+    if (small) {
+        if (d.router_f32) router_logits_small_kernel<true><<<d.T, 128, 0, s>>>(a);
+        else router_logits_small_kernel<false><<<d.T, 128, 0, s>>>(a);
+        const size_t smem = (size_t)kTokBlock * d.E * sizeof(float);
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(router_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        const bool fuse = nb == 1 && scan_splits > 0 && scanned != nullptr;
+        router_finish_kernel<<<nb, kFinishThreads, smem, s>>>(a, d, fuse ? scan_splits : 0);
+        if (fuse) *scanned = true;
+        return cudaGetLastError();
+    }
     return d.router_f32 ? launch_router_w<true>(a, nb, s) : launch_router_w<false>(a, nb, s);
 }
 

@@ -37,27 +37,42 @@ def test_quantiser_byte_exact():
         np.testing.assert_array_equal(p.cpu().numpy(), p_ref)
 
 
-@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
-def test_forward_nvfp4_decode_shape(impl):
-    import gpu_util as G
-    import tmt_moe_b200 as M
-    T, D, H, E, K = 64, 1024, 2048, 16, 2
-    data = synth.make(T, D, H, E, K, seed=31, need_dy=False)
+def _setup(M, G, T, D, H, E, K, seed, tiny_blocks=False):
+    data = synth.make(T, D, H, E, K, seed=seed, need_dy=False)
     up_q, down_q, up_dq, down_dq, us, ds, keep = [], [], [], [], [], [], []
     for e in range(E):
         for W, qs, dqs, sc in ((data["Wup"][e], up_q, up_dq, us), (data["Wdown"][e], down_q, down_dq, ds)):
+            if tiny_blocks:                              # blocks far below the tensor's amax: subnormal e4m3 scales, zero scales
+                W = W.copy()
+                f = O.bf16_to_f32(W)
+                f[1::4, 16:64] *= 2.0 ** -15
+                f[2::4, 64:96] *= 2.0 ** -20
+                W[...] = O.f32_to_bf16(f)
             p, s, ts = _quantize_gpu(M, G, W)
             keep += [p, s]
             qs.append((p, s, ts, W.shape[0], W.shape[1]))
             dqs.append(O.nvfp4_dequantize(p.cpu().numpy(), s.cpu().numpy(), 1.0))
             sc.append(ts)
+    return data, up_q, down_q, np.stack(up_dq), np.stack(down_dq), np.array(us, np.float32), np.array(ds, np.float32), keep
+
+
+# Two routes: steps of a few tokens read the packed weights directly (register-operand MMA); larger steps expand the
+# weights once and run the grouped tcgen05 kernels. TMT_MOE_DECODE_MAX_TOKENS = 0 forces the second route.
+@pytest.mark.parametrize("route", ["small_batch", "expanded"])
+@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
+def test_forward_nvfp4_decode_shape(impl, route, monkeypatch):
+    import gpu_util as G
+    import tmt_moe_b200 as M
+    if route == "expanded":
+        monkeypatch.setenv("TMT_MOE_DECODE_MAX_TOKENS", "0")
+    T, D, H, E, K = 64, 1024, 2048, 16, 2
+    data, up_q, down_q, up_dq, down_dq, us, ds, keep = _setup(M, G, T, D, H, E, K, 31)
     pad = 256 if impl == 2 else 128
-    ref = O.forward(data["X"], data["Wr"], np.stack(up_dq), np.stack(down_dq), K, up_scale=np.array(us, np.float32),
-                    down_scale=np.array(ds, np.float32), pad=pad)
+    ref = O.forward(data["X"], data["Wr"], up_dq, down_dq, K, up_scale=us, down_scale=ds, pad=pad)
     moe = M.MoE(T, D, E, K, hidden=H, training=False, gemm_impl=impl)
     X, Wr = G.dev(data["X"]), G.dev(data["Wr"])
     Y = torch.zeros((T, D), dtype=torch.int16, device="cuda")
-    for _ in range(2):                                   # second call reuses the expanded weights
+    for _ in range(2):                                   # second call reuses the weight tables
         moe.forward_nvfp4(X, Wr, up_q, down_q, Y)
         torch.cuda.synchronize()
     assert moe.device_status() == 0
@@ -66,3 +81,35 @@ def test_forward_nvfp4_decode_shape(impl):
     assert synth.rel_l2(got, O.bf16_to_f32(ref["Y"])) <= 1e-2
     full = O.forward(data["X"], data["Wr"], data["Wup"], data["Wdown"], K, pad=pad)
     print("NVFP4 vs unquantised weights: relative L2 = %.3f" % synth.rel_l2(got, O.bf16_to_f32(full["Y"])))
+
+
+@pytest.mark.parametrize("case", [
+    pytest.param(dict(T=37, D=256, H=512, E=4, K=2, beta=0.5, tiny=False), id="ragged_37_tokens_beta_two_passes_per_expert"),
+    pytest.param(dict(T=64, D=512, H=256, E=8, K=3, beta=0.0, tiny=True), id="top3_subnormal_and_zero_block_scales"),
+    pytest.param(dict(T=1, D=256, H=256, E=16, K=2, beta=0.0, tiny=False), id="one_token_most_experts_idle"),
+])
+def test_small_batch_route_matches_expanded_route(case, monkeypatch):
+    """Both routes multiply the same bf16 values (q * block scale) with fp32 accumulation; only the order of the sums and
+    one bf16 rounding of the SiLU input can differ. Against the oracle: relative L2 <= 1e-2; between routes: <= 3e-3."""
+    import gpu_util as G
+    import tmt_moe_b200 as M
+    T, D, H, E, K = case["T"], case["D"], case["H"], case["E"], case["K"]
+    data, up_q, down_q, up_dq, down_dq, us, ds, keep = _setup(M, G, T, D, H, E, K, 77, tiny_blocks=case["tiny"])
+    ref = O.forward(data["X"], data["Wr"], up_dq, down_dq, K, up_scale=us, down_scale=ds, pad=128)
+    rng = np.random.default_rng(5)
+    Y0 = O.f32_to_bf16(rng.standard_normal((T, D), dtype=np.float32) * 0.1)
+    X, Wr = G.dev(data["X"]), G.dev(data["Wr"])
+    outs = {}
+    for route in ("small_batch", "expanded"):
+        monkeypatch.setenv("TMT_MOE_DECODE_MAX_TOKENS", "256" if route == "small_batch" else "0")
+        moe = M.MoE(64, D, E, K, hidden=H, training=False, gemm_impl=0)
+        Y = G.dev(Y0.copy())
+        moe.forward_nvfp4(X, Wr, up_q, down_q, Y, beta=case["beta"], tokens=T)
+        torch.cuda.synchronize()
+        assert moe.device_status() == 0
+        np.testing.assert_array_equal(moe.read("idx", tokens=T), ref["idx"])
+        outs[route] = O.bf16_to_f32(G.host_u16(Y))
+        moe.close()
+    want = O.bf16_to_f32(ref["Y"]) + case["beta"] * O.bf16_to_f32(Y0)
+    assert synth.rel_l2(outs["small_batch"], want) <= 1e-2
+    assert synth.rel_l2(outs["small_batch"], outs["expanded"]) <= 3e-3

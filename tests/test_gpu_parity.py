@@ -319,3 +319,29 @@ def test_router_usage_telemetry_accumulates_on_the_device():
     assert abs(u["min_share"] - share.min()) < 1e-12 and abs(u["max_share"] - share.max()) < 1e-12
     assert layer.moe.usage(reset=True)["passes"] == 3
     assert layer.moe.usage()["passes"] == 0 and layer.moe.usage()["totals"].sum() == 0
+
+
+@pytest.mark.parametrize("cfg,bias_on", [
+    (dict(T=37, D=256, H=256, E=4, K=2), False),
+    (dict(T=200, D=512, H=128, E=16, K=2, router_f32=True), True),
+    (dict(T=130, D=256, H=128, E=40, K=4), False),
+], ids=["37_tokens_4_experts", "200_tokens_fp32_router_bias", "130_tokens_40_experts_top4"])
+def test_per_token_router_and_tiled_router_agree_bitwise(cfg, bias_on, monkeypatch):
+    """Short batches compute the logits with one block per token, long ones with 64-token tiles; the chains, their
+    order and the butterfly are the same, so every routing product is identical bit for bit (and equals the oracle's)."""
+    T, D, H, E, K = cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"]
+    rf = cfg.get("router_f32", False)
+    data = synth.make(T, D, H, E, K, rf, seed=11)
+    bias = (np.random.default_rng(3).standard_normal(E) * 0.5).astype(np.float32) if bias_on else None
+    ref = O.forward(data["X"], data["Wr"], data["Wup"], data["Wdown"], K, bias=bias, pad=128)
+    got = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("TMT_MOE_ROUTER_SMALL", flag)
+        layer = G.Layer(data, T, D, E, K, H, rf, training=False, gemm_impl=0, bias=bias)
+        layer.forward(None, 0.0)
+        assert layer.moe.device_status() == 0
+        G.check_routing(layer, ref)
+        got[flag] = {n: layer.moe.read(n) for n in ("logits", "probs", "lse", "idx", "w", "slot_of", "counts", "poff")}
+        got[flag]["stat"] = layer.moe.stats()[0]
+    for n, v in got["0"].items():
+        np.testing.assert_array_equal(v, got["1"][n], err_msg=n)
