@@ -172,7 +172,12 @@ int tmt_moe_quantize_nvfp4(const void* W_bf16, int rows, int cols, void* packed,
                            float* tensor_scale_host, void* stream);
 
 /* Forward with NVFP4 expert weights (hidden > 0 only, training = 0). Wup / Wdown are HOST
- * arrays of E descriptors. Router as in tmt_moe_forward. */
+ * arrays of E descriptors. Router as in tmt_moe_forward.
+ * Steps of at most 256 tokens with tokens * topk <= 1024 (the sampler's case), 16-byte aligned
+ * packed / scales pointers, dim and hidden multiples of 256: the expert products read the packed
+ * weights in place, so these must stay valid while the handle uses them. Larger steps expand the
+ * weights once into scratch owned by the handle. Same numerics on both routes; the environment
+ * variable TMT_MOE_DECODE_MAX_TOKENS moves the switch point (0: always expand). */
 int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter,
                           const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, void* Y,
                           float beta, int tokens);

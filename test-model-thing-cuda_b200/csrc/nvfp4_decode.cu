@@ -17,17 +17,22 @@
 // The k order inside one MMA is free as long as both operands agree: a thread takes 32 consecutive k
 // (16 bytes of codes = two scale blocks) per 128-k chunk, and the token rows are staged in shared
 // memory already permuted to match.
+#include <cstdlib>
+
 #include "kernels.cuh"
 #include "nvfp4_decode.h"
+#include "tc_util.cuh"
 
 namespace tmt {
 namespace {
 
-constexpr int kNT = 16;                 // tokens (assignments) of one expert per pass: two MMA column tiles
-constexpr int kRowsPerCta = 64;         // 4 row groups of 16 weight rows
+constexpr int kNT = 8;                  // tokens (assignments) of one expert per pass: one MMA column tile
+constexpr int kRowsPerCta = 128;        // 8 row groups of 16 weight rows (times RGW)
 constexpr int kKSplit = 2;              // warps sharing a row group, each with half of the chunks
-constexpr int kThreads = 128 * kKSplit;
-constexpr int kSB = 4;                 // staged rows a thread fetches before it stores any
+constexpr int kThreads = 256 * kKSplit;
+constexpr int kListBytes = kDecodeMaxAsg * 4, kRedBytes = 2 * 4 * 256 * 4, kLutBytes = 256 * 4;
+constexpr int kSB = 4;                  // staged rows a thread fetches before it stores any
+constexpr int kMaxSmem = 227 * 1024;
 
 __device__ __forceinline__ uint32_t mul_bf2(uint32_t a, uint32_t b) {
     uint32_t d;
@@ -40,13 +45,6 @@ __device__ __forceinline__ uint32_t expand_pair(uint32_t w, uint32_t s2) {
     const uint32_t mag = (I == 0 ? w << 6 : I == 1 ? w << 2 : I == 2 ? w >> 2 : w >> 6) & 0x01C001C0u;
     const uint32_t sgn = (I == 0 ? w << 12 : I == 1 ? w << 8 : I == 2 ? w << 4 : w) & 0x80008000u;
     return mul_bf2(mag | sgn, s2);
-}
-// e4m3 (unsigned) * 2^112 as bf16, duplicated into both halves
-__device__ __forceinline__ uint32_t scale_bf2(uint32_t byte) {
-    const uint32_t e = byte >> 3, m = byte & 7u;
-    uint32_t b = (byte << 4) + (232u << 7);                       // normal: exponent e - 7 + 112 + 127
-    if (e == 0) b = f2bf((float)m * 0x1p103f);                    // subnormal: m * 2^-9 * 2^112
-    return b | (b << 16);
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -63,45 +61,70 @@ __device__ __forceinline__ void sts16u(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-struct Chunk { uint4 a, b; uint32_t sa, sb; };      // 32 codes of rows g and g + 8 and their two block scales each
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// one row of codes or scales, global -> shared memory, completion counted in bytes on `bar`
+__device__ __forceinline__ void bulk_load_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
 // MODE 0: out[asg][row] = bf16(silu(a)), a = bf16(es * acc)          (up-projection; src row = asg / src_div)
 // MODE 1: out[asg][row] = bf16(gate[asg] * (es * acc))               (down-projection; src row = asg)
-template <int MODE>
-__global__ void __launch_bounds__(kThreads, 4) fp4_rows_kernel(const Fp4RowsArgs p) {
-    extern __shared__ __align__(16) uint8_t smem[];
+// A block owns 128 * RGW weight rows of one expert (one block per SM). All of them are requested at the start, one bulk
+// copy per row of codes and per row of scales into padded shared-memory rows (pitch = row + 64 / + 16 bytes: the 8 rows
+// a warp reads together fall on different banks), so the whole tile is in flight at once and no register holds
+// prefetched weights. 16 warps = 8 row groups x 2 k halves; RGW row groups per warp, one after the other.
+template <int MODE, int RGW>
+__global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs p) {
+    extern __shared__ __align__(128) uint8_t smem[];
     int* list = reinterpret_cast<int*>(smem);                         // assignments of this expert, ascending
-    float* red = reinterpret_cast<float*>(smem + kDecodeMaxAsg * 4);  // [128][8] partial sums of the second k half
-    const uint32_t stage = (uint32_t)__cvta_generic_to_shared(smem) + kDecodeMaxAsg * 4 + 128 * 8 * 4;
-    __shared__ int s_cnt;
+    float* red = reinterpret_cast<float*>(smem + kListBytes);         // [2][4][256] partial sums of the second k half
+    const int kdim = p.kdim, nchunks = kdim >> 7;
+    constexpr int R = kRowsPerCta * RGW;
+    const uint32_t cpitch = (uint32_t)(kdim >> 1) + 64, spitch = (uint32_t)(kdim >> 4) + 16;
+    const uint32_t rowb = (uint32_t)kdim * 2 + 64;                    // staged token row pitch
+    const uint32_t lut = tc::smem_u32(smem) + kListBytes + kRedBytes; // e4m3 byte -> scale * 2^112 as bf16x2
+    const uint32_t codes = lut + kLutBytes;
+    const uint32_t scales = codes + R * cpitch;
+    const uint32_t stage = scales + R * spitch;
+    __shared__ __align__(8) uint64_t wbar;
+    __shared__ int s_cnt, abort_s;
     __shared__ unsigned masks[kDecodeMaxAsg / 32];
     const int e = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int rgroup = warp & 3, ks = warp >> 2;
-    const int kdim = p.kdim, nchunks = kdim >> 7;
+    const int rgroup = warp & 7, ks = warp >> 3;
     const int ch0 = ks * nchunks / kKSplit, ch1 = (ks + 1) * nchunks / kKSplit;
-    const uint32_t rowb = (uint32_t)kdim * 2 + 64;                    // staged row pitch: +64 bytes keeps 8 lanes on 32 banks
-    const int r0 = blockIdx.x * kRowsPerCta + rgroup * 16;
-    const uint8_t* pa = p.packed[e] + (size_t)(r0 + g) * (kdim >> 1) + c * 16;
-    const uint8_t* pb = pa + (size_t)8 * (kdim >> 1);
-    const uint8_t* sa = p.scales[e] + (size_t)(r0 + g) * (kdim >> 4) + c * 2;
-    const uint8_t* sb = sa + (size_t)8 * (kdim >> 4);
-    auto load_chunk = [&](int j) {
-        Chunk ck;
-        ck.a = ldg16(pa + j * 64); ck.b = ldg16(pb + j * 64);
-        ck.sa = __ldg(reinterpret_cast<const uint16_t*>(sa + j * 8));
-        ck.sb = __ldg(reinterpret_cast<const uint16_t*>(sb + j * 8));
-        return ck;
-    };
-    // the first weights travel while the token list is built and the rows are staged
-    Chunk cur = load_chunk(ch0), nxt = cur;
-    if (ch0 + 1 < ch1) nxt = load_chunk(ch0 + 1);
-
-    // token list, ascending: warp w takes the 32-assignment slices w, w + 8, ...; one load latency in all
+    // this warp's first slice of the assignment table, asked for before anything that has to wait for a pointer
+    const int first_idx = warp * 32 + lane < p.n_asg ? p.idx[warp * 32 + lane] : -1;
+    const int row0 = blockIdx.x * R;
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        tc::mbar_init(tc::smem_u32(&wbar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::fence_async_smem();
+        tc::mbar_expect_tx(tc::smem_u32(&wbar), (uint32_t)R * (uint32_t)((kdim >> 1) + (kdim >> 4)));
+    }
+    if (threadIdx.x < 256) {   // scale table: entry = e4m3 * 2^112 as bf16 in both halves
+        const uint32_t byte = threadIdx.x, ex = byte >> 3, m = byte & 7u;
+        uint32_t b = (byte << 4) + (232u << 7);                       // normal: exponent ex - 7 + 112 + 127
+        if (ex == 0) b = f2bf((float)m * 0x1p103f);                   // subnormal: m * 2^-9 * 2^112
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut + byte * 4), "r"(b | (b << 16)) : "memory");
+    }
+    // token list, ascending: warp w takes the 32-assignment slices w, w + 16, ...; one load latency in all
     for (int sl = warp; sl * 32 < p.n_asg; sl += kThreads / 32) {
         const int i = sl * 32 + lane;
-        const unsigned m = __ballot_sync(0xffffffffu, i < p.n_asg && p.idx[i] == e);
+        const int ie = sl == warp ? first_idx : (i < p.n_asg ? p.idx[i] : -1);
+        const unsigned m = __ballot_sync(0xffffffffu, ie == e);
         if (lane == 0) masks[sl] = m;
     }
     __syncthreads();
@@ -119,31 +142,40 @@ __global__ void __launch_bounds__(kThreads, 4) fp4_rows_kernel(const Fp4RowsArgs
         if (lane == 31) s_cnt = incl;
     }
     __syncthreads();
-    const int cnt = s_cnt;
+    const int cnt = (p.dbg & 1) ? 0 : s_cnt;      // measurement only: bit 0 = stop after the token list
+    if (cnt == 0) return;                          // an expert without tokens asks for no weights
+    if (threadIdx.x < R) {
+        bulk_load_row(codes + threadIdx.x * cpitch, p.packed[e] + (size_t)(row0 + threadIdx.x) * (kdim >> 1), (uint32_t)(kdim >> 1),
+                      tc::smem_u32(&wbar));
+    } else if (threadIdx.x >= 256 && threadIdx.x - 256 < R) {
+        const int r = threadIdx.x - 256;
+        bulk_load_row(scales + r * spitch, p.scales[e] + (size_t)(row0 + r) * (kdim >> 4), (uint32_t)(kdim >> 4), tc::smem_u32(&wbar));
+    }
     const float es = p.es[e];
     const int pieces_per_row = kdim >> 3;
     const int lanes_per_row = min(pieces_per_row, kThreads), rows_per_iter = kThreads / lanes_per_row;
     const int sub = threadIdx.x / lanes_per_row, v0 = threadIdx.x - sub * lanes_per_row;
+    int turn = 0;                                                     // alternates the two halves of `red`
+    bool have_weights = false;
 
     for (int pass = 0; pass * kNT < cnt; ++pass) {
         const int n_here = min(kNT, cnt - pass * kNT);
-        const int ntiles = (n_here + 7) >> 3;
-        if (pass > 0) __syncthreads();                                // everyone has left the previous rows
-        // rows of the pass -> shared memory, permuted; kSB 16-byte loads in flight per thread
-        for (int n0 = sub; n0 < ntiles * 8; n0 += kSB * rows_per_iter) {
+        // rows of the pass -> shared memory, permuted; kSB 16-byte loads in flight per thread. Columns past n_here stay
+        // as they are: a column of the product depends on nothing but its own token. (Every warp has passed the last
+        // barrier of the previous pass, so nobody still reads the previous rows.)
+        for (int n0 = sub; n0 < ((p.dbg & 4) ? 0 : n_here); n0 += kSB * rows_per_iter) {    // bit 2 = no staging
             for (int v = v0; v < pieces_per_row; v += lanes_per_row) {
                 uint4 x[kSB];
 #pragma unroll
                 for (int u = 0; u < kSB; ++u) {
                     const int n = n0 + u * rows_per_iter;
-                    x[u] = make_uint4(0, 0, 0, 0);
                     if (n < n_here) x[u] = ldg16(p.src + (size_t)(list[pass * kNT + n] / p.src_div) * p.src_ld + v * 8);
                 }
                 const int j = v >> 4, r = v & 15;
 #pragma unroll
                 for (int u = 0; u < kSB; ++u) {
                     const int n = n0 + u * rows_per_iter;
-                    if (n >= ntiles * 8) break;
+                    if (n >= n_here) break;
                     uint4 o;
                     o.x = __byte_perm(x[u].x, x[u].z, 0x5410); o.y = __byte_perm(x[u].x, x[u].z, 0x7632);     // (k0,k4) (k1,k5)
                     o.z = __byte_perm(x[u].y, x[u].w, 0x5410); o.w = __byte_perm(x[u].y, x[u].w, 0x7632);     // (k2,k6) (k3,k7)
@@ -151,58 +183,51 @@ __global__ void __launch_bounds__(kThreads, 4) fp4_rows_kernel(const Fp4RowsArgs
                 }
             }
         }
-        __syncthreads();
+        if (!have_weights) {       // bounded wait; a block that gives up reports it in the status word and leaves
+            const bool ok = tc::mbar_wait(tc::smem_u32(&wbar), 0, &abort_s, p.status);
+            if (!__syncthreads_and(ok)) return;
+            have_weights = true;
+        } else {
+            __syncthreads();
+        }
 
-        float acc[2][4];
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[t][i] = 0.0f;
-        if (pass > 0) { cur = load_chunk(ch0); nxt = ch0 + 1 < ch1 ? load_chunk(ch0 + 1) : cur; }
 #pragma unroll 1
-        for (int j = ch0; j < ch1; ++j) {
-            Chunk fut = nxt;
-            if (j + 2 < ch1) fut = load_chunk(j + 2);
-            const uint32_t a_w[4] = {cur.a.x, cur.a.y, cur.a.z, cur.a.w}, b_w[4] = {cur.b.x, cur.b.y, cur.b.z, cur.b.w};
-            const uint32_t sA[2] = {scale_bf2(cur.sa & 0xffu), scale_bf2(cur.sa >> 8)};
-            const uint32_t sB[2] = {scale_bf2(cur.sb & 0xffu), scale_bf2(cur.sb >> 8)};
-            const uint32_t bbase = stage + (uint32_t)g * rowb + (uint32_t)(j * 256 + c * 16);
+        for (int rg = 0; rg < RGW; ++rg, ++turn) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const int lrow = rg * kRowsPerCta + rgroup * 16 + g;      // row inside the block's tile; its partner is 8 further
+            const uint32_t crow = codes + (uint32_t)lrow * cpitch + (uint32_t)c * 16;
+            const uint32_t srow = scales + (uint32_t)lrow * spitch + (uint32_t)c * 2;
+            const uint32_t brow = stage + (uint32_t)g * rowb + (uint32_t)c * 16;
+#pragma unroll 2
+            for (int j = ch0; j < ((p.dbg & 2) ? ch0 : ch1); ++j) {     // bit 1 = no products
+                const uint4 ca = lds16u(crow + j * 64), cb = lds16u(crow + 8 * cpitch + j * 64);
+                const uint32_t sa = lds_u16(srow + j * 8), sb = lds_u16(srow + 8 * spitch + j * 8);
+                const uint32_t a_w[4] = {ca.x, ca.y, ca.z, ca.w}, b_w[4] = {cb.x, cb.y, cb.z, cb.w};
+                const uint32_t sA[2] = {lds_u32(lut + (sa & 0xffu) * 4), lds_u32(lut + (sa >> 8) * 4)};
+                const uint32_t sB[2] = {lds_u32(lut + (sb & 0xffu) * 4), lds_u32(lut + (sb >> 8) * 4)};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint32_t wa = a_w[q], wb = b_w[q], s_a = sA[q >> 1], s_b = sB[q >> 1];
-                const uint32_t a00 = expand_pair<0>(wa, s_a), a01 = expand_pair<1>(wa, s_a);
-                const uint32_t a02 = expand_pair<2>(wa, s_a), a03 = expand_pair<3>(wa, s_a);
-                const uint32_t a80 = expand_pair<0>(wb, s_b), a81 = expand_pair<1>(wb, s_b);
-                const uint32_t a82 = expand_pair<2>(wb, s_b), a83 = expand_pair<3>(wb, s_b);
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (t < ntiles) {
-                        const uint4 x = lds16u(bbase + (uint32_t)(t * 8) * rowb + (uint32_t)q * 64);
-                        mma_bf16(acc[t], a00, a80, a01, a81, x.x, x.y);
-                        mma_bf16(acc[t], a02, a82, a03, a83, x.z, x.w);
-                    }
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t wa = a_w[q], wb = b_w[q], s_a = sA[q >> 1], s_b = sB[q >> 1];
+                    const uint4 x = lds16u(brow + (uint32_t)(j * 256 + q * 64));
+                    mma_bf16(acc, expand_pair<0>(wa, s_a), expand_pair<0>(wb, s_b), expand_pair<1>(wa, s_a), expand_pair<1>(wb, s_b), x.x, x.y);
+                    mma_bf16(acc, expand_pair<2>(wa, s_a), expand_pair<2>(wb, s_b), expand_pair<3>(wa, s_a), expand_pair<3>(wb, s_b), x.z, x.w);
                 }
             }
-            cur = nxt; nxt = fut;
-        }
-        // the second k half hands its sums to the first
-        if (ks == 1) {
+            // the second k half hands its sums to the first (two buffers in turn: one barrier per row group)
+            float* rbuf = red + (turn & 1) * (4 * 256);
+            if (ks == 1) {
 #pragma unroll
-            for (int t = 0; t < 2; ++t)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) red[(t * 4 + i) * 128 + rgroup * 32 + lane] = acc[t][i];
-        }
-        __syncthreads();
-        if (ks == 0) {
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
+                for (int i = 0; i < 4; ++i) rbuf[i * 256 + rgroup * 32 + lane] = acc[i];
+            }
+            __syncthreads();
+            if (ks == 0) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int n = t * 8 + c * 2 + (i & 1);
+                    const int n = c * 2 + (i & 1);
                     if (n >= n_here) continue;
                     const int asg = list[pass * kNT + n];
-                    const int row = r0 + g + (i >> 1) * 8;
-                    const float v = acc[t][i] + red[(t * 4 + i) * 128 + rgroup * 32 + lane];
+                    const int row = row0 + lrow + (i >> 1) * 8;
+                    const float v = acc[i] + rbuf[i * 256 + rgroup * 32 + lane];
                     float o;
                     if constexpr (MODE == 0) {
                         const float a = round_bf(es * v);
@@ -242,20 +267,30 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const uint16_t* __r
     stg16(dst, make_uint4(pack_bf2(acc[0], acc[1]), pack_bf2(acc[2], acc[3]), pack_bf2(acc[4], acc[5]), pack_bf2(acc[6], acc[7])));
 }
 
-size_t rows_smem(int kdim) { return (size_t)kDecodeMaxAsg * 4 + 128 * 8 * 4 + (size_t)kNT * (kdim * 2 + 64); }
+size_t rows_smem(int kdim, int rgw) {
+    return (size_t)kListBytes + kRedBytes + kLutBytes + (size_t)kRowsPerCta * rgw * ((kdim >> 1) + 64 + (kdim >> 4) + 16) +
+           (size_t)kNT * (kdim * 2 + 64);
+}
+
+template <int MODE, int RGW>
+cudaError_t launch_rows_t(const Fp4RowsArgs& a, int experts, cudaStream_t s) {
+    const size_t smem = rows_smem(a.kdim, RGW);
+    cudaError_t e = cudaFuncSetAttribute(fp4_rows_kernel<MODE, RGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    fp4_rows_kernel<MODE, RGW><<<dim3(a.rows / (kRowsPerCta * RGW), experts), kThreads, smem, s>>>(a);
+    return cudaGetLastError();
+}
 
 }  // namespace
 
+// A block covers 256 weight rows when the tile fits in shared memory and that still gives about one block per SM,
+// else 128 (TMT_MOE_FP4_ROW_GROUPS = 1 / 2 forces the choice where the shape allows it).
 cudaError_t launch_fp4_rows(const Fp4RowsArgs& a, int experts, int mode, cudaStream_t s) {
-    const size_t smem = rows_smem(a.kdim);
-    cudaError_t e = mode == 0
-        ? cudaFuncSetAttribute(fp4_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-        : cudaFuncSetAttribute(fp4_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    const dim3 grid(a.rows / kRowsPerCta, experts);
-    if (mode == 0) fp4_rows_kernel<0><<<grid, kThreads, smem, s>>>(a);
-    else fp4_rows_kernel<1><<<grid, kThreads, smem, s>>>(a);
-    return cudaGetLastError();
+    const bool two_ok = a.rows % (2 * kRowsPerCta) == 0 && rows_smem(a.kdim, 2) <= (size_t)kMaxSmem;
+    int rgw = two_ok && (long)(a.rows / (2 * kRowsPerCta)) * experts >= 120 ? 2 : 1;
+    if (const char* f = getenv("TMT_MOE_FP4_ROW_GROUPS")) if (*f == '1' || (*f == '2' && two_ok)) rgw = *f - '0';
+    if (mode == 0) return rgw == 2 ? launch_rows_t<0, 2>(a, experts, s) : launch_rows_t<0, 1>(a, experts, s);
+    return rgw == 2 ? launch_rows_t<1, 2>(a, experts, s) : launch_rows_t<1, 1>(a, experts, s);
 }
 
 cudaError_t launch_decode_combine(const uint16_t* Ya, uint16_t* Y, float beta, int T, int D, int K, cudaStream_t s) {
@@ -265,7 +300,7 @@ cudaError_t launch_decode_combine(const uint16_t* Ya, uint16_t* Y, float beta, i
 }
 
 bool fp4_rows_shape_ok(int rows, int kdim) {
-    return rows % kRowsPerCta == 0 && kdim % 256 == 0 && rows_smem(kdim) <= 200 * 1024;
+    return rows % kRowsPerCta == 0 && kdim % 256 == 0 && rows_smem(kdim, 1) <= (size_t)kMaxSmem;
 }
 
 }  // namespace tmt

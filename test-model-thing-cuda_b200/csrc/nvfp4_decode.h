@@ -17,9 +17,11 @@ struct Fp4RowsArgs {
     const int* idx;                     // [n_asg] expert of each assignment
     const float* gate;                  // [n_asg] gate weights (mode 1)
     int n_asg, rows, kdim;
+    int* status;                        // device status word (a bounded wait that ran out is reported there)
+    int dbg;                            // measurement only (TMT_MOE_FP4_DEBUG): 1 stop after the list, 2 no products, 4 no staging
 };
 
-// out = expert rows x the assignments routed to the expert; grid = (rows / 64, experts).
+// out = expert rows x the assignments routed to the expert; grid = (rows / 128 or 256, experts).
 cudaError_t launch_fp4_rows(const Fp4RowsArgs& a, int experts, int mode, cudaStream_t s);
 cudaError_t launch_decode_combine(const uint16_t* Ya, uint16_t* Y, float beta, int T, int D, int K, cudaStream_t s);
 bool fp4_rows_shape_ok(int rows, int kdim);

@@ -307,12 +307,15 @@ __global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, co
 
 // Scan, part 2: one block. True and padded group starts (moe.cu:413-419), tile -> expert table,
 // number of tiles in use, split table of the router weight-gradient product.
-__device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteBufs& b, int splits, int* poff_s) {
+__device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteBufs& b, int splits, int* poff_s, int* cnt_s) {
     const int E = d.E;
+    // counts first, all at once: read one by one between the stores below, every load would wait a full round trip
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt_s[e] = b.counts[e];
+    __syncthreads();
     if (threadIdx.x == 0) {
         int tk = 0, ptk = 0;
         for (int e = 0; e < E; ++e) {
-            const int c = b.counts[e];
+            const int c = cnt_s[e];
             b.off[e] = tk; tk += c;
             poff_s[e] = ptk; b.poff[e] = ptk;
             ptk += (c + d.pad - 1) / d.pad * d.pad;
@@ -323,7 +326,7 @@ __device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteB
         if (b.use_acc) b.use_acc[E] += 1;
     }
     if (b.use_acc)      // router-balance telemetry: usage accumulated on the device, read when the host asks
-        for (int e = threadIdx.x; e < E; e += blockDim.x) b.use_acc[e] += b.counts[e];
+        for (int e = threadIdx.x; e < E; e += blockDim.x) b.use_acc[e] += cnt_s[e];
     __syncthreads();
     const int used = poff_s[E] <= d.cap ? poff_s[E] / kPad : 0;
     for (int i = threadIdx.x; i < d.max_tiles; i += blockDim.x) {
@@ -341,8 +344,8 @@ __device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteB
     for (int i = threadIdx.x; i <= splits; i += blockDim.x) b.split_poff[i] = (int)((long)used * i / splits) * kPad;
 }
 __global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, const RouteBufs b, int splits) {
-    __shared__ int poff_s[257];
-    scan_finish_dev(d, b, splits, poff_s);
+    __shared__ int poff_s[257], cnt_s[256];
+    scan_finish_dev(d, b, splits, poff_s, cnt_s);
 }
 
 // Few tokens (sampler steps, short sequences): the 64-token block above would leave all but a handful of SMs idle.
@@ -411,7 +414,7 @@ __global__ void __launch_bounds__(kFinishThreads) router_finish_kernel(const Rou
     float* lg = reinterpret_cast<float*>(smem);          // [kTokBlock][E]
     __shared__ int sidx[kTokBlock * 8];
     __shared__ float zs[kTokBlock];
-    __shared__ int poff_s[257];
+    __shared__ int poff_s[257], cnt_s[256];
     const long tok0 = (long)blockIdx.x * kTokBlock;
     for (int i = threadIdx.x; i < kTokBlock * a.E; i += kFinishThreads) {
         const long t = tok0 + i / a.E;
@@ -424,7 +427,7 @@ __global__ void __launch_bounds__(kFinishThreads) router_finish_kernel(const Rou
         const int warp = threadIdx.x >> 5;
         scan_columns_dev(d, a.b, 1, warp, kFinishThreads / 32, warp == kFinishThreads / 32 - 1);
         __syncthreads();
-        scan_finish_dev(d, a.b, splits, poff_s);
+        scan_finish_dev(d, a.b, splits, poff_s, cnt_s);
     }
 }
 

@@ -88,11 +88,13 @@ def test_forward_nvfp4_decode_shape(impl, route, monkeypatch):
     pytest.param(dict(T=64, D=512, H=256, E=8, K=3, beta=0.0, tiny=True), id="top3_subnormal_and_zero_block_scales"),
     pytest.param(dict(T=1, D=256, H=256, E=16, K=2, beta=0.0, tiny=False), id="one_token_most_experts_idle"),
 ])
-def test_small_batch_route_matches_expanded_route(case, monkeypatch):
+@pytest.mark.parametrize("row_groups", ["1", "2"])
+def test_small_batch_route_matches_expanded_route(case, row_groups, monkeypatch):
     """Both routes multiply the same bf16 values (q * block scale) with fp32 accumulation; only the order of the sums and
     one bf16 rounding of the SiLU input can differ. Against the oracle: relative L2 <= 1e-2; between routes: <= 3e-3."""
     import gpu_util as G
     import tmt_moe_b200 as M
+    monkeypatch.setenv("TMT_MOE_FP4_ROW_GROUPS", row_groups)     # 64 or 128 weight rows per block
     T, D, H, E, K = case["T"], case["D"], case["H"], case["E"], case["K"]
     data, up_q, down_q, up_dq, down_dq, us, ds, keep = _setup(M, G, T, D, H, E, K, 77, tiny_blocks=case["tiny"])
     ref = O.forward(data["X"], data["Wr"], up_dq, down_dq, K, up_scale=us, down_scale=ds, pad=128)
