@@ -20,6 +20,7 @@
 #include <cstdlib>
 
 #include "kernels.cuh"
+#include "launch_pdl.cuh"
 #include "nvfp4_decode.h"
 #include "tc_util.cuh"
 
@@ -104,9 +105,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
     const int g = lane >> 2, c = lane & 3;
     const int rgroup = warp & 7, ks = warp >> 3;
     const int ch0 = ks * nchunks / kKSplit, ch1 = (ks + 1) * nchunks / kKSplit;
-    // this warp's first slice of the assignment table, asked for before anything that has to wait for a pointer
-    const int first_idx = warp * 32 + lane < p.n_asg ? p.idx[warp * 32 + lane] : -1;
     const int row0 = blockIdx.x * R;
+    pdl_begin();
     if (threadIdx.x == 0) {
         abort_s = 0;
         tc::mbar_init(tc::smem_u32(&wbar), 1);
@@ -120,6 +120,19 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
         if (ex == 0) b = f2bf((float)m * 0x1p103f);                   // subnormal: m * 2^-9 * 2^112
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut + byte * 4), "r"(b | (b << 16)) : "memory");
     }
+    __syncthreads();
+    // The weights do not depend on the kernels before this one: ask for the block's whole tile now, so that it travels
+    // while those kernels finish (an expert that turns out to have no tokens pays for the copy and waits for it below).
+    if (threadIdx.x < R) {
+        bulk_load_row(codes + threadIdx.x * cpitch, p.packed[e] + (size_t)(row0 + threadIdx.x) * (kdim >> 1), (uint32_t)(kdim >> 1),
+                      tc::smem_u32(&wbar));
+    } else if (threadIdx.x >= 256 && threadIdx.x - 256 < R) {
+        const int r = threadIdx.x - 256;
+        bulk_load_row(scales + r * spitch, p.scales[e] + (size_t)(row0 + r) * (kdim >> 4), (uint32_t)(kdim >> 4), tc::smem_u32(&wbar));
+    }
+    pdl_wait();        // everything above read only the weights and wrote only this block's shared memory
+    // this warp's first slice of the assignment table, asked for before anything that has to wait for a pointer
+    const int first_idx = warp * 32 + lane < p.n_asg ? p.idx[warp * 32 + lane] : -1;
     // token list, ascending: warp w takes the 32-assignment slices w, w + 16, ...; one load latency in all
     for (int sl = warp; sl * 32 < p.n_asg; sl += kThreads / 32) {
         const int i = sl * 32 + lane;
@@ -143,13 +156,9 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
     }
     __syncthreads();
     const int cnt = (p.dbg & 1) ? 0 : s_cnt;      // measurement only: bit 0 = stop after the token list
-    if (cnt == 0) return;                          // an expert without tokens asks for no weights
-    if (threadIdx.x < R) {
-        bulk_load_row(codes + threadIdx.x * cpitch, p.packed[e] + (size_t)(row0 + threadIdx.x) * (kdim >> 1), (uint32_t)(kdim >> 1),
-                      tc::smem_u32(&wbar));
-    } else if (threadIdx.x >= 256 && threadIdx.x - 256 < R) {
-        const int r = threadIdx.x - 256;
-        bulk_load_row(scales + r * spitch, p.scales[e] + (size_t)(row0 + r) * (kdim >> 4), (uint32_t)(kdim >> 4), tc::smem_u32(&wbar));
+    if (cnt == 0) {                                // nothing to do, but the copies must have landed before the block may leave
+        tc::mbar_wait(tc::smem_u32(&wbar), 0, &abort_s, p.status);
+        return;
     }
     const float es = p.es[e];
     const int pieces_per_row = kdim >> 3;
@@ -247,6 +256,8 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const uint16_t* __r
                                                              int T, int D, int K) {
     const int nvec = D >> 3;
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_begin();
+    pdl_wait();
     if (i >= (long)T * nvec) return;
     const long t = i / nvec; const int v = (int)(i - t * nvec);
     float acc[8];
@@ -277,8 +288,7 @@ cudaError_t launch_rows_t(const Fp4RowsArgs& a, int experts, cudaStream_t s) {
     const size_t smem = rows_smem(a.kdim, RGW);
     cudaError_t e = cudaFuncSetAttribute(fp4_rows_kernel<MODE, RGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    fp4_rows_kernel<MODE, RGW><<<dim3(a.rows / (kRowsPerCta * RGW), experts), kThreads, smem, s>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(fp4_rows_kernel<MODE, RGW>, dim3(a.rows / (kRowsPerCta * RGW), experts), dim3(kThreads), smem, s, a);
 }
 
 }  // namespace
@@ -295,8 +305,7 @@ cudaError_t launch_fp4_rows(const Fp4RowsArgs& a, int experts, int mode, cudaStr
 
 cudaError_t launch_decode_combine(const uint16_t* Ya, uint16_t* Y, float beta, int T, int D, int K, cudaStream_t s) {
     const long n = (long)T * (D >> 3);
-    decode_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(Ya, Y, beta, T, D, K);
-    return cudaGetLastError();
+    return launch_pdl(decode_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, Ya, Y, beta, T, D, K);
 }
 
 bool fp4_rows_shape_ok(int rows, int kdim) {

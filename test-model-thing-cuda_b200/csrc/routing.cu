@@ -14,6 +14,7 @@
 #include <cstdlib>
 
 #include "kernels.cuh"
+#include "launch_pdl.cuh"
 
 namespace tmt {
 namespace {
@@ -356,6 +357,8 @@ template <bool WF32>
 __global__ void __launch_bounds__(128) router_logits_small_kernel(const RouterArgs a) {
     const int s = threadIdx.x & 7, grp = threadIdx.x >> 3;
     const long t = blockIdx.x;
+    pdl_begin();
+    pdl_wait();
     const int nvec = a.D >> 3;
     const unsigned full = 0xffffffffu;
     const uint16_t* xrow = a.X + t * a.D;
@@ -416,6 +419,8 @@ __global__ void __launch_bounds__(kFinishThreads) router_finish_kernel(const Rou
     __shared__ float zs[kTokBlock];
     __shared__ int poff_s[257], cnt_s[256];
     const long tok0 = (long)blockIdx.x * kTokBlock;
+    pdl_begin();
+    pdl_wait();
     for (int i = threadIdx.x; i < kTokBlock * a.E; i += kFinishThreads) {
         const long t = tok0 + i / a.E;
         lg[i] = t < a.T ? a.b.logits[tok0 * a.E + i] : 0.0f;
@@ -469,17 +474,17 @@ cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t
     bool small = (long)d.T * d.E <= kSmallRouterLogits;
     if (const char* f = getenv("TMT_MOE_ROUTER_SMALL")) if (*f) small = *f != '0';
     if (small) {
-        if (d.router_f32) router_logits_small_kernel<true><<<d.T, 128, 0, s>>>(a);
-        else router_logits_small_kernel<false><<<d.T, 128, 0, s>>>(a);
+        cudaError_t le = d.router_f32 ? launch_pdl(router_logits_small_kernel<true>, dim3(d.T), dim3(128), 0, s, a)
+                                      : launch_pdl(router_logits_small_kernel<false>, dim3(d.T), dim3(128), 0, s, a);
+        if (le != cudaSuccess) return le;
         const size_t smem = (size_t)kTokBlock * d.E * sizeof(float);
         if (smem > 40 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(router_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
         const bool fuse = nb == 1 && scan_splits > 0 && scanned != nullptr;
-        router_finish_kernel<<<nb, kFinishThreads, smem, s>>>(a, d, fuse ? scan_splits : 0);
         if (fuse) *scanned = true;
-        return cudaGetLastError();
+        return launch_pdl(router_finish_kernel, dim3(nb), dim3(kFinishThreads), smem, s, a, d, fuse ? scan_splits : 0);
     }
     return d.router_f32 ? launch_router_w<true>(a, nb, s) : launch_router_w<false>(a, nb, s);
 }
