@@ -54,8 +54,11 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // Second half of the router, on the logits of one block of kTokBlock tokens in shared memory (lg, [kTokBlock][E]):
 // softmax, top-k, gate weights, then the block's stable ranks, counts and statistics partials.
+// keep_cnt / keep_sp / keep_z (shared memory, may be NULL): the block's counts, probability sums and z partial stay on
+// chip as well, for a caller that goes on to the scan itself.
 template <int NTHR>
-__device__ __forceinline__ void route_block_finish(const RouterArgs& a, float* lg, int* sidx, float* zs, long tok0) {
+__device__ __forceinline__ void route_block_finish(const RouterArgs& a, float* lg, int* sidx, float* zs, long tok0,
+                                                   int* keep_cnt = nullptr, float* keep_sp = nullptr, float* keep_z = nullptr) {
     const int E = a.E, K = a.K;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int s = lane & 7, g = lane >> 3;
@@ -124,17 +127,19 @@ __device__ __forceinline__ void route_block_finish(const RouterArgs& a, float* l
             if (hit) a.b.rank[(long)blockIdx.x * n_asg + c0 + lane] = running + __popc(m & ((1u << lane) - 1));
             running += __popc(m);
         }
-        if (lane == 0) a.b.block_counts[(long)blockIdx.x * E + e] = running;
+        if (lane == 0) { a.b.block_counts[(long)blockIdx.x * E + e] = running; if (keep_cnt) keep_cnt[e] = running; }
     }
     for (int e = threadIdx.x; e < E; e += NTHR) {
         float sp = 0.0f;
         for (int tb = 0; tb < kTokBlock; ++tb) sp += lg[tb * E + e];
         a.b.block_sump[(long)blockIdx.x * E + e] = sp;
+        if (keep_sp) keep_sp[e] = sp;
     }
     if (threadIdx.x == NTHR - 1) {
         float z = 0.0f;
         for (int tb = 0; tb < kTokBlock; ++tb) z += zs[tb];
         a.b.block_z[blockIdx.x] = z;
+        if (keep_z) *keep_z = z;
     }
 }
 
@@ -308,11 +313,14 @@ __global__ void __launch_bounds__(256) scan_columns_kernel(const RouteDims d, co
 
 // Scan, part 2: one block. True and padded group starts (moe.cu:413-419), tile -> expert table,
 // number of tiles in use, split table of the router weight-gradient product.
-__device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteBufs& b, int splits, int* poff_s, int* cnt_s) {
+__device__ __forceinline__ void scan_finish_dev(const RouteDims& d, const RouteBufs& b, int splits, int* poff_s, int* cnt_s,
+                                                bool counts_ready = false) {
     const int E = d.E;
     // counts first, all at once: read one by one between the stores below, every load would wait a full round trip
-    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt_s[e] = b.counts[e];
-    __syncthreads();
+    if (!counts_ready) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) cnt_s[e] = b.counts[e];
+        __syncthreads();
+    }
     if (threadIdx.x == 0) {
         int tk = 0, ptk = 0;
         for (int e = 0; e < E; ++e) {
@@ -426,13 +434,21 @@ __global__ void __launch_bounds__(kFinishThreads) router_finish_kernel(const Rou
         lg[i] = t < a.T ? a.b.logits[tok0 * a.E + i] : 0.0f;
     }
     __syncthreads();
-    route_block_finish<kFinishThreads>(a, lg, sidx, zs, tok0);
-    if (splits > 0) {
-        __syncthreads();        // the block's counts and partials are in global memory, written by this block
-        const int warp = threadIdx.x >> 5;
-        scan_columns_dev(d, a.b, 1, warp, kFinishThreads / 32, warp == kFinishThreads / 32 - 1);
+    __shared__ float sp_s[256], z_s;
+    const bool fused = splits > 0;
+    route_block_finish<kFinishThreads>(a, lg, sidx, zs, tok0, fused ? cnt_s : nullptr, fused ? sp_s : nullptr, fused ? &z_s : nullptr);
+    if (fused) {
+        // One block holds every token: its counts and partial sums ARE the totals (what the first part of the scan
+        // computes from a single block: base 0, the same sums with zeros added), and they are still in shared memory.
         __syncthreads();
-        scan_finish_dev(d, a.b, splits, poff_s, cnt_s);
+        const int E = a.E;
+        for (int e = threadIdx.x; e < E; e += kFinishThreads) {
+            a.b.block_base[e] = 0;
+            a.b.counts[e] = cnt_s[e];
+            a.b.stat[e] = E == 1 ? 0.0f : sp_s[e];
+        }
+        if (threadIdx.x == kFinishThreads - 1) a.b.stat[E] = E == 1 ? 0.0f : z_s / (float)d.T;
+        scan_finish_dev(d, a.b, splits, poff_s, cnt_s, true);
     }
 }
 
