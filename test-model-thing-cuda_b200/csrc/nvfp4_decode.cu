@@ -27,11 +27,12 @@
 namespace tmt {
 namespace {
 
-constexpr int kNT = 8;                  // tokens (assignments) of one expert per pass: one MMA column tile
+constexpr int kNT = 16;                 // tokens (assignments) of one expert per pass: two MMA column tiles share one expansion
 constexpr int kRowsPerCta = 128;        // 8 row groups of 16 weight rows (times RGW)
 constexpr int kKSplit = 2;              // warps sharing a row group, each with half of the chunks
 constexpr int kThreads = 256 * kKSplit;
-constexpr int kListBytes = kDecodeMaxAsg * 4, kRedBytes = 2 * 4 * 256 * 4, kLutBytes = 256 * 4;
+constexpr int kListBytes = kDecodeMaxAsg * 4, kLutBytes = 256 * 4;
+__host__ __device__ constexpr int red_bytes(int rgw) { return rgw * 8 * 256 * 4; }
 constexpr int kSB = 4;                  // staged rows a thread fetches before it stores any
 constexpr int kMaxSmem = 227 * 1024;
 
@@ -88,12 +89,12 @@ template <int MODE, int RGW>
 __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
     int* list = reinterpret_cast<int*>(smem);                         // assignments of this expert, ascending
-    float* red = reinterpret_cast<float*>(smem + kListBytes);         // [2][4][256] partial sums of the second k half
-    const int kdim = p.kdim, nchunks = kdim >> 7;
+    float* red = reinterpret_cast<float*>(smem + kListBytes);         // [RGW][2][4][256] partial sums of the second k half
+    const int kdim = p.kdim;
     constexpr int R = kRowsPerCta * RGW;
     const uint32_t cpitch = (uint32_t)(kdim >> 1) + 64, spitch = (uint32_t)(kdim >> 4) + 16;
-    const uint32_t rowb = (uint32_t)kdim * 2 + 64;                    // staged token row pitch
-    const uint32_t lut = tc::smem_u32(smem) + kListBytes + kRedBytes; // e4m3 byte -> scale * 2^112 as bf16x2
+    const uint32_t rowb = (uint32_t)(kdim / p.kphases) * 2 + 64;      // staged token row pitch
+    const uint32_t lut = tc::smem_u32(smem) + kListBytes + red_bytes(RGW); // e4m3 byte -> scale * 2^112 as bf16x2
     const uint32_t codes = lut + kLutBytes;
     const uint32_t scales = codes + R * cpitch;
     const uint32_t stage = scales + R * spitch;
@@ -104,7 +105,6 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
     const int rgroup = warp & 7, ks = warp >> 3;
-    const int ch0 = ks * nchunks / kKSplit, ch1 = (ks + 1) * nchunks / kKSplit;
     const int row0 = blockIdx.x * R;
     pdl_begin();
     if (threadIdx.x == 0) {
@@ -161,92 +161,119 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
         return;
     }
     const float es = p.es[e];
-    const int pieces_per_row = kdim >> 3;
+    // token rows are staged kstage columns at a time (the whole row when it fits beside the weight tile)
+    const int kstage = kdim / p.kphases, cpp = kstage >> 7;          // chunks per phase, split between the two k halves
+    const int pieces_per_row = kstage >> 3;
     const int lanes_per_row = min(pieces_per_row, kThreads), rows_per_iter = kThreads / lanes_per_row;
     const int sub = threadIdx.x / lanes_per_row, v0 = threadIdx.x - sub * lanes_per_row;
-    int turn = 0;                                                     // alternates the two halves of `red`
+    const int jl0 = ks * cpp / kKSplit, jl1 = (ks + 1) * cpp / kKSplit;
     bool have_weights = false;
 
     for (int pass = 0; pass * kNT < cnt; ++pass) {
         const int n_here = min(kNT, cnt - pass * kNT);
-        // rows of the pass -> shared memory, permuted; kSB 16-byte loads in flight per thread. Columns past n_here stay
-        // as they are: a column of the product depends on nothing but its own token. (Every warp has passed the last
-        // barrier of the previous pass, so nobody still reads the previous rows.)
-        for (int n0 = sub; n0 < ((p.dbg & 4) ? 0 : n_here); n0 += kSB * rows_per_iter) {    // bit 2 = no staging
-            for (int v = v0; v < pieces_per_row; v += lanes_per_row) {
-                uint4 x[kSB];
+        const int ntiles = (n_here + 7) >> 3;
+        float acc[RGW][2][4];
 #pragma unroll
-                for (int u = 0; u < kSB; ++u) {
-                    const int n = n0 + u * rows_per_iter;
-                    if (n < n_here) x[u] = ldg16(p.src + (size_t)(list[pass * kNT + n] / p.src_div) * p.src_ld + v * 8);
-                }
-                const int j = v >> 4, r = v & 15;
+        for (int rg = 0; rg < RGW; ++rg)
 #pragma unroll
-                for (int u = 0; u < kSB; ++u) {
-                    const int n = n0 + u * rows_per_iter;
-                    if (n >= n_here) break;
-                    uint4 o;
-                    o.x = __byte_perm(x[u].x, x[u].z, 0x5410); o.y = __byte_perm(x[u].x, x[u].z, 0x7632);     // (k0,k4) (k1,k5)
-                    o.z = __byte_perm(x[u].y, x[u].w, 0x5410); o.w = __byte_perm(x[u].y, x[u].w, 0x7632);     // (k2,k6) (k3,k7)
-                    sts16u(stage + (uint32_t)n * rowb + (uint32_t)(j * 256 + (r & 3) * 64 + (r >> 2) * 16), o);
-                }
-            }
-        }
-        if (!have_weights) {       // bounded wait; a block that gives up reports it in the status word and leaves
-            const bool ok = tc::mbar_wait(tc::smem_u32(&wbar), 0, &abort_s, p.status);
-            if (!__syncthreads_and(ok)) return;
-            have_weights = true;
-        } else {
-            __syncthreads();
-        }
-
-#pragma unroll 1
-        for (int rg = 0; rg < RGW; ++rg, ++turn) {
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const int lrow = rg * kRowsPerCta + rgroup * 16 + g;      // row inside the block's tile; its partner is 8 further
-            const uint32_t crow = codes + (uint32_t)lrow * cpitch + (uint32_t)c * 16;
-            const uint32_t srow = scales + (uint32_t)lrow * spitch + (uint32_t)c * 2;
-            const uint32_t brow = stage + (uint32_t)g * rowb + (uint32_t)c * 16;
-#pragma unroll 2
-            for (int j = ch0; j < ((p.dbg & 2) ? ch0 : ch1); ++j) {     // bit 1 = no products
-                const uint4 ca = lds16u(crow + j * 64), cb = lds16u(crow + 8 * cpitch + j * 64);
-                const uint32_t sa = lds_u16(srow + j * 8), sb = lds_u16(srow + 8 * spitch + j * 8);
-                const uint32_t a_w[4] = {ca.x, ca.y, ca.z, ca.w}, b_w[4] = {cb.x, cb.y, cb.z, cb.w};
-                const uint32_t sA[2] = {lds_u32(lut + (sa & 0xffu) * 4), lds_u32(lut + (sa >> 8) * 4)};
-                const uint32_t sB[2] = {lds_u32(lut + (sb & 0xffu) * 4), lds_u32(lut + (sb >> 8) * 4)};
+            for (int t = 0; t < 2; ++t)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t wa = a_w[q], wb = b_w[q], s_a = sA[q >> 1], s_b = sB[q >> 1];
-                    const uint4 x = lds16u(brow + (uint32_t)(j * 256 + q * 64));
-                    mma_bf16(acc, expand_pair<0>(wa, s_a), expand_pair<0>(wb, s_b), expand_pair<1>(wa, s_a), expand_pair<1>(wb, s_b), x.x, x.y);
-                    mma_bf16(acc, expand_pair<2>(wa, s_a), expand_pair<2>(wb, s_b), expand_pair<3>(wa, s_a), expand_pair<3>(wb, s_b), x.z, x.w);
-                }
-            }
-            // the second k half hands its sums to the first (two buffers in turn: one barrier per row group)
-            float* rbuf = red + (turn & 1) * (4 * 256);
-            if (ks == 1) {
+                for (int i = 0; i < 4; ++i) acc[rg][t][i] = 0.0f;
+        for (int ph = 0; ph < p.kphases; ++ph) {
+            if (pass + ph > 0) __syncthreads();                       // everyone has left the rows staged before
+            // rows of the pass -> shared memory, permuted; kSB 16-byte loads in flight per thread. Columns past n_here
+            // stay as they are: a column of the product depends on nothing but its own token.
+            for (int n0 = sub; n0 < ((p.dbg & 4) ? 0 : n_here); n0 += kSB * rows_per_iter) {    // bit 2 = no staging
+                for (int v = v0; v < pieces_per_row; v += lanes_per_row) {
+                    uint4 x[kSB];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) rbuf[i * 256 + rgroup * 32 + lane] = acc[i];
-            }
-            __syncthreads();
-            if (ks == 0) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int n = c * 2 + (i & 1);
-                    if (n >= n_here) continue;
-                    const int asg = list[pass * kNT + n];
-                    const int row = row0 + lrow + (i >> 1) * 8;
-                    const float v = acc[i] + rbuf[i * 256 + rgroup * 32 + lane];
-                    float o;
-                    if constexpr (MODE == 0) {
-                        const float a = round_bf(es * v);
-                        o = a * sigmoid_fast(a);
-                    } else {
-                        o = p.gate[asg] * (es * v);
+                    for (int u = 0; u < kSB; ++u) {
+                        const int n = n0 + u * rows_per_iter;
+                        if (n < n_here)
+                            x[u] = ldg16(p.src + (size_t)(list[pass * kNT + n] / p.src_div) * p.src_ld + (size_t)ph * kstage + v * 8);
                     }
-                    p.out[(size_t)asg * p.out_ld + row] = f2bf(o);
+                    const int j = v >> 4, r = v & 15;
+#pragma unroll
+                    for (int u = 0; u < kSB; ++u) {
+                        const int n = n0 + u * rows_per_iter;
+                        if (n >= n_here) break;
+                        uint4 o;
+                        o.x = __byte_perm(x[u].x, x[u].z, 0x5410); o.y = __byte_perm(x[u].x, x[u].z, 0x7632);     // (k0,k4) (k1,k5)
+                        o.z = __byte_perm(x[u].y, x[u].w, 0x5410); o.w = __byte_perm(x[u].y, x[u].w, 0x7632);     // (k2,k6) (k3,k7)
+                        sts16u(stage + (uint32_t)n * rowb + (uint32_t)(j * 256 + (r & 3) * 64 + (r >> 2) * 16), o);
+                    }
                 }
             }
+            if (!have_weights) {       // bounded wait; a block that gives up reports it in the status word and leaves
+                const bool ok = tc::mbar_wait(tc::smem_u32(&wbar), 0, &abort_s, p.status);
+                if (!__syncthreads_and(ok)) return;
+                have_weights = true;
+            } else {
+                __syncthreads();
+            }
+#pragma unroll
+            for (int rg = 0; rg < RGW; ++rg) {
+                const int lrow = rg * kRowsPerCta + rgroup * 16 + g;  // row inside the block's tile; its partner is 8 further
+                const uint32_t crow = codes + (uint32_t)lrow * cpitch + (uint32_t)(c * 16 + ph * cpp * 64);
+                const uint32_t srow = scales + (uint32_t)lrow * spitch + (uint32_t)(c * 2 + ph * cpp * 8);
+                const uint32_t brow = stage + (uint32_t)g * rowb + (uint32_t)c * 16;
+#pragma unroll 2
+                for (int j = jl0; j < ((p.dbg & 2) ? jl0 : jl1); ++j) {     // bit 1 = no products
+                    const uint4 ca = lds16u(crow + j * 64), cb = lds16u(crow + 8 * cpitch + j * 64);
+                    const uint32_t sa = lds_u16(srow + j * 8), sb = lds_u16(srow + 8 * spitch + j * 8);
+                    const uint32_t a_w[4] = {ca.x, ca.y, ca.z, ca.w}, b_w[4] = {cb.x, cb.y, cb.z, cb.w};
+                    const uint32_t sA[2] = {lds_u32(lut + (sa & 0xffu) * 4), lds_u32(lut + (sa >> 8) * 4)};
+                    const uint32_t sB[2] = {lds_u32(lut + (sb & 0xffu) * 4), lds_u32(lut + (sb >> 8) * 4)};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t wa = a_w[q], wb = b_w[q], s_a = sA[q >> 1], s_b = sB[q >> 1];
+                        const uint32_t a00 = expand_pair<0>(wa, s_a), a01 = expand_pair<1>(wa, s_a);
+                        const uint32_t a02 = expand_pair<2>(wa, s_a), a03 = expand_pair<3>(wa, s_a);
+                        const uint32_t a80 = expand_pair<0>(wb, s_b), a81 = expand_pair<1>(wb, s_b);
+                        const uint32_t a82 = expand_pair<2>(wb, s_b), a83 = expand_pair<3>(wb, s_b);
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (t < ntiles) {
+                                const uint4 x = lds16u(brow + (uint32_t)(t * 8) * rowb + (uint32_t)(j * 256 + q * 64));
+                                mma_bf16(acc[rg][t], a00, a80, a01, a81, x.x, x.y);
+                                mma_bf16(acc[rg][t], a02, a82, a03, a83, x.z, x.w);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        // the second k half hands its sums to the first
+        if (ks == 1) {
+#pragma unroll
+            for (int rg = 0; rg < RGW; ++rg)
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) red[((rg * 2 + t) * 4 + i) * 256 + rgroup * 32 + lane] = acc[rg][t][i];
+        }
+        __syncthreads();
+        if (ks == 0) {
+#pragma unroll
+            for (int rg = 0; rg < RGW; ++rg)
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int n = t * 8 + c * 2 + (i & 1);
+                        if (n >= n_here) continue;
+                        const int asg = list[pass * kNT + n];
+                        const int row = row0 + rg * kRowsPerCta + rgroup * 16 + g + (i >> 1) * 8;
+                        const float v = acc[rg][t][i] + red[((rg * 2 + t) * 4 + i) * 256 + rgroup * 32 + lane];
+                        float o;
+                        if constexpr (MODE == 0) {
+                            const float a = round_bf(es * v);
+                            o = a * sigmoid_fast(a);
+                        } else {
+                            o = p.gate[asg] * (es * v);
+                        }
+                        p.out[(size_t)asg * p.out_ld + row] = f2bf(o);
+                    }
         }
     }
 }
@@ -278,14 +305,21 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const uint16_t* __r
     stg16(dst, make_uint4(pack_bf2(acc[0], acc[1]), pack_bf2(acc[2], acc[3]), pack_bf2(acc[4], acc[5]), pack_bf2(acc[6], acc[7])));
 }
 
-size_t rows_smem(int kdim, int rgw) {
-    return (size_t)kListBytes + kRedBytes + kLutBytes + (size_t)kRowsPerCta * rgw * ((kdim >> 1) + 64 + (kdim >> 4) + 16) +
-           (size_t)kNT * (kdim * 2 + 64);
+size_t rows_smem(int kdim, int rgw, int kphases) {
+    return (size_t)kListBytes + red_bytes(rgw) + kLutBytes + (size_t)kRowsPerCta * rgw * ((kdim >> 1) + 64 + (kdim >> 4) + 16) +
+           (size_t)kNT * (kdim / kphases * 2 + 64);
+}
+// Fewest staging phases (1, 2 or 4 slices of whole 256-column units) with which the tile fits; 0: none does.
+int pick_phases(int kdim, int rgw) {
+    for (int ph = 1; ph <= 4; ph *= 2)
+        if (kdim % (256 * ph) == 0 && rows_smem(kdim, rgw, ph) <= (size_t)kMaxSmem) return ph;
+    return 0;
 }
 
 template <int MODE, int RGW>
-cudaError_t launch_rows_t(const Fp4RowsArgs& a, int experts, cudaStream_t s) {
-    const size_t smem = rows_smem(a.kdim, RGW);
+cudaError_t launch_rows_t(Fp4RowsArgs a, int experts, cudaStream_t s) {
+    a.kphases = pick_phases(a.kdim, RGW);
+    const size_t smem = rows_smem(a.kdim, RGW, a.kphases);
     cudaError_t e = cudaFuncSetAttribute(fp4_rows_kernel<MODE, RGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     return launch_pdl(fp4_rows_kernel<MODE, RGW>, dim3(a.rows / (kRowsPerCta * RGW), experts), dim3(kThreads), smem, s, a);
@@ -296,7 +330,7 @@ cudaError_t launch_rows_t(const Fp4RowsArgs& a, int experts, cudaStream_t s) {
 // A block covers 256 weight rows when the tile fits in shared memory and that still gives about one block per SM,
 // else 128 (TMT_MOE_FP4_ROW_GROUPS = 1 / 2 forces the choice where the shape allows it).
 cudaError_t launch_fp4_rows(const Fp4RowsArgs& a, int experts, int mode, cudaStream_t s) {
-    const bool two_ok = a.rows % (2 * kRowsPerCta) == 0 && rows_smem(a.kdim, 2) <= (size_t)kMaxSmem;
+    const bool two_ok = a.rows % (2 * kRowsPerCta) == 0 && pick_phases(a.kdim, 2) == 1;
     int rgw = two_ok && (long)(a.rows / (2 * kRowsPerCta)) * experts >= 120 ? 2 : 1;
     if (const char* f = getenv("TMT_MOE_FP4_ROW_GROUPS")) if (*f == '1' || (*f == '2' && two_ok)) rgw = *f - '0';
     if (mode == 0) return rgw == 2 ? launch_rows_t<0, 2>(a, experts, s) : launch_rows_t<0, 1>(a, experts, s);
@@ -309,7 +343,7 @@ cudaError_t launch_decode_combine(const uint16_t* Ya, uint16_t* Y, float beta, i
 }
 
 bool fp4_rows_shape_ok(int rows, int kdim) {
-    return rows % kRowsPerCta == 0 && kdim % 256 == 0 && rows_smem(kdim, 1) <= (size_t)kMaxSmem;
+    return rows % kRowsPerCta == 0 && kdim % 256 == 0 && pick_phases(kdim, 1) > 0;
 }
 
 }  // namespace tmt
