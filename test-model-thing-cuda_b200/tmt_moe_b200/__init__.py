@@ -210,7 +210,14 @@ class MoE:
             for i, (p, s, ts, r, c) in enumerate(ws):
                 a[i] = Nvfp4Weight(_ptr(p), _ptr(s), ts, r, c)
             return a
-        _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), arr(Wup), arr(Wdown), _ptr(Y),
+        # a sampler calls this once per byte with the same weight lists: the descriptor arrays are built once per pair of
+        # lists (the lists themselves are kept alive by the cache entry)
+        key = (id(Wup), id(Wdown))
+        hit = getattr(self, "_nvfp4_desc", None)
+        if hit is None or hit[0] != key or hit[1] is not Wup or hit[2] is not Wdown:
+            hit = (key, Wup, Wdown, arr(Wup), arr(Wdown))
+            self._nvfp4_desc = hit
+        _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), hit[3], hit[4], _ptr(Y),
                                               ctypes.c_float(beta), t), self.lib)
 
     def ep_init_torch(self, dist):
