@@ -115,3 +115,31 @@ def test_small_batch_route_matches_expanded_route(case, row_groups, monkeypatch)
     want = O.bf16_to_f32(ref["Y"]) + case["beta"] * O.bf16_to_f32(Y0)
     assert synth.rel_l2(outs["small_batch"], want) <= 1e-2
     assert synth.rel_l2(outs["small_batch"], outs["expanded"]) <= 3e-3
+
+
+def test_small_batch_route_is_deterministic_and_independent_of_batch_composition():
+    """Same inputs, same bits: across calls, across handles, and for a token whichever other tokens share its step (a
+    column of the expert products depends on its own token only; the token list is built in ascending order)."""
+    import gpu_util as G
+    import tmt_moe_b200 as M
+    T, D, H, E, K = 64, 1024, 2048, 16, 2
+    data, up_q, down_q, up_dq, down_dq, us, ds, keep = _setup(M, G, T, D, H, E, K, 5)
+    X, Wr = G.dev(data["X"]), G.dev(data["Wr"])
+    outs = []
+    for handle in range(2):
+        moe = M.MoE(T, D, E, K, hidden=H, training=False, gemm_impl=2)
+        for _ in range(2):
+            Y = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+            moe.forward_nvfp4(X, Wr, up_q, down_q, Y)
+            torch.cuda.synchronize()
+            assert moe.device_status() == 0
+            outs.append(G.host_u16(Y))
+        moe.close()
+    for o in outs[1:]:
+        np.testing.assert_array_equal(o, outs[0])
+    # the first 20 tokens alone
+    moe = M.MoE(T, D, E, K, hidden=H, training=False, gemm_impl=2)
+    Y = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+    moe.forward_nvfp4(X, Wr, up_q, down_q, Y, tokens=20)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(G.host_u16(Y)[:20], outs[0][:20])
