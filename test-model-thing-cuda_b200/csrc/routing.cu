@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(128) router_logits_small_kernel(const RouterAr
         const bool valid = e < a.E;
         const int er = valid ? e : 0;
         float acc = 0.0f;
-        constexpr int kB = 4;                   // vectors in flight per lane (the chain itself stays sequential)
+        constexpr int kB = 8;                   // vectors in flight per lane (the chain itself stays sequential)
         for (int v0 = s; v0 < nvec; v0 += 8 * kB) {
             uint4 xv[kB], wa[kB], wb[kB];
 #pragma unroll
