@@ -89,15 +89,18 @@ template <int MODE, int RGW>
 __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
     int* list = reinterpret_cast<int*>(smem);                         // assignments of this expert, ascending
-    float* red = reinterpret_cast<float*>(smem + kListBytes);         // [RGW][2][4][256] partial sums of the second k half
     const int kdim = p.kdim;
     constexpr int R = kRowsPerCta * RGW;
     const uint32_t cpitch = (uint32_t)(kdim >> 1) + 64, spitch = (uint32_t)(kdim >> 4) + 16;
     const uint32_t rowb = (uint32_t)(kdim / p.kphases) * 2 + 64;      // staged token row pitch
-    const uint32_t lut = tc::smem_u32(smem) + kListBytes + red_bytes(RGW); // e4m3 byte -> scale * 2^112 as bf16x2
+    // [RGW][2][4][256] partial sums of the second k half: a region of their own, or (red_in_stage: when that is what lets
+    // whole token rows fit) the start of the staged rows, which are dead by the time the sums are exchanged
+    const int redb = p.red_in_stage ? 0 : red_bytes(RGW);
+    const uint32_t lut = tc::smem_u32(smem) + kListBytes + redb;      // e4m3 byte -> scale * 2^112 as bf16x2
     const uint32_t codes = lut + kLutBytes;
     const uint32_t scales = codes + R * cpitch;
     const uint32_t stage = scales + R * spitch;
+    float* red = reinterpret_cast<float*>(p.red_in_stage ? smem + (stage - tc::smem_u32(smem)) : smem + kListBytes);
     __shared__ __align__(8) uint64_t wbar;
     __shared__ int s_cnt, abort_s;
     __shared__ unsigned masks[kDecodeMaxAsg / 32];
@@ -244,6 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
             }
         }
         // the second k half hands its sums to the first
+        if (p.red_in_stage) __syncthreads();                          // every warp has read its last staged row
         if (ks == 1) {
 #pragma unroll
             for (int rg = 0; rg < RGW; ++rg)
@@ -305,8 +309,8 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const uint16_t* __r
     stg16(dst, make_uint4(pack_bf2(acc[0], acc[1]), pack_bf2(acc[2], acc[3]), pack_bf2(acc[4], acc[5]), pack_bf2(acc[6], acc[7])));
 }
 
-size_t rows_smem(int kdim, int rgw, int kphases) {
-    return (size_t)kListBytes + red_bytes(rgw) + kLutBytes + (size_t)kRowsPerCta * rgw * ((kdim >> 1) + 64 + (kdim >> 4) + 16) +
+size_t rows_smem(int kdim, int rgw, int kphases, bool red_in_stage = false) {
+    return (size_t)kListBytes + (red_in_stage ? 0 : red_bytes(rgw)) + kLutBytes + (size_t)kRowsPerCta * rgw * ((kdim >> 1) + 64 + (kdim >> 4) + 16) +
            (size_t)kNT * (kdim / kphases * 2 + 64);
 }
 // Fewest staging phases (1, 2 or 4 slices of whole 256-column units) with which the tile fits; 0: none does.
@@ -319,7 +323,10 @@ int pick_phases(int kdim, int rgw) {
 template <int MODE, int RGW>
 cudaError_t launch_rows_t(Fp4RowsArgs a, int experts, cudaStream_t s) {
     a.kphases = pick_phases(a.kdim, RGW);
-    const size_t smem = rows_smem(a.kdim, RGW, a.kphases);
+    // two slices only because of the exchange buffer: put that buffer into the staged rows and keep the rows whole
+    a.red_in_stage = a.kphases == 2 && rows_smem(a.kdim, RGW, 1, true) <= (size_t)kMaxSmem && !getenv("TMT_MOE_FP4_TWO_SLICES");
+    if (a.red_in_stage) a.kphases = 1;
+    const size_t smem = rows_smem(a.kdim, RGW, a.kphases, a.red_in_stage);
     cudaError_t e = cudaFuncSetAttribute(fp4_rows_kernel<MODE, RGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     return launch_pdl(fp4_rows_kernel<MODE, RGW>, dim3(a.rows / (kRowsPerCta * RGW), experts), dim3(kThreads), smem, s, a);

@@ -17,6 +17,7 @@ struct Fp4RowsArgs {
     const int* idx;                     // [n_asg] expert of each assignment
     const float* gate;                  // [n_asg] gate weights (mode 1)
     int n_asg, rows, kdim;
+    int red_in_stage;                   // set by the launcher: the k-half exchange buffer lives in the staged rows
     int kphases;                        // set by the launcher: the token rows are staged in this many column slices
     int* status;                        // device status word (a bounded wait that ran out is reported there)
     int dbg;                            // measurement only (TMT_MOE_FP4_DEBUG): 1 stop after the list, 2 no products, 4 no staging
