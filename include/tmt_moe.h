@@ -30,21 +30,24 @@ extern "C" {
 typedef struct tmt_moe tmt_moe;
 
 enum { TMT_MOE_BF16 = 0, TMT_MOE_F32 = 1 };
-enum { TMT_MOE_GEMM_TCGEN05 = 0, TMT_MOE_GEMM_SIMT = 1, TMT_MOE_GEMM_TCGEN05_2CTA = 2 };
+/* Grouped GEMM kernel. AUTO (what a zero-initialised descriptor selects) is the fastest one: CTA pairs on 256x256
+ * tiles, expert groups padded to 256 rows. TCGEN05 = one CTA per 128x256 tile (groups padded to 128 rows). SIMT = slow
+ * independent kernel the tests cross-check the tensor-core products with; nothing switches to it at run time. */
+enum { TMT_MOE_GEMM_AUTO = 0, TMT_MOE_GEMM_SIMT = 1, TMT_MOE_GEMM_TCGEN05_2CTA = 2, TMT_MOE_GEMM_TCGEN05 = 3 };
 enum { TMT_MOE_EP_PEER = 0, TMT_MOE_EP_NCCL = 1 };
 
 /* Replaces the (N,E,K,D) arguments of moe_keep_alloc / moe_ws_alloc (moe.cu:330-362) and
  * the config knobs experts=, topk= (tmt-cuda/src/config.h:12). */
 typedef struct tmt_moe_desc {
     int tokens;        /* capacity: most rows (batch*seqlen) one call may carry            */
-    int dim;           /* model width D, multiple of 8                                     */
-    int hidden;        /* expert hidden width H (multiple of 8); 0 = reference mode        */
+    int dim;           /* model width D, multiple of 64 (one TMA box of bf16)              */
+    int hidden;        /* expert hidden width H (multiple of 64); 0 = reference mode       */
     int experts;       /* E >= 1 (no upper bound of 16 as in config.h:51-52; E <= 256)      */
     int topk;          /* 1 <= K <= min(E, 8)                                               */
     int router_dtype;  /* TMT_MOE_BF16 (the reference's work copy, model.cu:513) or _F32    */
     int training;      /* 1: keep what backward needs; 0: forward only                     */
-    int gemm_impl;     /* TMT_MOE_GEMM_TCGEN05 (one CTA per tile), _TCGEN05_2CTA (CTA pairs on 256x256 tiles,
-                          groups padded to 256 rows) or _SIMT (slow cross-check kernel)            */
+    int gemm_impl;     /* TMT_MOE_GEMM_AUTO (= _TCGEN05_2CTA: CTA pairs on 256x256 tiles, groups padded to 256
+                          rows), _TCGEN05 (one CTA per tile) or _SIMT (slow cross-check kernel)               */
     int device;        /* CUDA device ordinal                                              */
     int host_io;       /* 1: also allocate staging for the *_host entry points             */
     void* stream;      /* cudaStream_t all work is queued on; NULL = legacy default stream  */
@@ -195,6 +198,11 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128);
  * s's rows start inside local group le. Returns the expert-side row count, -1 on bad arguments. */
 long long tmt_moe_ep_plan(int G, int r, int E, int pad, const int* cnt_all, int* tok_poff, int* x_counts,
                           int* x_poff, int* src_off);
+/* The capacity check every rank runs on the all-gathered counts before any row moves (host arithmetic, exported
+ * for CPU tests): -1 when the padded expert-side rows of every rank fit into x_cap rows, otherwise the lowest rank
+ * that overflows (its row count in *rows_out, may be NULL); -2 on bad arguments. Same input on every rank, hence
+ * the same verdict: a step that overflows one rank fails on all ranks together, with both transports. */
+int tmt_moe_ep_check_capacity(int G, int E, int pad, const int* cnt_all, long long x_cap, long long* rows_out);
 
 /* ---- entry point that allocates nothing (no counterpart in the reference) ---------------
  * dWrouter[e, d] = sum_t bf16(dlogits[t, e]) * X[t, d], the router_dw phase of

@@ -4,6 +4,15 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Measurement switches (kernel phases turned off one at a time, results are then wrong) exist only in builds made with
+// -DTMT_MOE_MEASURE; in the product build every test of them is the constant 0 and the environment variables that set
+// them are not read.
+#ifdef TMT_MOE_MEASURE
+#define TMT_DBG(p, bit) ((p).dbg & (bit))
+#else
+#define TMT_DBG(p, bit) 0
+#endif
+
 namespace tmt {
 
 // Rows of one GEMM row tile and unit of every tile table. Expert groups start on a multiple of the

@@ -164,6 +164,27 @@ long long tmt_moe_ep_plan(int G, int r, int E, int pad, const int* cnt_all, int*
     return xp;
 }
 
+// Every rank's expert-side row count against the capacity, from the all-gathered counts that every rank holds:
+// all ranks reach the same verdict for a step, so an overloaded rank never leaves its peers waiting in an exchange.
+// Returns -1 when every rank fits, otherwise the lowest rank that does not (its row count in *rows_out); -2 on bad arguments.
+int tmt_moe_ep_check_capacity(int G, int E, int pad, const int* cnt_all, long long x_cap, long long* rows_out) {
+    if (G < 1 || E < 1 || E % G || pad < 1 || !cnt_all) return -2;
+    const int EL = E / G;
+    for (int g = 0; g < G; ++g) {
+        long long rows = 0;
+        for (int le = 0; le < EL; ++le) {
+            long long n = 0;
+            for (int s = 0; s < G; ++s) n += cnt_all[(size_t)s * E + g * EL + le];
+            rows += (n + pad - 1) / pad * pad;
+        }
+        if (rows > x_cap || rows > 0x7fffffffLL) {
+            if (rows_out) *rows_out = rows;
+            return g;
+        }
+    }
+    return -1;
+}
+
 int tmt_moe_ep_unique_id(void* id128) {
     try {
         if (!id128) throw std::runtime_error("null argument");
@@ -291,11 +312,16 @@ void plan_step(tmt_moe* h) {
     NC(ep, ep->AllGather(h->rb.counts, ep->cnt_all_dev, E, ncclInt32, ep->comm, h->stream));
     CKE(cudaMemcpyAsync(ep->cnt_all.data(), ep->cnt_all_dev, (size_t)G * E * sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     CKE(cudaStreamSynchronize(h->stream));
+    // Both transports: the verdict is the same on every rank (same cnt_all), so all of them refuse the step together,
+    // before any row moves; no rank is left waiting for a partner that threw.
+    long long over_rows = 0;
+    const int over = tmt_moe_ep_check_capacity(G, E, h->pad, ep->cnt_all.data(), ep->x_cap, &over_rows);
+    if (over != -1)
+        throw std::runtime_error("expert-side capacity exceeded on rank " + std::to_string(over) + ": " + std::to_string(over_rows) +
+                                 " rows routed to it, room for " + std::to_string(ep->x_cap) + " (raise desc.ep_capacity_factor)");
     const long long rows = tmt_moe_ep_plan(G, ep->r, E, h->pad, ep->cnt_all.data(), ep->tok_poff.data(), ep->x_counts.data(),
                                            ep->x_poff.data(), ep->src_off.data());
-    if (rows < 0 || rows > ep->x_cap)
-        throw std::runtime_error("expert-side capacity exceeded: " + std::to_string(rows) + " rows routed to this rank, room for " +
-                                 std::to_string(ep->x_cap) + " (raise desc.ep_capacity_factor)");
+    if (rows < 0) throw std::runtime_error("exchange plan failed");
     int* t = ep->x_tables_host.data();
     memcpy(t, ep->x_poff.data(), (EL + 1) * sizeof(int));
     memcpy(t + EL + 1, ep->x_counts.data(), EL * sizeof(int));
@@ -309,10 +335,7 @@ void plan_step(tmt_moe* h) {
         // where this rank's rows start inside the owner's group: the owner's plan, computed here as well
         std::vector<int> o_tok(E + 1), o_cnt(EL), o_poff(EL + 1), o_src((size_t)G * EL);
         for (int g = 0; g < G; ++g) {
-            const long long orow = tmt_moe_ep_plan(G, g, E, h->pad, ep->cnt_all.data(), o_tok.data(), o_cnt.data(), o_poff.data(), o_src.data());
-            if (orow < 0 || orow > ep->x_cap)
-                throw std::runtime_error("expert-side capacity exceeded on rank " + std::to_string(g) + ": " + std::to_string(orow) +
-                                         " rows, room for " + std::to_string(ep->x_cap) + " (raise desc.ep_capacity_factor)");
+            tmt_moe_ep_plan(G, g, E, h->pad, ep->cnt_all.data(), o_tok.data(), o_cnt.data(), o_poff.data(), o_src.data());
             for (int le = 0; le < EL; ++le) ep->dest_row0_host[g * EL + le] = o_poff[le] + o_src[(size_t)ep->r * EL + le];
         }
         CKE(cudaMemcpyAsync(ep->dest_row0, ep->dest_row0_host.data(), E * sizeof(int), cudaMemcpyHostToDevice, h->stream));

@@ -146,7 +146,7 @@ __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s,
         // double-buffered: the store of the previous chunk has read its buffer before anyone writes the next chunk there
         if (!two && s.issuer) bulk_wait_read<0>();
         if (!epi_group_sync(s, p.status)) return false;
-        if (s.issuer && !(p.dbg & 4)) {
+        if (s.issuer && !TMT_DBG(p, 4)) {
             tma_store_2d(m0, b0, ccol0, row0);
             if (two) tma_store_2d(m1, b1, ccol0, row0);
             bulk_commit();
@@ -163,7 +163,7 @@ template <int EPI, int GROUPS>
 __device__ __forceinline__ bool epi_drain_tile(const GemmParams& p, EpiState& s, int expert, int row0, int tcol0, int nkb,
                                                uint32_t tm, bool row_ok) {
     using namespace tc;
-    if (p.dbg & 16) return true;           // measurement only: no epilogue work at all
+    if (TMT_DBG(p, 16)) return true;           // measurement only: no epilogue work at all
     constexpr int kWarpCols = kBN / GROUPS;
     const int r_in_tile = s.quarter * 32 + s.lane;
     const long row = (long)row0 + r_in_tile;
@@ -198,7 +198,7 @@ __device__ __forceinline__ bool epi_drain_tile(const GemmParams& p, EpiState& s,
                             __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
             fence_async_smem();
             if (!epi_group_sync(s, p.status)) return false;
-            if (s.issuer && !(p.dbg & 4)) {
+            if (s.issuer && !TMT_DBG(p, 4)) {
                 tma_store_2d(m0, b0, ccol0, row0);
                 bulk_commit();
             }
@@ -216,7 +216,7 @@ __device__ __forceinline__ bool epi_drain_tile(const GemmParams& p, EpiState& s,
 #pragma unroll
                 for (int i = 0; i < kChunk; ++i) v[i] = 0.0f;
             }
-            if (row_ok && !(p.dbg & 4)) epilogue_chunk<EPI>(p, expert, row, col0, v, sw);
+            if (row_ok && !TMT_DBG(p, 4)) epilogue_chunk<EPI>(p, expert, row, col0, v, sw);
         }
     }
     if (EPI == kEpiDh && row_ok && tcol0 + s.half * kEpiCols < p.N)

@@ -136,13 +136,13 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
                     if (prof) t0 = clock64();
                     ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status);
                     if (prof) t1 = clock64();
-                    if (ok) mbar_expect_tx(fb, (p.dbg & 1) ? 0u : p.tx_bytes);
+                    if (ok) mbar_expect_tx(fb, TMT_DBG(p, 1) ? 0u : p.tx_bytes);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 const uint32_t sa = tiles_s + s * kStageBytes, sb = sa + kATile;
                 const int k0 = (ti.kb0 + kb) * kBK;
-                if (!(p.dbg & 1)) {
+                if (!TMT_DBG(p, 1)) {
                     if (lane == 0) {
                         if (p.a_mn) tma_load_3d(sa, ma, fb, 0, k0, ti.row0 >> 6);        // 2 blocks of 64 m x 64 k
                         else tma_load_2d(sa, ma, fb, k0, ti.row0);                       // 64 k x 128 rows
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
             const uint32_t d_tmem = tmem_base + acc * kBN;
             for (int kb = 0; kb < ti.nkb; ++kb) {
                 if (prof) t0 = clock64();
-                if (!(s & 1) && !(p.dbg & 64)) {          // both stages of the pair (s, s+1) have landed once this barrier completes
+                if (!(s & 1) && !TMT_DBG(p, 64)) {          // both stages of the pair (s, s+1) have landed once this barrier completes
                     ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status));
                     if (!ok) break;
                     tc_fence_after();
@@ -212,8 +212,8 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
-                        if (!(p.dbg & 2)) tc_mma(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
-                    if (!(p.dbg & 128)) tc_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs have read it
+                        if (!TMT_DBG(p, 2)) tc_mma(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                    if (!TMT_DBG(p, 128)) tc_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs have read it
                 }
                 __syncwarp();
                 if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
         es.quarter = warp & 3;                  // TMEM lanes [32*quarter, 32*quarter+32)
         es.half = (warp - 2) >> 2;
         es.lane = lane;
-        es.staged = p.mapC0 != nullptr && !(p.dbg & 8);     // bit 3 of the measurement switches: per-thread-row global stores
+        es.staged = p.mapC0 != nullptr && !TMT_DBG(p, 8);     // bit 3 of the measurement switches: per-thread-row global stores
         es.issuer = ((warp - 2) & 3) == 0 && lane == 0;     // one thread per group issues the TMA stores
         es.cbuf = tiles_s + kStages * kStageBytes;          // two staging buffers of kStagingBytes
         es.gbar = smem_u32(&group_bar[es.half]);
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_kernel(c
             if (!get_tile(p, t, m_tiles, n_tiles, ti)) break;
             if (prof) t0 = clock64();
             bool ok = true;
-            if (!(p.dbg & 32) || lane == 0) ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);   // bit 5: one lane per warp waits
+            if (!TMT_DBG(p, 32) || lane == 0) ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);   // bit 5: one lane per warp waits
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (prof) t1 = clock64();

@@ -186,13 +186,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                     if (prof) t0 = clock64();
                     ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status);
                     if (prof) t1 = clock64();
-                    if (ok && leader) mbar_expect_tx(fb_local, (p.dbg & 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
+                    if (ok && leader) mbar_expect_tx(fb_local, TMT_DBG(p, 1) ? 0u : 2 * p.tx_bytes);      // both CTAs' bytes
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 const uint32_t sa = tiles_s + s * kStageBytes2, sb = sa + kATile2;
                 const int k0 = (ti.kb0 + kb) * kBK;
-                if (!(p.dbg & 1)) {
+                if (!TMT_DBG(p, 1)) {
                     if (lane == 0) {
                         if (p.a_mn) tma_load_3d_pair(sa, ma, fb, 0, k0, ti.row0 >> 6);
                         else tma_load_2d_pair(sa, ma, fb, k0, ti.row0);
@@ -249,7 +249,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int kb = 0; kb < ti.nkb; ++kb) {
                     if (prof) t0 = clock64();
-                    if (!(s & 1) && !(p.dbg & 64)) {          // both stages of the pair (s, s+1), in both CTAs, have landed once this barrier completes
+                    if (!(s & 1) && !TMT_DBG(p, 64)) {          // both stages of the pair (s, s+1), in both CTAs, have landed once this barrier completes
                         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s >> 1]), ph, abort_flag, p.status));
                         if (!ok) break;
                         tc_fence_after();
@@ -260,8 +260,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                     if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < kBK / 16; ++k)
-                            if (!(p.dbg & 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
-                        if (!(p.dbg & 128)) tc_commit_pair(smem_u32(&empty_bar[s]));    // releases stage s in both CTAs
+                            if (!TMT_DBG(p, 2)) tc_mma_pair(d_tmem, da + (uint64_t)(k * a_kstep), db + (uint64_t)(k * b_kstep), idesc, (kb | k) != 0);
+                        if (!TMT_DBG(p, 128)) tc_commit_pair(smem_u32(&empty_bar[s]));    // releases stage s in both CTAs
                     }
                     __syncwarp();
                     if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
@@ -291,7 +291,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
         es.quarter = warp & 3;                  // TMEM lanes [32*quarter, 32*quarter+32)
         es.half = (warp - 2) >> 2;
         es.lane = lane;
-        es.staged = p.mapC0 != nullptr && !(p.dbg & 8);
+        es.staged = p.mapC0 != nullptr && !TMT_DBG(p, 8);
         es.issuer = ((warp - 2) & 3) == 0 && lane == 0;
         es.cbuf = tiles_s + kStages2 * kStageBytes2;
         es.gbar = smem_u32(&group_bar[es.half]);
@@ -304,7 +304,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
             if (!get_tile2(p, t, m_pairs, n_tiles, rank, ti)) break;
             if (prof) t0 = clock64();
             bool ok = true;
-            if (!(p.dbg & 32) || lane == 0) ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);   // bit 5: one lane per warp waits
+            if (!TMT_DBG(p, 32) || lane == 0) ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, p.status);   // bit 5: one lane per warp waits
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (prof) t1 = clock64();

@@ -589,10 +589,12 @@ tmt_moe* create_impl(const tmt_moe_desc* dsc) {
     h->num_sms = prop.multiProcessorCount;
     h->local_experts = d.experts / d.ep_world;
     const int T = d.tokens, E = d.experts, K = d.topk, D = d.dim, H = d.hidden;
-    if (d.gemm_impl < 0 || d.gemm_impl > 2) throw std::runtime_error("unknown gemm_impl");
+    if (d.gemm_impl < 0 || d.gemm_impl > 3) throw std::runtime_error("unknown gemm_impl");
     h->tensor_core = d.gemm_impl != TMT_MOE_GEMM_SIMT;
-    h->two_cta = d.gemm_impl == TMT_MOE_GEMM_TCGEN05_2CTA;
-    if (const char* dbg = getenv("TMT_MOE_GEMM_DEBUG")) h->gemm_dbg = atoi(dbg);     // measurement only, results are then wrong
+    h->two_cta = d.gemm_impl == TMT_MOE_GEMM_TCGEN05_2CTA || d.gemm_impl == TMT_MOE_GEMM_AUTO;
+#ifdef TMT_MOE_MEASURE
+    if (const char* dbg = getenv("TMT_MOE_GEMM_DEBUG")) h->gemm_dbg = atoi(dbg);     // measurement builds only: results are then wrong
+#endif
     if (const char* cyc = getenv("TMT_MOE_GEMM_CYCLES"))                               // measurement only: per-role cycle counters
         if (atoi(cyc) && h->num_sms <= kGemmCycCtas) h->gemm_cyc = dalloc<long long>(h, (size_t)kGemmCycLaunches * kGemmCycCtas * kCycSlots);
     h->pad = h->two_cta ? 2 * kPad : kPad;
@@ -896,14 +898,15 @@ long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes
         else if (s == "tok_of_slot") { src = h->rb.tok_of_slot; n = (size_t)h->dims.cap * 4; }
         else if (s == "tile_expert") { src = h->rb.tile_expert; n = (size_t)h->dims.max_tiles * 4; }
         else if (s == "num_m_tiles") { src = h->rb.num_m_tiles; n = 4; }
-        // grouped activations, all cap rows (debugging / cross-checks; cap comes from "cap")
+        // grouped activations, all gcap rows: the rows of the grouped GEMM buffers ("gcap"; equal to "cap" on one GPU)
         else if (s == "Xg") { src = h->Xg; n = (size_t)h->gcap * h->d.dim * 2; }
         else if (s == "Yg") { src = h->Yg; n = (size_t)h->gcap * h->d.dim * 2; }
         else if (s == "dYg") { src = h->d.training ? h->dYg : nullptr; n = (size_t)h->gcap * h->d.dim * 2; }
         else if (s == "dXg") { src = h->dXg; n = (size_t)h->gcap * h->d.dim * 2; }
-        else if (s == "P") { src = h->P; n = (size_t)h->dims.cap * h->d.hidden * 2; }
-        else if (s == "Hact") { src = h->Hact; n = (size_t)h->dims.cap * h->d.hidden * 2; }
-        else if (s == "dP") { src = h->d.training ? h->dP : nullptr; n = (size_t)h->dims.cap * h->d.hidden * 2; }
+        else if (s == "gcap") { n = 4; int gc = (int)h->gcap; if (dst_bytes < 4) throw std::runtime_error("destination too small"); memcpy(dst, &gc, 4); return 4; }
+        else if (s == "P") { src = h->P; n = (size_t)h->gcap * h->d.hidden * 2; }
+        else if (s == "Hact") { src = h->Hact; n = (size_t)h->gcap * h->d.hidden * 2; }
+        else if (s == "dP") { src = h->d.training ? h->dP : nullptr; n = (size_t)h->gcap * h->d.hidden * 2; }
         else if (s == "sw_part") { src = h->sw_part; n = (size_t)h->gcap * h->sw_ld * 4; }
         else throw std::runtime_error("unknown tensor name: " + s);
         if (!src) throw std::runtime_error("tensor not kept by this handle: " + s);

@@ -170,16 +170,18 @@ void forward_small(tmt_moe* h, const uint16_t* X, const void* Wr, const tmt_nvfp
     up.out = h->Hact; up.out_ld = H;
     up.idx = h->rb.idx; up.gate = h->rb.w; up.n_asg = tokens * K; up.rows = H; up.kdim = D;
     up.status = h->rb.status;
-    const char* dbg = getenv("TMT_MOE_FP4_DEBUG");
+#ifdef TMT_MOE_MEASURE
+    const char* dbg = getenv("TMT_MOE_FP4_DEBUG");            // measurement builds only: results are then wrong
     up.dbg = dbg && *dbg ? atoi(dbg) : 0;
+#endif
     prof_mark(h, kPhGemmUp);
-    if (!(up.dbg & 8)) CKQ(launch_fp4_rows(up, E, 0, h->stream));        // 8: measurement only, no expert products at all
+    if (!TMT_DBG(up, 8)) CKQ(launch_fp4_rows(up, E, 0, h->stream));        // 8: measurement only, no expert products at all
     Fp4RowsArgs down = up;
     down.packed = tab + 2 * E; down.scales = tab + 3 * E; down.es = es + E;
     down.src = h->Hact; down.src_ld = H; down.src_div = 1;
     down.out = h->Yg; down.out_ld = D; down.rows = D; down.kdim = H;
     prof_mark(h, kPhGemmDown);
-    if (!(up.dbg & 8)) CKQ(launch_fp4_rows(down, E, 1, h->stream));
+    if (!TMT_DBG(up, 8)) CKQ(launch_fp4_rows(down, E, 1, h->stream));
     prof_mark(h, kPhCombine);
     CKQ(launch_decode_combine(h->Yg, Y, beta, tokens, D, K, h->stream));
     prof_mark(h, -1);

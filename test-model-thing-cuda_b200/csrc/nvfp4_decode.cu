@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
         if (lane == 31) s_cnt = incl;
     }
     __syncthreads();
-    const int cnt = (p.dbg & 1) ? 0 : s_cnt;      // measurement only: bit 0 = stop after the token list
+    const int cnt = TMT_DBG(p, 1) ? 0 : s_cnt;      // measurement only: bit 0 = stop after the token list
     if (cnt == 0) {                                // nothing to do, but the copies must have landed before the block may leave
         tc::mbar_wait(tc::smem_u32(&wbar), 0, &abort_s, p.status);
         return;
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
             if (pass + ph > 0) __syncthreads();                       // everyone has left the rows staged before
             // rows of the pass -> shared memory, permuted; kSB 16-byte loads in flight per thread. Columns past n_here
             // stay as they are: a column of the product depends on nothing but its own token.
-            for (int n0 = sub; n0 < ((p.dbg & 4) ? 0 : n_here); n0 += kSB * rows_per_iter) {    // bit 2 = no staging
+            for (int n0 = sub; n0 < (TMT_DBG(p, 4) ? 0 : n_here); n0 += kSB * rows_per_iter) {    // bit 2 = no staging
                 for (int v = v0; v < pieces_per_row; v += lanes_per_row) {
                     uint4 x[kSB];
 #pragma unroll
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp4_rows_kernel(const Fp4RowsArgs
                 const uint32_t srow = scales + (uint32_t)lrow * spitch + (uint32_t)(c * 2 + ph * cpp * 8);
                 const uint32_t brow = stage + (uint32_t)g * rowb + (uint32_t)c * 16;
 #pragma unroll 2
-                for (int j = jl0; j < ((p.dbg & 2) ? jl0 : jl1); ++j) {     // bit 1 = no products
+                for (int j = jl0; j < (TMT_DBG(p, 2) ? jl0 : jl1); ++j) {     // bit 1 = no products
                     const uint4 ca = lds16u(crow + j * 64), cb = lds16u(crow + 8 * cpitch + j * 64);
                     const uint32_t sa = lds_u16(srow + j * 8), sb = lds_u16(srow + 8 * spitch + j * 8);
                     const uint32_t a_w[4] = {ca.x, ca.y, ca.z, ca.w}, b_w[4] = {cb.x, cb.y, cb.z, cb.w};

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "common.cuh"
+
 namespace tmt {
 
 constexpr int kDecodeMaxAsg = 1024;     // tokens * topk the small-batch route accepts

@@ -46,7 +46,7 @@ inline void moe_keep_alloc(MoeKeep& k, int N, int E, int K, int D, int hidden = 
     tmt_moe_desc d{};
     d.tokens = N; d.dim = D; d.hidden = hidden; d.experts = E; d.topk = K;
     d.router_dtype = TMT_MOE_BF16;        // the reference passes the bf16 work copy (model.cu:513)
-    d.training = 1; d.gemm_impl = TMT_MOE_GEMM_TCGEN05;
+    d.training = 1; d.gemm_impl = TMT_MOE_GEMM_AUTO;
     int dev = 0;
     cudaGetDevice(&dev);
     d.device = dev; d.host_io = 0; d.stream = stream; d.ep_world = 1; d.ep_rank = 0; d.ep_capacity_factor = 0; d.ep_transport = 0;

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtmt_moe_b200.so")
 
 BF16, F32 = 0, 1
-GEMM_TCGEN05, GEMM_SIMT, GEMM_TCGEN05_2CTA = 0, 1, 2
+GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05_2CTA, GEMM_TCGEN05 = 0, 1, 2, 3
 EP_PEER, EP_NCCL = 0, 1
 
 EXPORTS = (
@@ -29,6 +29,7 @@ EXPORTS = (
     "tmt_moe_debug_gemm_cycles", "tmt_moe_step_host_async", "tmt_moe_host_wait",
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
     "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes", "tmt_moe_usage",
+    "tmt_moe_ep_check_capacity",
 )
 
 
@@ -104,7 +105,7 @@ class MoE:
     """One MoE layer's state (the reference's MoeKeep + MoeWs)."""
 
     def __init__(self, tokens, dim, experts, topk, hidden=0, router_dtype=BF16, training=True,
-                 gemm_impl=GEMM_TCGEN05, device=0, host_io=False, stream=None, ep_world=1, ep_rank=0,
+                 gemm_impl=GEMM_AUTO, device=0, host_io=False, stream=None, ep_world=1, ep_rank=0,
                  ep_capacity_factor=0.0, ep_transport=0):
         self.lib = load()
         self.desc = Desc(tokens, dim, hidden, experts, topk, router_dtype, int(training), gemm_impl, device,
@@ -112,7 +113,7 @@ class MoE:
         self.h = ctypes.c_void_p()
         _check(self.lib.tmt_moe_create(ctypes.byref(self.desc), ctypes.byref(self.h)), self.lib)
         self.tokens, self.dim, self.hidden, self.experts, self.topk = tokens, dim, hidden, experts, topk
-        self.pad = 256 if gemm_impl == GEMM_TCGEN05_2CTA else 128      # rows every expert group is padded to
+        self.pad = 256 if gemm_impl in (GEMM_AUTO, GEMM_TCGEN05_2CTA) else 128      # rows every expert group is padded to
         self._keep = None
 
     def close(self):
@@ -187,12 +188,15 @@ class MoE:
             cap = np.zeros(1, np.int32)
             self.lib.tmt_moe_read(self.h, b"cap", _ptr(cap), ctypes.c_size_t(4))
             cap = int(cap[0])
+            gcap = np.zeros(1, np.int32)              # rows of the grouped GEMM buffers (differs from cap under expert parallelism)
+            self.lib.tmt_moe_read(self.h, b"gcap", _ptr(gcap), ctypes.c_size_t(4))
+            gcap = int(gcap[0])
             D, H = self.dim, self.hidden
             shapes.update({"slotw": ((cap,), np.float32), "tok_of_slot": ((cap,), np.int32),
                            "tile_expert": ((cap // 128,), np.int32), "num_m_tiles": ((1,), np.int32),
-                           "Xg": ((cap, D), np.uint16), "Yg": ((cap, D), np.uint16), "dYg": ((cap, D), np.uint16),
-                           "dXg": ((cap, D), np.uint16), "P": ((cap, H), np.uint16), "Hact": ((cap, H), np.uint16),
-                           "dP": ((cap, H), np.uint16), "sw_part": ((cap, (H + 127) // 128), np.float32)})
+                           "Xg": ((gcap, D), np.uint16), "Yg": ((gcap, D), np.uint16), "dYg": ((gcap, D), np.uint16),
+                           "dXg": ((gcap, D), np.uint16), "P": ((gcap, H), np.uint16), "Hact": ((gcap, H), np.uint16),
+                           "dP": ((gcap, H), np.uint16), "sw_part": ((gcap, (H + 127) // 128), np.float32)})
         shape, dt = shapes[name]
         out = np.empty(shape, dt)
         n = self.lib.tmt_moe_read(self.h, name.encode(), _ptr(out), ctypes.c_size_t(out.nbytes))

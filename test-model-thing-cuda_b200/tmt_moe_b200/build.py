@@ -10,6 +10,8 @@ LIB = os.path.join(HERE, "libtmt_moe_b200.so")
 OBJ = os.path.join(HERE, "build")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+if os.environ.get("TMT_MOE_MEASURE"):       # measurement build: compiles the kernels' phase switches in (results can be wrong)
+    FLAGS.append("-DTMT_MOE_MEASURE")
 
 
 def sources():

@@ -130,6 +130,76 @@ def test_plan_rejects_bad_arguments():
     assert lib.tmt_moe_ep_plan(2, 2, 4, 128, p, p, p, p, p) == -1     # rank out of range
 
 
+def _overflow_worker(rank, world, port, q):
+    """Every rank routes its own tokens with a bias that sends almost everything to rank 0's experts, gathers the
+    counts and runs the library's capacity check: all ranks must name the same overloaded rank and row count."""
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import synth
+        import tmt_moe_b200 as M
+        from oracle import oracle as O
+        lib = M.load()
+        T, D, E, K = 256, 64, 6, 2
+        d = synth.make(T, D, 0, E, K, seed=90 + rank, router_std=0.3)
+        d["Wr"] = synth.make(T, D, 0, E, K, seed=90, router_std=0.3)["Wr"]
+        bias = np.array([40, 40] + [0] * (E - 2), np.float32)        # experts 0 and 1 (rank 0 at any world size here) take every token
+        rt = O.router(d["X"], d["Wr"], K, bias=bias)
+        counts = O.layout(rt["idx"], E, PAD)[0]
+        gathered = [torch.zeros(E, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(counts.astype(np.int32)))
+        cnt_all = np.ascontiguousarray(torch.stack(gathered).numpy(), np.int32)
+        p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        # the capacity of a handle created with ep_capacity_factor = 1.0: roundup(T*K, pad) + pad * local experts
+        EL = E // world
+        x_cap = (T * K + PAD - 1) // PAD * PAD + PAD * EL
+        rows = ctypes.c_longlong(-1)
+        bad = lib.tmt_moe_ep_check_capacity(world, E, PAD, p(cnt_all), ctypes.c_longlong(x_cap), ctypes.byref(rows))
+        roomy = lib.tmt_moe_ep_check_capacity(world, E, PAD, p(cnt_all), ctypes.c_longlong(world * T * K + PAD * EL), None)
+        q.put((rank, "ok", int(bad), int(rows.value), int(roomy)))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAIL: %s\n%s" % (exc, traceback.format_exc()), 0, 0, 0))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_capacity_overflow_is_seen_by_every_rank(world):
+    """A step that routes more rows to one rank than it has room for: every rank reaches the same verdict from the
+    gathered counts (with either transport the step is refused everywhere, before any row moves)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29100 + os.getpid() % 400 + world
+    procs = [ctx.Process(target=_overflow_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg, bad, rows, roomy in res:
+        assert msg == "ok", "rank %d: %s" % (rank, msg)
+    verdicts = {(bad, rows, roomy) for _, _, bad, rows, roomy in res}
+    assert len(verdicts) == 1, res                      # the same on every rank
+    bad, rows, roomy = verdicts.pop()
+    assert bad == 0 and rows == world * 256 * 2 and roomy == -1     # everything went to rank 0's two experts (multiples of 128)
+
+
+def test_capacity_check_arguments():
+    sys.path[:0] = [os.path.join(ROOT, "test-model-thing-cuda_b200")]
+    import tmt_moe_b200 as M
+    lib = M.load()
+    cnt = np.array([[130, 0, 1, 0], [0, 0, 0, 300]], np.int32)       # 2 ranks, 4 experts
+    p = cnt.ctypes.data_as(ctypes.c_void_p)
+    rows = ctypes.c_longlong(0)
+    assert lib.tmt_moe_ep_check_capacity(2, 4, 128, p, ctypes.c_longlong(256), ctypes.byref(rows)) == 1
+    assert rows.value == 128 + 384                      # rank 1: expert 2 has 1 row -> 128, expert 3 has 300 -> 384
+    assert lib.tmt_moe_ep_check_capacity(2, 4, 128, p, ctypes.c_longlong(512), None) == -1
+    assert lib.tmt_moe_ep_check_capacity(2, 4, 128, p, ctypes.c_longlong(255), ctypes.byref(rows)) == 0 and rows.value == 256
+    assert lib.tmt_moe_ep_check_capacity(2, 5, 128, p, ctypes.c_longlong(512), None) == -2
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_exchange_plan_two_cpu_ranks(world):
     ctx = mp.get_context("spawn")

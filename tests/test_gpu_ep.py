@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q, transport, gemm_impl=0, waves=1):
+def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1):
     try:
         sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TMT_MOE_EP_WAVES=str(waves))
@@ -77,7 +77,7 @@ def _worker(rank, world, port, q, transport, gemm_impl=0, waves=1):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport,gemm_impl,waves", [pytest.param(0, 0, 1, id="peer"), pytest.param(1, 0, 1, id="nccl"),
+@pytest.mark.parametrize("transport,gemm_impl,waves", [pytest.param(0, 3, 1, id="peer"), pytest.param(1, 3, 1, id="nccl"),
                                                        pytest.param(0, 2, 1, id="peer-cta_pairs"), pytest.param(1, 2, 1, id="nccl-cta_pairs"),
                                                        pytest.param(0, 2, 2, id="peer-cta_pairs-two_expert_waves")])
 def test_expert_parallel_two_gpus(transport, gemm_impl, waves):

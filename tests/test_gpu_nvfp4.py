@@ -59,7 +59,7 @@ def _setup(M, G, T, D, H, E, K, seed, tiny_blocks=False):
 # Two routes: steps of a few tokens read the packed weights directly (register-operand MMA); larger steps expand the
 # weights once and run the grouped tcgen05 kernels. TMT_MOE_DECODE_MAX_TOKENS = 0 forces the second route.
 @pytest.mark.parametrize("route", ["small_batch", "expanded"])
-@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
+@pytest.mark.parametrize("impl", [pytest.param(3, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
 def test_forward_nvfp4_decode_shape(impl, route, monkeypatch):
     import gpu_util as G
     import tmt_moe_b200 as M
@@ -104,7 +104,7 @@ def test_small_batch_route_matches_expanded_route(case, row_groups, monkeypatch)
     outs = {}
     for route in ("small_batch", "expanded"):
         monkeypatch.setenv("TMT_MOE_DECODE_MAX_TOKENS", "256" if route == "small_batch" else "0")
-        moe = M.MoE(64, D, E, K, hidden=H, training=False, gemm_impl=0)
+        moe = M.MoE(64, D, E, K, hidden=H, training=False, gemm_impl=3)
         Y = G.dev(Y0.copy())
         moe.forward_nvfp4(X, Wr, up_q, down_q, Y, beta=case["beta"], tokens=T)
         torch.cuda.synchronize()

@@ -28,8 +28,9 @@ def _mods():
     O.build()
 
 
-IMPLS = [pytest.param(0, id="tcgen05"), pytest.param(1, id="simt"), pytest.param(2, id="tcgen05_2cta")]
-PAD = {0: 128, 1: 128, 2: 256}
+# gemm_impl values of include/tmt_moe.h: 0 = AUTO (the CTA-pair kernel), 1 = SIMT cross-check, 2 = CTA pairs, 3 = one CTA per tile
+IMPLS = [pytest.param(3, id="tcgen05"), pytest.param(1, id="simt"), pytest.param(2, id="tcgen05_2cta")]
+PAD = {0: 256, 1: 128, 2: 256, 3: 128}
 OUT_L2, OUT_MAX, GRAD_L2 = 1e-2, 2e-2, 3e-2
 
 
@@ -114,7 +115,7 @@ def test_tie_break_lowest_index():
     G.check_routing(layer, ref)
 
 
-@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
+@pytest.mark.parametrize("impl", [pytest.param(3, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
 def test_topk4_64_experts(impl):
     """Config-5 routing shape at reduced size: 64 experts, top-4, fp32 router."""
     _fwd_bwd(dict(T=1024, D=256, H=256, E=64, K=4, router_f32=True), impl, seed=6, w_std=0.08, router_std=0.1)
@@ -139,7 +140,7 @@ def test_tcgen05_matches_simt_buffers():
     cfg = dict(T=900, D=192, H=448, E=4, K=2)
     data = synth.make(cfg["T"], cfg["D"], cfg["H"], cfg["E"], cfg["K"], seed=8, w_std=0.08)
     got = {}
-    for impl in (0, 1, 2):
+    for impl in (3, 1, 2):
         layer = G.Layer(data, cfg["T"], cfg["D"], cfg["E"], cfg["K"], cfg["H"], gemm_impl=impl)
         layer.forward()
         g = layer.backward(data["dY"], 0.1, 0.001)
@@ -150,7 +151,7 @@ def test_tcgen05_matches_simt_buffers():
                     sw=layer.moe.read("sw_part")[real].sum(1))
         got[impl] = bufs
         assert layer.moe.device_status() == 0
-    for impl in (0, 2):
+    for impl in (3, 2):
         for n in got[impl]:
             assert np.isfinite(got[impl][n]).all(), (impl, n)
             assert synth.rel_l2(got[impl][n], got[1][n]) <= 4e-3, (impl, n)
@@ -162,7 +163,7 @@ def test_config1_full():
     _fwd_bwd(synth.CONFIGS["c1"], 0, seed=11, backward=False)
 
 
-@pytest.mark.parametrize("impl", [pytest.param(0, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
+@pytest.mark.parametrize("impl", [pytest.param(3, id="tcgen05"), pytest.param(2, id="tcgen05_2cta")])
 @pytest.mark.parametrize("name,tokens", [("c2", 1024), ("c4", 2048)])
 def test_training_configs_reduced_tokens(name, tokens, impl):
     """Configs 2 and 4 with their true widths and expert counts on a token subsample the CPU
@@ -221,7 +222,7 @@ def test_host_step_equals_device_path():
     Y = layer.forward(data["Y0"], 1.0).copy()
     g = layer.backward(data["dY"], 0.1, 0.001)
     stat, _, _ = layer.moe.stats()
-    host = M.MoE(cfg["T"], cfg["D"], cfg["E"], cfg["K"], hidden=cfg["H"], host_io=True)
+    host = M.MoE(cfg["T"], cfg["D"], cfg["E"], cfg["K"], hidden=cfg["H"], host_io=True, gemm_impl=M.GEMM_TCGEN05)
     pin = lambda a: torch.from_numpy(a.view(np.int16).copy()).pin_memory()
     hX, hdY, hY = pin(data["X"]), pin(data["dY"]), pin(data["Y0"])
     hdX = torch.zeros_like(hX).pin_memory()
@@ -254,7 +255,7 @@ def test_host_steps_queued_back_to_back():
         Y = layer.forward(None, 0.0).copy()
         g = layer.backward(b["dY"], 0.1, 0.001)
         want.append((Y, g["dX"].copy()))
-    host = M.MoE(cfg["T"], cfg["D"], E, cfg["K"], hidden=cfg["H"], host_io=True)
+    host = M.MoE(cfg["T"], cfg["D"], E, cfg["K"], hidden=cfg["H"], host_io=True, gemm_impl=M.GEMM_TCGEN05)
     pin = lambda a: torch.from_numpy(a.view(np.int16).copy()).pin_memory()
     bufs = [(pin(b["X"]), pin(b["dY"]), torch.zeros(cfg["T"], cfg["D"], dtype=torch.int16).pin_memory(),
              torch.zeros(cfg["T"], cfg["D"], dtype=torch.int16).pin_memory(), torch.zeros(E + 1).pin_memory()) for b in batches]
@@ -337,7 +338,7 @@ def test_per_token_router_and_tiled_router_agree_bitwise(cfg, bias_on, monkeypat
     got = {}
     for flag in ("0", "1"):
         monkeypatch.setenv("TMT_MOE_ROUTER_SMALL", flag)
-        layer = G.Layer(data, T, D, E, K, H, rf, training=False, gemm_impl=0, bias=bias)
+        layer = G.Layer(data, T, D, E, K, H, rf, training=False, gemm_impl=3, bias=bias)
         layer.forward(None, 0.0)
         assert layer.moe.device_status() == 0
         G.check_routing(layer, ref)
