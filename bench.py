@@ -27,7 +27,7 @@ import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for _p in (ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")):
+for _p in (ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200")):
     if _p not in sys.path:
         sys.path.insert(0, _p)
 
@@ -368,7 +368,7 @@ def main():
         if rank != 0:
             return
         import numpy as np
-        import synth
+        from tmt_moe_b200 import synth
         sample = 2048 if cfg.get("nvfp4") else min(cpu_sample_tokens(cfg), 1024 if args.steps + args.warmup > 4 else 1 << 30)
         host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
         if cfg.get("zipf"):
@@ -408,7 +408,7 @@ def main():
                 stream=stream, ep_world=world, ep_rank=rank,
                 ep_transport=M.EP_PEER if args.ep_transport == "peer" else M.EP_NCCL)
     if cfg.get("zipf"):
-        import synth
+        from tmt_moe_b200 import synth
         moe.set_router_bias(synth.zipf_bias(E, 2.0))
     if world > 1:
         moe.ep_init_torch(dist)
@@ -578,7 +578,7 @@ def main():
                     "gemm_tcgen05_2cta_kernel" if args.gemm == "2cta" else "gemm_tcgen05_kernel", gemm_launches),
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 # dram read + write per launch, averaged over the six launches: ncu capture at 32768 tokens scaled to
-                # the full token count (activations x 4, weights fixed), profiles/step_kernels_config5_32k_tokens.md
+                # the full token count (activations x 4, weights fixed)
                 "traffic": 6.1e9 if (args.config == "c5" and not args.tokens and world == 1) else None,
                 "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
                 "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}
@@ -616,7 +616,7 @@ def main():
     if e2e is not None:
         line["e2e"] = e2e
     if world == 1 and not args.no_cpu_baseline:
-        import synth
+        from tmt_moe_b200 import synth
         sample = 2048 if cfg.get("nvfp4") else cpu_sample_tokens(cfg)
         host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
         if cfg.get("zipf"):

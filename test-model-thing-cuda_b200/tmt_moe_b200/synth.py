@@ -3,7 +3,18 @@
 the comparison helpers the parity tests share. bf16 tensors are uint16 bit patterns."""
 import numpy as np
 
-from oracle import oracle as O
+
+class O:
+    """bf16 bit patterns <-> fp32 (round to nearest even), in numpy."""
+
+    @staticmethod
+    def f32_to_bf16(x):
+        u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+    @staticmethod
+    def bf16_to_f32(b):
+        return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 CONFIGS = {
     # name: tokens, dim, hidden, experts, topk, router fp32

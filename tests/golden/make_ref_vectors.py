@@ -2,7 +2,7 @@
 moe_backward (recompiled for sm_100a, oracle/_ref/libtmt_ref.so) on seeded inputs.
 
 Run on a machine with a GPU:  python tests/golden/make_ref_vectors.py [out_dir]
-Inputs are regenerated from the seed by the tests (tests/synth.py), so only outputs are stored.
+Inputs are regenerated from the seed by the tests (tmt_moe_b200/synth.py), so only outputs are stored.
 Cases stay inside what the reference computes correctly (experts <= 4, see oracle/ref_driver.cu)."""
 import os
 import sys
@@ -10,9 +10,9 @@ import sys
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-sys.path[:0] = [ROOT, os.path.join(ROOT, "tests")]
+sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200")]
 
-import synth  # noqa: E402
+from tmt_moe_b200 import synth  # noqa: E402
 from oracle import ref  # noqa: E402
 
 # name: tokens, dim, experts, topk, seed, beta, aux, zcoef, weight std, router std

@@ -67,7 +67,7 @@ def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        import synth
+        from tmt_moe_b200 import synth
         import tmt_moe_b200 as M
         from oracle import oracle as O
         lib = M.load()
@@ -137,7 +137,7 @@ def _overflow_worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        import synth
+        from tmt_moe_b200 import synth
         import tmt_moe_b200 as M
         from oracle import oracle as O
         lib = M.load()

@@ -11,7 +11,7 @@ import sys
 import numpy as np
 import pytest
 
-import synth
+from tmt_moe_b200 import synth
 from oracle import oracle as O
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))

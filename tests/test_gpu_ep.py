@@ -21,7 +21,7 @@ def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1):
         import torch.distributed as dist
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-        import synth
+        from tmt_moe_b200 import synth
         import gpu_util as G
         import tmt_moe_b200 as M
         from oracle import oracle as O

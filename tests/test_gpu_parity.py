@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-import synth
+from tmt_moe_b200 import synth
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu

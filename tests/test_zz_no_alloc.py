@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-import synth
+from tmt_moe_b200 import synth
 
 pytestmark = pytest.mark.gpu
 
