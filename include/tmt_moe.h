@@ -180,10 +180,16 @@ int tmt_moe_quantize_nvfp4(const void* W_bf16, int rows, int cols, void* packed,
  * packed / scales pointers, dim and hidden multiples of 256: the expert products read the packed
  * weights in place, so these must stay valid while the handle uses them. Larger steps expand the
  * weights once into scratch owned by the handle. Same numerics on both routes; the environment
- * variable TMT_MOE_DECODE_MAX_TOKENS moves the switch point (0: always expand). */
+ * variable TMT_MOE_DECODE_MAX_TOKENS moves the switch point (0: always expand).
+ * The expansion is reused while the descriptors name the same pointers and tensor scales. A caller that
+ * re-quantises INTO THE SAME BUFFERS (after an optimizer step or a checkpoint load) must call
+ * tmt_moe_nvfp4_weights_changed before the next forward, or large steps keep using the old expansion. */
 int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter,
                           const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, void* Y,
                           float beta, int tokens);
+/* Drops everything the handle derived from NVFP4 weights (the bf16 expansion, the pointer table of the small-batch
+ * route): the next tmt_moe_forward_nvfp4 builds it again from the descriptors it is given. */
+int tmt_moe_nvfp4_weights_changed(tmt_moe* h);
 
 /* ---- expert parallelism over NCCL (no counterpart in the reference) -------------------
  * One process per GPU. Rank 0 creates an id, the host program ships the 128 bytes to all

@@ -220,6 +220,13 @@ int tmt_moe_quantize_nvfp4(const void* W, int rows, int cols, void* packed, void
     } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
 }
 
+int tmt_moe_nvfp4_weights_changed(tmt_moe* h) {
+    if (!h) { set_error("null handle"); return -1; }
+    h->q_key.clear(); h->q_scales_host.clear();             // the next large step expands the weights again
+    h->q_table_key.clear(); h->q_table_scales.clear();      // the next small step rebuilds its pointer table
+    return 0;
+}
+
 int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter, const tmt_nvfp4_weight* Wup,
                           const tmt_nvfp4_weight* Wdown, void* Y, float beta, int tokens) {
     if (!h) { set_error("null handle"); return -1; }

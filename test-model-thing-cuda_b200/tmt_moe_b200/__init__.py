@@ -29,7 +29,7 @@ EXPORTS = (
     "tmt_moe_debug_gemm_cycles", "tmt_moe_step_host_async", "tmt_moe_host_wait",
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
     "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes", "tmt_moe_usage",
-    "tmt_moe_ep_check_capacity",
+    "tmt_moe_ep_check_capacity", "tmt_moe_nvfp4_weights_changed",
 )
 
 
@@ -214,15 +214,21 @@ class MoE:
             for i, (p, s, ts, r, c) in enumerate(ws):
                 a[i] = Nvfp4Weight(_ptr(p), _ptr(s), ts, r, c)
             return a
-        # a sampler calls this once per byte with the same weight lists: the descriptor arrays are built once per pair of
-        # lists (the lists themselves are kept alive by the cache entry)
-        key = (id(Wup), id(Wdown))
+        # a sampler calls this once per byte with the same weights: the descriptor arrays are built once per set of
+        # pointers, scales and shapes (a list mutated in place gets new arrays; the tensors are kept alive by the entry)
+        def sig(ws):
+            return tuple((_ptr(p).value, _ptr(s).value, float(ts), r, c) for p, s, ts, r, c in ws)
+        key = (sig(Wup), sig(Wdown))
         hit = getattr(self, "_nvfp4_desc", None)
-        if hit is None or hit[0] != key or hit[1] is not Wup or hit[2] is not Wdown:
-            hit = (key, Wup, Wdown, arr(Wup), arr(Wdown))
+        if hit is None or hit[0] != key:
+            hit = (key, list(Wup), list(Wdown), arr(Wup), arr(Wdown))
             self._nvfp4_desc = hit
         _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), hit[3], hit[4], _ptr(Y),
                                               ctypes.c_float(beta), t), self.lib)
+
+    def nvfp4_weights_changed(self):
+        """Call after re-quantising into the same buffers: derived copies are rebuilt at the next forward_nvfp4."""
+        _check(self.lib.tmt_moe_nvfp4_weights_changed(self.h), self.lib)
 
     def ep_init_torch(self, dist):
         """Creates the handle's NCCL communicator: rank 0 makes the id, torch.distributed ships it."""

@@ -54,6 +54,51 @@ def test_oracle_matches_reference_outputs(oracle, name):
     _check(c, fwd, b, ref)
 
 
+def _identity_down(c):
+    """hidden = dim and Wdown[e] = I: the two-matrix layer computes gate * silu(x Wup^T), the reference's
+    single-matrix layer up to one more bf16 rounding (of the SiLU output and of the gated row)."""
+    eye = O.f32_to_bf16(np.eye(c["D"], dtype=np.float32))
+    return np.ascontiguousarray(np.broadcast_to(eye, (c["E"], c["D"], c["D"])))
+
+
+MULTI = sorted(n for n in CASES if CASES[n]["E"] > 1)
+
+
+@pytest.mark.parametrize("name", MULTI)
+def test_two_matrix_oracle_pinned_by_reference_outputs(oracle, name):
+    """The oracle's two-matrix mode (up-projection + SiLU, down-projection + gate, and their backward chain) against
+    the reference's own outputs: with an identity down-projection both compute the same function. Same tolerances as
+    the single-matrix comparison."""
+    c = CASES[name]
+    d = inputs(c)
+    ref = _load(name)
+    f = oracle.forward(d["X"], d["Wr"], d["Wup"], _identity_down(c), c["K"], Y=d["Y0"] if c["beta"] else None, beta=c["beta"])
+    b = oracle.backward(f, d["dY"], c["aux"], c["zcoef"])
+    fwd = dict(idx=f["idx"], counts=f["counts"], logits=f["logits"], probs=f["probs"], aux=f["aux"],
+               z=float(f["stat"][c["E"]]), Y=f["Y"])
+    _check(c, fwd, b, ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("impl", [pytest.param(2, id="tcgen05_2cta"), pytest.param(3, id="tcgen05")])
+@pytest.mark.parametrize("name", MULTI)
+def test_cuda_two_matrix_mode_pinned_by_reference_outputs(name, impl):
+    """The CUDA up / down / dH epilogue chain against the reference's outputs, identity down-projection."""
+    import gpu_util as G
+    c = CASES[name]
+    d = dict(inputs(c))
+    d["Wdown"] = _identity_down(c)
+    ref = _load(name)
+    layer = G.Layer(d, c["T"], c["D"], c["E"], c["K"], c["D"], gemm_impl=impl)
+    Y = layer.forward(d["Y0"] if c["beta"] else None, c["beta"])
+    stat, counts, aux = layer.moe.stats()
+    g = layer.backward(d["dY"], c["aux"], c["zcoef"])
+    assert layer.moe.device_status() == 0
+    fwd = dict(idx=layer.moe.read("idx"), counts=counts.astype(np.int32), logits=layer.moe.read("logits"),
+               probs=layer.moe.read("probs"), aux=aux, z=float(stat[c["E"]]), Y=Y)
+    _check(c, fwd, g, ref)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_cuda_matches_reference_outputs(name):

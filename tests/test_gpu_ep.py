@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1):
+def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1, shape=(900, 256, 384, 8, 2)):
     try:
         sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TMT_MOE_EP_WAVES=str(waves))
@@ -25,7 +25,7 @@ def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1):
         import gpu_util as G
         import tmt_moe_b200 as M
         from oracle import oracle as O
-        T, D, H, E, K = 900, 256, 384, 8, 2
+        T, D, H, E, K = shape
         rf = True
         data = [synth.make(T, D, H, E, K, rf, seed=70 + g, w_std=0.06, router_std=0.1, dy_std=0.05) for g in range(world)]
         allX = np.concatenate([d["X"] for d in data])
@@ -76,22 +76,28 @@ def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1):
         q.put((rank, "FAIL: %s\n%s" % (exc, traceback.format_exc())))
 
 
+SMALL = (900, 256, 384, 8, 2)
+C5_WIDTHS = (1024, 2048, 2048, 64, 4)      # the benchmarked configuration's widths, 32 experts per rank, on a token sample
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("transport,gemm_impl,waves", [pytest.param(0, 3, 1, id="peer"), pytest.param(1, 3, 1, id="nccl"),
-                                                       pytest.param(0, 2, 1, id="peer-cta_pairs"), pytest.param(1, 2, 1, id="nccl-cta_pairs"),
-                                                       pytest.param(0, 2, 2, id="peer-cta_pairs-two_expert_waves")])
-def test_expert_parallel_two_gpus(transport, gemm_impl, waves):
+@pytest.mark.parametrize("transport,gemm_impl,waves,shape", [
+    pytest.param(0, 3, 1, SMALL, id="peer"), pytest.param(1, 3, 1, SMALL, id="nccl"),
+    pytest.param(0, 2, 1, SMALL, id="peer-cta_pairs"), pytest.param(1, 2, 1, SMALL, id="nccl-cta_pairs"),
+    pytest.param(0, 2, 2, SMALL, id="peer-cta_pairs-two_expert_waves"),
+    pytest.param(0, 0, 1, C5_WIDTHS, id="peer-config5_widths"), pytest.param(1, 0, 1, C5_WIDTHS, id="nccl-config5_widths")])
+def test_expert_parallel_two_gpus(transport, gemm_impl, waves, shape):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 200 + 7 * transport + 17 * gemm_impl + 3 * waves
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport, gemm_impl, waves)) for r in range(world)]
+    port = 29700 + os.getpid() % 200 + 7 * transport + 17 * gemm_impl + 3 * waves + (60 if shape[1] > 256 else 0)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, transport, gemm_impl, waves, shape)) for r in range(world)]
     for p in procs:
         p.start()
     res = []
     try:
         for _ in procs:
-            res.append(q.get(timeout=240))
+            res.append(q.get(timeout=600))
     finally:
         for p in procs:
             p.join(timeout=30)

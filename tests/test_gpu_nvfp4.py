@@ -143,3 +143,46 @@ def test_small_batch_route_is_deterministic_and_independent_of_batch_composition
     moe.forward_nvfp4(X, Wr, up_q, down_q, Y, tokens=20)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(G.host_u16(Y)[:20], outs[0][:20])
+
+
+def test_requantising_in_place_is_followed_by_both_routes(monkeypatch):
+    """Weights re-quantised INTO THE SAME BUFFERS with an unchanged tensor scale (rows reversed: same amax): the
+    descriptors do not change, so the handle is told with tmt_moe_nvfp4_weights_changed; after that the expanded route
+    (which caches a bf16 expansion) and the small-batch route (which reads the packed bytes) both compute with the new
+    weights."""
+    import gpu_util as G
+    import tmt_moe_b200 as M
+    T, D, H, E, K = 48, 256, 256, 4, 2
+    data, up_q, down_q, up_dq, down_dq, us, ds, keep = _setup(M, G, T, D, H, E, K, 91)
+    X, Wr = G.dev(data["X"]), G.dev(data["Wr"])
+    handles = {}
+    for route, limit in (("small_batch", "256"), ("expanded", "0")):
+        monkeypatch.setenv("TMT_MOE_DECODE_MAX_TOKENS", limit)
+        moe = M.MoE(64, D, E, K, hidden=H, training=False, gemm_impl=3)
+        Y = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+        moe.forward_nvfp4(X, Wr, up_q, down_q, Y, tokens=T)           # builds the expansion / the table from the old weights
+        torch.cuda.synchronize()
+        handles[route] = moe
+    # new weights into the same packed / scale buffers
+    new_up, new_down = data["Wup"][:, ::-1].copy(), data["Wdown"][:, ::-1].copy()
+    up_dq2, down_dq2 = [], []
+    for e in range(E):
+        for W, q, dq in ((new_up[e], up_q[e], up_dq2), (new_down[e], down_q[e], down_dq2)):
+            ts = M.quantize_nvfp4(G.dev(W), W.shape[0], W.shape[1], q[0], q[1])
+            assert ts == q[2]                                         # same tensor scale: nothing in the descriptor changed
+            dq.append(O.nvfp4_dequantize(q[0].cpu().numpy(), q[1].cpu().numpy(), 1.0))
+    torch.cuda.synchronize()
+    ref = O.forward(data["X"], data["Wr"], np.stack(up_dq2), np.stack(down_dq2), K, up_scale=us, down_scale=ds, pad=128)
+    old = O.forward(data["X"], data["Wr"], up_dq, down_dq, K, up_scale=us, down_scale=ds, pad=128)
+    want, stale = O.bf16_to_f32(ref["Y"]), O.bf16_to_f32(old["Y"])
+    assert synth.rel_l2(stale, want) > 0.5                            # the two weight sets give clearly different outputs
+    for route, limit in (("small_batch", "256"), ("expanded", "0")):
+        monkeypatch.setenv("TMT_MOE_DECODE_MAX_TOKENS", limit)
+        moe = handles[route]
+        moe.nvfp4_weights_changed()
+        Y = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+        moe.forward_nvfp4(X, Wr, up_q, down_q, Y, tokens=T)
+        torch.cuda.synchronize()
+        assert moe.device_status() == 0
+        assert synth.rel_l2(O.bf16_to_f32(G.host_u16(Y)), want) <= 1e-2, route
+        moe.close()

@@ -121,6 +121,13 @@ def test_topk4_64_experts(impl):
     _fwd_bwd(dict(T=1024, D=256, H=256, E=64, K=4, router_f32=True), impl, seed=6, w_std=0.08, router_std=0.1)
 
 
+@pytest.mark.parametrize("impl", [pytest.param(2, id="tcgen05_2cta"), pytest.param(3, id="tcgen05")])
+def test_config5_true_widths(impl):
+    """The benchmarked configuration at its own widths (dim 2048, hidden 2048, 64 experts, top-4, fp32 router) on a
+    token sample the oracle finishes in seconds: routing bit-exact, forward and every gradient in tolerance."""
+    _fwd_bwd(dict(synth.CONFIGS["c5"], T=2048), impl, seed=17)
+
+
 def test_single_token_and_partial_batch():
     cfg = dict(T=257, D=128, H=192, E=4, K=2)
     data = synth.make(257, 128, 192, 4, 2, seed=7, w_std=0.1)

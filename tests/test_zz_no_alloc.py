@@ -43,6 +43,35 @@ def test_no_alloc_router_gradient_twice_in_a_row():
         assert synth.rel_l2(got, ref) <= 1e-5          # same products, only the summation order differs
 
 
+@pytest.mark.parametrize("T,D,E", [(70, 2048, 64), (90, 512, 80), (45, 256, 16), (130, 384, 32)],
+                         ids=["64_experts_x_2048_exactly_the_limit", "80_experts_two_passes", "16_experts", "32_experts"])
+def test_no_alloc_all_expert_widths_on_a_side_stream(T, D, E):
+    """Every accumulator width of the first kernel (8 is covered above; here 16, 32, 64), the loop over more than 64
+    experts and the largest size the built-in scratch holds, on a stream of its own, against the product written out in
+    numpy: sum over tokens of bf16(dlogits[t, e]) * X[t, d] in float64."""
+    import tmt_moe_b200 as M
+    from oracle import oracle as O
+    lib = M.load()
+    rng = np.random.default_rng(1000 + E)
+    dl = (rng.standard_normal((T, E)) * 0.05).astype(np.float32)
+    X = O.f32_to_bf16(rng.standard_normal((T, D), dtype=np.float32))
+    want = O.bf16_to_f32(O.f32_to_bf16(dl)).astype(np.float64).T @ O.bf16_to_f32(X).astype(np.float64)
+    d_dl = torch.from_numpy(dl).cuda()
+    d_X = torch.from_numpy(X.view(np.int16).copy()).cuda()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    for _ in range(2):                                   # the second call finds the first one's partial sums in the array
+        out = torch.full((E, D), float("nan"), device="cuda")
+        side.wait_stream(torch.cuda.current_stream())
+        rc = lib.tmt_moe_router_dw_noalloc(ctypes.c_void_p(d_dl.data_ptr()), ctypes.c_void_p(d_X.data_ptr()), T, D, E,
+                                           ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(side.cuda_stream))
+        assert rc == 0, lib.tmt_moe_last_error().decode()
+        side.synchronize()
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert synth.rel_l2(got, want) <= 1e-5
+
+
 def test_no_alloc_rejects_sizes_beyond_the_scratch():
     import tmt_moe_b200 as M
     lib = M.load()
