@@ -321,15 +321,100 @@ def bench_ln(args):
     print(json.dumps(line), flush=True)
 
 
+def bench_ref4(args):
+    """The reference's own GPU implementation (tmt-cuda/src/moe.cu recompiled for sm_100a, cuBLAS per expert; oracle/_ref)
+    beside this library on the same B200, same seeded inputs, same method: the reference's harness shape (profile.cu:
+    dim 1280, top-2, 15 warm-ups, 60 iterations between two CUDA events) in reference mode (one dim x dim matrix per
+    expert, SiLU in combine) with 4 experts, the most its fused router computes correctly (moe.cu:15-34), at 2048 and at
+    16384 tokens. Forward alone and forward + backward."""
+    import torch
+    import tmt_moe_b200 as M
+    from tmt_moe_b200 import synth
+    from oracle import ref as R
+    D, E, K = 1280, 4, 2
+    warm, iters = 15, 60
+    torch.cuda.set_device(0)
+    want_ref = R.available()
+    cases = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    wall0 = time.time()
+    for N in (2048, 16384):
+        host = synth.make(N, D, 0, E, K, False, seed=4242 + N, need_dy=True)
+        case = {"tokens": N}
+        if args.impl == "b200":
+            dev = lambda a: torch.from_numpy(a.view("int16").copy()).cuda()
+            X, dY, Wr, W = dev(host["X"]), dev(host["dY"]), dev(host["Wr"]), dev(host["Wup"])
+            Wl = [W[e] for e in range(E)]
+            Y, dX = torch.zeros_like(X), torch.zeros_like(X)
+            dWr = torch.zeros((E, D), device="cuda")
+            dW = torch.zeros((E, D, D), device="cuda")
+            dWl = [dW[e] for e in range(E)]
+            st = torch.cuda.Stream()
+            torch.cuda.set_stream(st)
+            moe = M.MoE(N, D, E, K, hidden=0, training=True, stream=st.cuda_stream)
+            fwd = lambda: moe.forward(X, Wr, Wl, None, Y, 0.0)
+            bwd = lambda: moe.backward(dY, Wr, Wl, None, dWr, dWl, None, dX, 0.01, 0.001)
+            for _ in range(warm):
+                fwd(); bwd()
+            torch.cuda.synchronize()
+            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            a.record()
+            for _ in range(iters):
+                fwd()
+            b.record()
+            for _ in range(iters):
+                fwd(); bwd()
+            c.record()
+            torch.cuda.synchronize()
+            if moe.device_status() != 0:
+                raise SystemExit("device status %d" % moe.device_status())
+            case["ms_fwd"], case["ms_fwd_bwd"] = a.elapsed_time(b) / iters, b.elapsed_time(c) / iters
+            case["launches_per_fwd_bwd"] = None
+            l0 = moe.launch_count
+            fwd(); bwd()
+            case["launches_per_fwd_bwd"] = moe.launch_count - l0
+            torch.cuda.synchronize()
+            moe.close()
+            torch.cuda.set_stream(torch.cuda.default_stream())
+        if want_ref:
+            rf, rfb = R.time_moe(host["X"], host["Wr"], host["Wup"], K, host["dY"], 0.01, 0.001, warm, iters)
+            case["reference_gpu"] = {"ms_fwd": rf, "ms_fwd_bwd": rfb, "kind": "reference recompiled sm_100a (cuBLAS per expert)"}
+            if "ms_fwd" in case:
+                case["speedup_fwd"], case["speedup_fwd_bwd"] = rf / case["ms_fwd"], rfb / case["ms_fwd_bwd"]
+        cases.append(case)
+    clocks = sampler.stop(wall0, time.time())
+    big = cases[-1]
+    work = ("reference mode (one dim x dim matrix per expert, SiLU in combine): dim=1280 experts=4 topk=2, tokens 2048 and 16384, "
+            "fwd and fwd+bwd, %d warm-ups + %d iterations between CUDA events; value quoted at 16384 tokens" % (warm, iters))
+    base = dict(metric="moe_layer_tokens_per_s_fwd_bwd", unit="tokens/s", n_gpus=1, steps=iters, warmup=warm, higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                config={"workload": work, "l2": "working set of the 16384-token case larger than L2; 2048-token case not flushed "
+                                                 "(the reference's own harness does not flush)"}, clocks=clocks)
+    if args.impl == "reference":
+        if not want_ref:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libtmt_ref.so is not built"}), flush=True)
+            return
+        ms = big["reference_gpu"]["ms_fwd_bwd"]
+        print(json.dumps(dict(base, impl="reference", value=big["tokens"] / (ms * 1e-3), ms_per_step=ms, cases=cases,
+                              gpu_launches=0)), flush=True)
+        return
+    ms = big["ms_fwd_bwd"]
+    print(json.dumps(dict(base, value=big["tokens"] / (ms * 1e-3), ms_per_step=ms, cases=cases,
+                          reference_gpu=big.get("reference_gpu"),
+                          gpu_launches=(big["launches_per_fwd_bwd"] or 0) * iters)), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS) + ["adamw5", "ln5"],
+    ap.add_argument("--config", default="c5", choices=sorted(CONFIGS) + ["adamw5", "ln5", "ref4"],
                     help="c1..c5: the MoE layer workloads; adamw5: the optimizer step over config 5's expert and router parameters "
                          "(the component after the layer's backward pass); ln5: the LayerNorm in front of the layer on config 5's "
-                         "activations, forward + backward. Both print their own metric, not the headline")
+                         "activations, forward + backward. Both print their own metric, not the headline. ref4: the reference's own GPU "
+                         "implementation (recompiled for sm_100a) timed beside this library in reference mode, 4 experts")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (not the headline workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -346,6 +431,8 @@ def main():
         return bench_adamw(args)
     if args.config == "ln5":
         return bench_ln(args)
+    if args.config == "ref4":
+        return bench_ref4(args)
     cfg = dict(CONFIGS[args.config])
     if args.tokens:
         cfg["T"] = args.tokens
@@ -403,7 +490,7 @@ def main():
     torch.cuda.synchronize()
     stream = torch.cuda.current_stream().cuda_stream
     moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32 if cfg["router_f32"] else M.BF16,
-                training=cfg["backward"], device=local_rank, host_io=(world == 1 and not args.no_e2e),
+                training=cfg["backward"], device=local_rank, host_io=(not args.no_e2e and not cfg.get("nvfp4")),
                 gemm_impl=M.GEMM_TCGEN05_2CTA if args.gemm == "2cta" else M.GEMM_TCGEN05,
                 stream=stream, ep_world=world, ep_rank=rank,
                 ep_transport=M.EP_PEER if args.ep_transport == "peer" else M.EP_NCCL)
@@ -532,7 +619,7 @@ def main():
         e_ms = e0.elapsed_time(e1) / args.steps
         e2e = {"value": tokens_per_step / (e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": n * T * D * 2,
                "d2h_bytes_per_step": n * T * D * 2, "ms_per_step": e_ms}
-    elif world == 1 and not args.no_e2e:
+    elif not args.no_e2e:
         hX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
         hX.copy_(d["X"])
         hdY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
@@ -549,16 +636,21 @@ def main():
         for _ in range(2):
             host_step()
         moe.host_wait()
-        torch.cuda.synchronize()
+        barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             host_step()
         moe.host_wait()                     # every Y, dX and statistics vector of the timed steps is in host memory
         e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        if dist is not None:                # the slowest rank's time, as for the device-timed value
+            t = torch.tensor([e_ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
         nio = 2 if cfg["backward"] else 1
-        e2e = {"value": T / (e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nio * nbytes,
-               "d2h_bytes_per_step": nio * nbytes + (E + 1) * 4, "ms_per_step": e_ms,
-               "timing": "host wall clock around %d queued tmt_moe_step_host_async calls and one tmt_moe_host_wait" % args.steps}
+        e2e = {"value": T * world / (e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": nio * nbytes * world,
+               "d2h_bytes_per_step": (nio * nbytes + (E + 1) * 4) * world, "ms_per_step": e_ms,
+               "timing": "host wall clock (max over ranks) around %d queued tmt_moe_step_host_async calls and one "
+                         "tmt_moe_host_wait per rank; bytes are the sum over the %d ranks" % (args.steps, world)}
 
     if rank != 0:
         if dist is not None:
@@ -597,17 +689,35 @@ def main():
     # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)
     bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12 + (T * D * 2 if cfg["backward"] else 0)), "combine": (A * D * 2 + T * D * 2),
                 "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
+    waves = int(os.environ.get("TMT_MOE_EP_WAVES", "1") or 1)
     for n, nb in bytes_of.items():
+        if world > 1:
+            break
         if n in phases and phases[n][0] > 0:
             gbs = nb / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
             hbm[n] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
                       "bytes_per_launch": nb}
+    nvlink = {}
+    if world > 1 and args.ep_transport == "peer":
+        # Expert parallel: the row kernels move (world-1)/world of their grouped rows over NVLink and are bound by it, not
+        # by HBM: rows leaving (dispatch, gradient dispatch) or entering (combine, scatter) this GPU per launch, against the
+        # measured peer-copy bandwidth of this pool (770 GB/s per direction). Only kernels that run alone on the main stream
+        # have a phase time: the scatter always runs on the second stream under the weight-gradient GEMMs, and with expert
+        # waves so do the other three.
+        out_bytes = A * D * 2 * (world - 1) / world
+        for n in ("dispatch", "combine", "grad_dispatch"):
+            if waves < 2 and n in phases and phases[n][0] > 0:
+                gbs = out_bytes / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
+                nvlink[n] = {"achieved": gbs, "peak": 770.0, "unit": "GB/s", "frac": gbs / 770.0, "bytes_over_nvlink": out_bytes,
+                             "exposed_ms": phases[n][0] / phases[n][1]}
+        nvlink["note"] = ("scatter runs on the second stream under the weight-gradient GEMMs" +
+                          ("; with %d expert waves dispatch, combine and gradient dispatch run there too (no phase time)" % waves if waves > 1 else ""))
     line = dict(base, value=value, ms_per_step=ms,
                 config={"workload": workload, "tokens_per_gpu": T,
-                        "parallelism": ("ep%d/%s" % (world, args.ep_transport)) if world > 1 else "single",
+                        "parallelism": ("ep%d/%s%s" % (world, args.ep_transport, "/waves%d" % waves if waves > 1 else "")) if world > 1 else "single",
                         "l2": "L2 flushed between steps" if flush else "working set larger than L2 (no flush needed)"},
                 clocks=clocks, gpu_launches=launches if not graph_info.get("cuda_graph") else launches0_per_loop * args.steps,
-                roofline=roofline, hbm_kernels=hbm,
+                roofline=roofline, hbm_kernels=hbm, **({"nvlink_kernels": nvlink} if nvlink else {}),
                 phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})
     line.update(graph_info)
     if cfg.get("nvfp4"):

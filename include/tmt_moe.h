@@ -98,7 +98,9 @@ int tmt_moe_backward(tmt_moe* h, const void* dY, const void* Wrouter, const void
 
 /* Host-buffer step used for end-to-end timing: copies X (and dY) from host memory, runs
  * forward (and backward when dY_host != NULL), copies Y (and dX) and the E+1 statistics back
- * and synchronises. Needs desc.host_io = 1. Weight and gradient pointers are device memory. */
+ * and synchronises. Needs desc.host_io = 1. Weight and gradient pointers are device memory.
+ * Works under expert parallelism too (every rank calls it with its own tokens); stat_host[E] is then the SUM over
+ * the ranks of each rank's mean lse^2 (tmt_moe_stats divides it by the rank count). */
 int tmt_moe_step_host(tmt_moe* h, const void* X_host, const void* dY_host, const void* Wrouter,
                       const void* const* Wup, const void* const* Wdown, float* dWrouter,
                       float* const* dWup, float* const* dWdown, void* Y_host, void* dX_host,

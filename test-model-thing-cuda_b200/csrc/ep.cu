@@ -426,6 +426,7 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
             CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, h->stream, peer_map(h, ep->peer_Xg),
                                 h->d.training ? ep->Xc : nullptr));
             h->launches += 1;
+            if (h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvXFree], h->stream));     // X has been read for the last time
             prof_mark(h, kPhExchange);
             rank_barrier(h);                    // every rank's rows have landed
             expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false);
@@ -453,6 +454,7 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
             for (int w = 0; w < W; ++w) {
                 CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, ep->side, wave_map(ep->peer_Xg, w),
                                     (h->d.training && w == 0) ? ep->Xc : nullptr));
+                if (w == W - 1 && h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvXFree], ep->side));   // last read of X
                 rank_barrier(h, ep->side);      // every rank's rows of this wave have landed
                 CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
                 h->launches += 1;
@@ -509,11 +511,27 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
     // came back unscaled and was kept)
     if (ep->peer) {
         zero_pads(h, h->dYg, D);             // own pad rows; peers store into data rows only
-        CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, h->dYg, h->s_j, /*mode=*/2, h->stream,
-                                 peer_map(h, ep->peer_dYg)));
-        h->launches += 1;
-        prof_mark(h, kPhExchange);
-        rank_barrier(h);
+        const bool waved = ep->overlap && ep->waves >= 2;
+        if (!waved) {
+            CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, h->dYg, h->s_j, /*mode=*/2, h->stream,
+                                     peer_map(h, ep->peer_dYg)));
+            h->launches += 1;
+            if (h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], h->stream));    // dY has been read for the last time
+            prof_mark(h, kPhExchange);
+            rank_barrier(h);
+        } else {
+            CKE(cudaEventRecord(ep->ev_fork, h->stream));
+            CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+            for (int w = 0; w < ep->waves; ++w) {
+                PeerMap pm = peer_map(h, ep->peer_dYg, true);
+                pm.wave_lo = (int)((long)ep->EL * w / ep->waves); pm.wave_hi = (int)((long)ep->EL * (w + 1) / ep->waves);
+                CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, h->dYg, h->s_j, /*mode=*/2, ep->side, pm));
+                if (w == ep->waves - 1 && h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], ep->side));
+                rank_barrier(h, ep->side);      // every rank's gradient rows of this wave have landed
+                CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
+                h->launches += 1;
+            }
+        }
         // Input-gradient products first; then the rows of dXg travel back (rank barrier + scatter on the side stream)
         // while the main stream computes the weight gradients, which need nothing from other ranks. Those two GEMM
         // launches leave two SMs free so that the barrier's kernel can start while they run.
@@ -524,7 +542,21 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
             router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
                             (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg));
         } else {
-            expert_backward(h, Wup, Wdown, dWup, dWdown, 1);
+            if (waved) {
+                // the same expert waves as in the forward pass: the gradient rows of wave w+1 travel (side stream) under the
+                // dH / dXg products of wave w (main stream)
+                struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
+                h->sm_limit = gemm_sms_beside_rows(h);
+                const int W = ep->waves, EL = ep->EL;
+                for (int w = 0; w < W; ++w) {
+                    const int lo = (int)((long)EL * w / W), hi = (int)((long)EL * (w + 1) / W);
+                    CKE(cudaStreamWaitEvent(h->stream, ep->ev_sent[w], 0));
+                    expert_backward(h, Wup, Wdown, dWup, dWdown, 1, ep->x_poff[lo] / kPad, (ep->x_poff[hi] - ep->x_poff[lo]) / kPad);
+                }
+                h->sm_limit = 0;
+            } else {
+                expert_backward(h, Wup, Wdown, dWup, dWdown, 1);
+            }
             router_backward(h, Wr, nullptr, ep->Xc, true, h->dXg, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
                             (long)h->d.tokens * ep->G, peer_map(h, ep->peer_dXg), /*defer_scatter=*/true);
             CKE(cudaEventRecord(ep->ev_fork, h->stream));
@@ -542,6 +574,7 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
     } else {
         CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
         h->launches += 1;
+        if (h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], h->stream));
         zero_pads(h, h->dYg, D);
         exchange(h, true, ep->dYs, h->dYg, D);
         expert_backward(h, Wup, Wdown, dWup, dWdown);

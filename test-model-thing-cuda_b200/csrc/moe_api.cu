@@ -394,7 +394,7 @@ void forward_impl(tmt_moe* h, const void* X, const void* Wr, const void* const* 
 
 // The four (reference mode: two) grouped gradient products over the rows in h->dYg.
 void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup,
-                     float* const* dWdown, int which) {
+                     float* const* dWdown, int which, int tile_begin, int tile_count) {
     const int D = h->d.dim, H = h->d.hidden;
     refresh_weights(h, Wup, Wdown);
     refresh_grads(h, dWup, dWdown);
@@ -403,11 +403,13 @@ void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdow
             GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
             dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
             dh.mapC0 = h->act_maps + kOutDP;
+            dh.tile_begin = tile_begin; dh.tile_count = tile_count;
             prof_mark(h, kPhGemmDh);
             run_gemm(h, dh);
             GemmParams dx = rows_gemm(h, kDPK, h->dP, kUpMN, h->up_ptrs, true, D, H, kEpiBf16);
             dx.out0 = h->dXg;
             dx.mapC0 = h->act_maps + kOutDXg;
+            dx.tile_begin = tile_begin; dx.tile_count = tile_count;
             prof_mark(h, kPhGemmDx);
             run_gemm(h, dx);
         }
@@ -812,7 +814,6 @@ int tmt_moe_step_host_async(tmt_moe* h, const void* X_host, const void* dY_host,
     GUARD({
         if (!h->Xs) throw std::runtime_error("handle was created with host_io = 0");
         if (!X_host || !Y_host) throw std::runtime_error("null argument");
-        if (h->d.ep_world > 1) throw std::runtime_error("host step is single-GPU");
         check_tokens(h, tokens);
         CK(cudaSetDevice(h->d.device));
         const size_t bytes = (size_t)tokens * h->d.dim * 2;
@@ -836,17 +837,19 @@ int tmt_moe_step_host_async(tmt_moe* h, const void* X_host, const void* dY_host,
         if (beta != 0.0f) CK(cudaMemcpyAsync(h->Ys, Y_host, bytes, cudaMemcpyHostToDevice, h->stream));
         h->host_hooks = true;
         struct Off { tmt_moe* h; ~Off() { h->host_hooks = false; } } off{h};
-        forward_impl(h, h->Xs, Wrouter, Wup, Wdown, h->Ys, beta, tokens);
+        if (h->d.ep_world > 1) ep_forward(h, h->Xs, Wrouter, Wup, Wdown, h->Ys, beta, tokens);
+        else forward_impl(h, h->Xs, Wrouter, Wup, Wdown, h->Ys, beta, tokens);
         CK(cudaEventRecord(ev[tmt_moe::kEvYWritten], h->stream));
         CK(cudaStreamWaitEvent(h->out_stream, ev[tmt_moe::kEvYWritten], 0));
         CK(cudaMemcpyAsync(Y_host, h->Ys, bytes, cudaMemcpyDeviceToHost, h->out_stream));
         if (stat_host)
-            CK(cudaMemcpyAsync(stat_host, h->rb.stat, (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->out_stream));
+            CK(cudaMemcpyAsync(stat_host, ep_stat(h), (h->d.experts + 1) * sizeof(float), cudaMemcpyDeviceToHost, h->out_stream));
         CK(cudaEventRecord(ev[tmt_moe::kEvYOut], h->out_stream));
         if (bwd) {
             CK(cudaStreamWaitEvent(h->stream, ev[tmt_moe::kEvDyReady], 0));
             CK(cudaStreamWaitEvent(h->stream, ev[tmt_moe::kEvDxOut], 0));   // the previous dX has left dXs
-            backward_impl(h, h->dYs, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, h->dXs, aux, zcoef);
+            if (h->d.ep_world > 1) ep_backward(h, h->dYs, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, h->dXs, aux, zcoef);
+            else backward_impl(h, h->dYs, Wrouter, Wup, Wdown, dWrouter, dWup, dWdown, h->dXs, aux, zcoef);
             CK(cudaEventRecord(ev[tmt_moe::kEvDxWritten], h->stream));
             CK(cudaStreamWaitEvent(h->out_stream, ev[tmt_moe::kEvDxWritten], 0));
             CK(cudaMemcpyAsync(dX_host, h->dXs, bytes, cudaMemcpyDeviceToHost, h->out_stream));

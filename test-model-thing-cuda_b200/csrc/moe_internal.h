@@ -120,8 +120,9 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
 void expert_forward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, bool gate_in_epilogue, int tile_begin = 0,
                     int tile_count = -1);
 // which: bit 0 = the products the input gradient needs (dH, dXg), bit 1 = the weight gradients (dWdown, dWup).
+// tile_count >= 0 restricts the bit-0 products to the 128-row tiles [tile_begin, tile_begin + tile_count).
 void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdown, float* const* dWup, float* const* dWdown,
-                     int which = 3);
+                     int which = 3, int tile_begin = 0, int tile_count = -1);
 // Router backward after the expert products: dlogits, dWr (local contribution) and dX.
 // grouped_x / x_is_ep: the token-side grouped copy of X (Xg, or the send buffer under expert parallelism).
 // pm: where the rows of dXg live (expert parallel with peer addressing); x_tokens: grouped_x is X in token order.

@@ -1,5 +1,6 @@
-"""Generates tests/golden/ref_moe_*.npz: outputs of the REFERENCE's own moe_forward /
-moe_backward (recompiled for sm_100a, oracle/_ref/libtmt_ref.so) on seeded inputs.
+"""Generates tests/golden/ref_moe_*.npz, ref_ln_*.npz and ref_adam_*.npz: outputs of the REFERENCE's own moe_forward /
+moe_backward, layernorm_fwd / layernorm_bwd and multi-tensor optimizer kernels (recompiled for sm_100a,
+oracle/_ref/libtmt_ref.so) on seeded inputs.
 
 Run on a machine with a GPU:  python tests/golden/make_ref_vectors.py [out_dir]
 Inputs are regenerated from the seed by the tests (tmt_moe_b200/synth.py), so only outputs are stored.
@@ -30,8 +31,46 @@ def inputs(c):
                       router_std=c["router_std"], dy_std=0.1, need_res=True)
 
 
+# LayerNorm (tmt-cuda/src/norm.cu): rows, dim, seed
+LN_CASES = {"ln_300x256": dict(N=300, D=256, seed=201), "ln_65x2048": dict(N=65, D=2048, seed=202),
+            "ln_129x64": dict(N=129, D=64, seed=203)}
+# multi-tensor AdamW (tmt-cuda/src/adam.cu): tensor sizes, flags (bit 0 in the norm, bit 1 updated), clip, step
+ADAM_CASES = {"adam_clip": dict(sizes=[4096 * 3 + 17, 1000, 8192], flags=[3, 3, 3], clip=0.5, step=3, seed=301),
+              "adam_noclip_frozen": dict(sizes=[5000, 4097, 64], flags=[3, 1, 3], clip=0.0, step=1, seed=302)}
+ADAM_HYP = dict(lr=3e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.01)
+
+
+def ln_inputs(c):
+    rng = np.random.default_rng(c["seed"])
+    O = synth.O
+    X = O.f32_to_bf16(rng.standard_normal((c["N"], c["D"]), dtype=np.float32) * 1.5 + 0.3)
+    dY = O.f32_to_bf16(rng.standard_normal((c["N"], c["D"]), dtype=np.float32) * 0.1)
+    gamma = (1 + 0.1 * rng.standard_normal(c["D"])).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(c["D"])).astype(np.float32)
+    return X, dY, gamma, beta
+
+
+def adam_inputs(c):
+    rng = np.random.default_rng(c["seed"])
+    n = sum(c["sizes"])
+    master = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    m = (rng.standard_normal(n) * 1e-3).astype(np.float32)
+    v = ((rng.standard_normal(n) * 1e-3) ** 2).astype(np.float32)
+    grad = (rng.standard_normal(n) * 1e-2).astype(np.float32)
+    return master, m, v, grad
+
+
 def main(out_dir):
     os.makedirs(out_dir, exist_ok=True)
+    for name, c in LN_CASES.items():
+        r = ref.ln_run(*ln_inputs(c))
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **r)
+        print(name, "mean[0]", r["mean"][0], "rstd[0]", r["rstd"][0], flush=True)
+    for name, c in ADAM_CASES.items():
+        master, m, v, grad = adam_inputs(c)
+        r = ref.adam_run(c["sizes"], c["flags"], master, m, v, grad, c["clip"], step=c["step"], **ADAM_HYP)
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **{k: np.asarray(x) for k, x in r.items()})
+        print(name, "sumsq", r["sumsq"], flush=True)
     for name, c in CASES.items():
         d = inputs(c)
         r = ref.run(d["X"], d["Wr"], d["Wup"], c["K"], Y0=d["Y0"] if c["beta"] else None, beta=c["beta"],

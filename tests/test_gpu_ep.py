@@ -37,7 +37,7 @@ def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1, shape=(900, 2
         mine = dict(base, X=data[rank]["X"], dY=data[rank]["dY"],
                     Wup=base["Wup"][rank * EL:(rank + 1) * EL], Wdown=base["Wdown"][rank * EL:(rank + 1) * EL])
         moe = M.MoE(T, D, E, K, hidden=H, router_dtype=M.F32, training=True, device=rank, ep_world=world, ep_rank=rank,
-                    ep_capacity_factor=2.0, ep_transport=transport, gemm_impl=gemm_impl)
+                    ep_capacity_factor=2.0, ep_transport=transport, gemm_impl=gemm_impl, host_io=True)
         moe.ep_init_torch(dist)
         X, dY, Wr = G.dev(mine["X"]), G.dev(mine["dY"]), G.dev(mine["Wr"])
         Wup_all, Wdown_all = G.dev(mine["Wup"]), G.dev(mine["Wdown"])
@@ -68,6 +68,20 @@ def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1, shape=(900, 2
             "dWdown": synth.rel_l2(dWdown_all.cpu().numpy(), rb["dWdown"][rank * EL:(rank + 1) * EL]),
         }
         assert errs["Y"] <= 1e-2 and max(errs.values()) <= 3e-2, errs
+        # the host-buffer step (pinned X / dY in, Y / dX / statistics out) gives exactly the device-pointer results
+        pin = lambda a: torch.from_numpy(a.view(np.int16).copy()).pin_memory()
+        hX, hdY = pin(mine["X"]), pin(mine["dY"])
+        hY, hdX = torch.zeros_like(hX).pin_memory(), torch.zeros_like(hX).pin_memory()
+        hstat = torch.zeros(E + 1).pin_memory()
+        dWr2 = torch.zeros_like(dWr)
+        for it in range(2):
+            moe.step_host(hX, hdY, Wr, Wup, Wdown, dWr2, [dWup_all[e] for e in range(EL)], [dWdown_all[e] for e in range(EL)],
+                          hY, hdX, hstat, 0.0, 0.1, 0.001, wait=(it == 1))
+        assert moe.device_status() == 0
+        np.testing.assert_array_equal(hY.numpy().view(np.uint16), G.host_u16(Y))
+        np.testing.assert_array_equal(hdX.numpy().view(np.uint16), G.host_u16(dX))
+        np.testing.assert_array_equal(dWr2.cpu().numpy(), dWr.cpu().numpy())
+        np.testing.assert_allclose(hstat.numpy()[:E], ref["stat"][:E], rtol=1e-4, atol=1e-6)
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok %s" % {k: "%.1e" % v for k, v in errs.items()}))
@@ -85,6 +99,7 @@ C5_WIDTHS = (1024, 2048, 2048, 64, 4)      # the benchmarked configuration's wid
     pytest.param(0, 3, 1, SMALL, id="peer"), pytest.param(1, 3, 1, SMALL, id="nccl"),
     pytest.param(0, 2, 1, SMALL, id="peer-cta_pairs"), pytest.param(1, 2, 1, SMALL, id="nccl-cta_pairs"),
     pytest.param(0, 2, 2, SMALL, id="peer-cta_pairs-two_expert_waves"),
+    pytest.param(0, 2, 4, SMALL, id="peer-cta_pairs-four_expert_waves"),
     pytest.param(0, 0, 1, C5_WIDTHS, id="peer-config5_widths"), pytest.param(1, 0, 1, C5_WIDTHS, id="nccl-config5_widths")])
 def test_expert_parallel_two_gpus(transport, gemm_impl, waves, shape):
     world = 2
