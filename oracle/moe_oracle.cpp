@@ -189,7 +189,7 @@ struct oracle_cfg {
     int pad;         // rows every expert group is padded to (0 = 128, the reference's padding)
 };
 
-int oracle_abi_version() { return 6; }
+int oracle_abi_version() { return 7; }
 
 // moe.cu:10-68 (+ optional per-expert logit bias, which the reference lacks).
 void oracle_router(const oracle_cfg* c, const uint16_t* X, const void* Wr, const float* bias,
@@ -675,6 +675,47 @@ void oracle_ln_backward(const uint16_t* X, const uint16_t* dY, const float* gamm
             for (int d = 0; d < D; ++d) dX[r * D + d] = f2bf(std::fmaf(xh[d], c1, std::fmaf(g[d], rs, c0)));
         }
         for (int d = 0; d < D; ++d) { dGamma[d] = dGamma[d] + bg[d]; dBeta[d] = dBeta[d] + bb[d]; }
+    }
+}
+
+// ---- sampler: Generator::sample for a batch of streams (tmt-cuda/src/generate.h:47-58) ----
+// Uniform draw of stream s at byte position pos: splitmix64 of a key built from (seed, s, pos), top 53 bits / 2^53.
+// The reference keeps ONE std::mt19937 per generator (generate.h:13, 55); a batch of independent streams needs draws
+// that do not depend on which streams share a step, hence a counter-based generator. Everything after the draw
+// follows generate.h:50-57: argmax (first maximum) for temp <= 0; otherwise p[i] = exp((l[i] - max) / temp) with the
+// quotient in fp32 and the exponential in double, sum in index order, r = u * sum, the first i with (r -= p[i]) <= 0,
+// 255 if none. margin (may be NULL) receives |r| at the stopping index relative to the sum: how far the draw was from
+// the boundary between two bytes.
+uint64_t oracle_splitmix64(uint64_t x) {
+    x += UINT64_C(0x9E3779B97F4A7C15);
+    x = (x ^ (x >> 30)) * UINT64_C(0xBF58476D1CE4E5B9);
+    x = (x ^ (x >> 27)) * UINT64_C(0x94D049BB133111EB);
+    return x ^ (x >> 31);
+}
+double oracle_sampler_uniform(uint64_t seed, int stream, long long pos) {
+    const uint64_t k = oracle_splitmix64(seed ^ oracle_splitmix64((uint64_t)stream * UINT64_C(0x632BE59BD9B4E019) + (uint64_t)pos));
+    return (double)(k >> 11) * (1.0 / 9007199254740992.0);
+}
+void oracle_sample(const uint16_t* logits, int streams, float temp, uint64_t seed, long long pos, int* next, double* margin) {
+    for (int s = 0; s < streams; ++s) {
+        float l[256];
+        for (int i = 0; i < 256; ++i) l[i] = bf2f(logits[(long)s * 256 + i]);
+        int best = 0;
+        for (int i = 1; i < 256; ++i) if (l[i] > l[best]) best = i;
+        if (margin) margin[s] = 1.0;
+        if (temp <= 0) { next[s] = best; continue; }
+        const float mx = l[best];
+        double p[256], sum = 0;
+        for (int i = 0; i < 256; ++i) sum += p[i] = std::exp((double)((l[i] - mx) / temp));
+        double r = oracle_sampler_uniform(seed, s, pos) * sum;
+        int pick = 255;
+        for (int i = 0; i < 256; ++i) if ((r -= p[i]) <= 0) { pick = i; break; }
+        next[s] = pick;
+        if (margin) {
+            // distance of the draw from both ends of the chosen byte's interval, relative to the sum
+            const double below = -r, above = p[pick] + r;
+            margin[s] = std::min(below, above) / sum;
+        }
     }
 }
 

@@ -38,7 +38,8 @@ def lib():
         _lib.oracle_abi_version.restype = ctypes.c_int
         _lib.oracle_sumsq.restype = ctypes.c_double
         _lib.oracle_clip_scale.restype = ctypes.c_float
-        assert _lib.oracle_abi_version() == 6, "stale oracle library: run make -C oracle -B"
+        _lib.oracle_sampler_uniform.restype = ctypes.c_double
+        assert _lib.oracle_abi_version() == 7, "stale oracle library: run make -C oracle -B"
     return _lib
 
 
@@ -243,3 +244,19 @@ def ln_backward(X, dY, gamma, mean, rstd):
                              _p(np.ascontiguousarray(gamma, np.float32)), _p(np.ascontiguousarray(mean, np.float32)),
                              _p(np.ascontiguousarray(rstd, np.float32)), _p(dX), _p(dG), _p(dB), ctypes.c_long(rows), ctypes.c_int(D))
     return dX, dG, dB
+
+
+def sample(logits, temp, seed, pos):
+    """Generator::sample (generate.h:47-58) for a batch: logits (streams, 256) bf16 bits. Returns (next byte per stream,
+    margin per stream = relative distance of the draw from the nearest boundary between two bytes)."""
+    S = logits.shape[0]
+    assert logits.shape[1] == 256
+    nxt = np.zeros(S, np.int32)
+    margin = np.zeros(S, np.float64)
+    lib().oracle_sample(_p(np.ascontiguousarray(logits, np.uint16)), ctypes.c_int(S), ctypes.c_float(temp), ctypes.c_uint64(seed),
+                        ctypes.c_longlong(pos), _p(nxt), _p(margin))
+    return nxt, margin
+
+
+def sampler_uniform(seed, stream, pos):
+    return float(lib().oracle_sampler_uniform(ctypes.c_uint64(seed), ctypes.c_int(stream), ctypes.c_longlong(pos)))

@@ -30,6 +30,10 @@ EXPORTS = (
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
     "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes", "tmt_moe_usage",
     "tmt_moe_ep_check_capacity", "tmt_moe_nvfp4_weights_changed",
+    "tmt_ckpt_hash", "tmt_ckpt_record_bytes", "tmt_ckpt_save_param", "tmt_ckpt_load_param",
+    "tmt_sampler_create", "tmt_sampler_destroy", "tmt_sampler_set_weights", "tmt_sampler_x", "tmt_sampler_y",
+    "tmt_sampler_stream", "tmt_sampler_step", "tmt_sampler_upload", "tmt_sampler_download", "tmt_sampler_sync",
+    "tmt_sampler_sample", "tmt_sampler_steps", "tmt_sampler_graphs",
 )
 
 
@@ -326,6 +330,121 @@ class AdamW:
             self.close()
         except Exception:   # noqa: BLE001
             pass
+
+
+class SamplerDesc(ctypes.Structure):
+    _fields_ = [("streams", ctypes.c_int), ("dim", ctypes.c_int), ("hidden", ctypes.c_int), ("experts", ctypes.c_int),
+                ("topk", ctypes.c_int), ("router_dtype", ctypes.c_int), ("ring", ctypes.c_int), ("device", ctypes.c_int),
+                ("stream", ctypes.c_void_p), ("seed", ctypes.c_uint64)]
+
+
+class Sampler:
+    """Batched multi-stream sampler session (include/tmt_sampler.h; the reference's Generator, generate.h:9-60, for many
+    streams): NVFP4 decode steps replayed as CUDA graphs over device-resident ring slots, and Generator::sample on the
+    device for all streams at once."""
+
+    def __init__(self, streams, dim, hidden, experts, topk, router_dtype=BF16, ring=4, device=0, stream=None, seed=1):
+        self.lib = load()
+        for name in ("tmt_sampler_x", "tmt_sampler_y", "tmt_sampler_stream"):
+            getattr(self.lib, name).restype = ctypes.c_void_p
+        self.lib.tmt_sampler_steps.restype = ctypes.c_longlong
+        self.lib.tmt_sampler_destroy.restype = None
+        self.desc = SamplerDesc(streams, dim, hidden, experts, topk, router_dtype, ring, device, stream, seed)
+        self.h = ctypes.c_void_p()
+        _check(self.lib.tmt_sampler_create(ctypes.byref(self.desc), ctypes.byref(self.h)), self.lib)
+        self.streams, self.dim, self.ring = streams, dim, ring
+        self._keep = None
+
+    def set_weights(self, Wrouter, Wup, Wdown):
+        """Wup / Wdown: lists of (packed, scales, tensor_scale, rows, cols), one entry per expert."""
+        def arr(ws):
+            a = (Nvfp4Weight * len(ws))()
+            for i, (p, sc, ts, r, c) in enumerate(ws):
+                a[i] = Nvfp4Weight(_ptr(p), _ptr(sc), ts, r, c)
+            return a
+        self._keep = (Wrouter, list(Wup), list(Wdown))
+        _check(self.lib.tmt_sampler_set_weights(self.h, _ptr(Wrouter), arr(Wup), arr(Wdown)), self.lib)
+
+    def x_ptr(self, slot):
+        return self.lib.tmt_sampler_x(self.h, slot)
+
+    def y_ptr(self, slot):
+        return self.lib.tmt_sampler_y(self.h, slot)
+
+    @property
+    def cuda_stream(self):
+        return self.lib.tmt_sampler_stream(self.h)
+
+    def step(self, slot, beta=0.0):
+        _check(self.lib.tmt_sampler_step(self.h, slot, ctypes.c_float(beta)), self.lib)
+
+    def upload(self, slot, X_host):
+        _check(self.lib.tmt_sampler_upload(self.h, slot, _ptr(X_host)), self.lib)
+
+    def download(self, slot, Y_host):
+        _check(self.lib.tmt_sampler_download(self.h, slot, _ptr(Y_host)), self.lib)
+
+    def sync(self):
+        _check(self.lib.tmt_sampler_sync(self.h), self.lib)
+
+    def sample(self, logits, temp, position, next_device):
+        _check(self.lib.tmt_sampler_sample(self.h, _ptr(logits), ctypes.c_float(temp), ctypes.c_longlong(position),
+                                           _ptr(next_device)), self.lib)
+
+    @property
+    def steps(self):
+        return self.lib.tmt_sampler_steps(self.h)
+
+    @property
+    def graphs(self):
+        return self.lib.tmt_sampler_graphs(self.h)
+
+    def close(self):
+        if getattr(self, "h", None) is not None and self.h.value:
+            self.lib.tmt_sampler_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:   # noqa: BLE001
+            pass
+
+
+CKPT_HASH_INIT = 14695981039346656037
+
+
+def ckpt_hash(h, data):
+    """The reference's streaming checkpoint checksum (FNV-1a 64, checkpoint.h:11-17) over a bytes-like object."""
+    lib = load()
+    lib.tmt_ckpt_hash.restype = ctypes.c_uint64
+    buf = (ctypes.c_char * len(data)).from_buffer_copy(bytes(data)) if len(data) else None
+    return int(lib.tmt_ckpt_hash(ctypes.c_uint64(h), buf, ctypes.c_size_t(len(data))))
+
+
+def ckpt_record_bytes(n):
+    lib = load()
+    lib.tmt_ckpt_record_bytes.restype = ctypes.c_size_t
+    return int(lib.tmt_ckpt_record_bytes(ctypes.c_longlong(n)))
+
+
+def ckpt_save_param(master, m, v, stream=None):
+    """One V3 parameter record (u64 n | master | m | v, checkpoint.h:142-148) of fp32 CUDA tensors, as bytes."""
+    lib = load()
+    n = master.numel()
+    rec = bytearray(ckpt_record_bytes(n))
+    buf = (ctypes.c_char * len(rec)).from_buffer(rec)
+    _check(lib.tmt_ckpt_save_param(_ptr(master), _ptr(m), _ptr(v), ctypes.c_longlong(n), buf, ctypes.c_size_t(len(rec)),
+                                   _ptr(stream)), lib)
+    return bytes(rec)
+
+
+def ckpt_load_param(record, master, m=None, v=None, work=None, stream=None):
+    """Reads one record into fp32 CUDA tensors and re-materialises the bf16 working copy (checkpoint.h:149)."""
+    lib = load()
+    buf = (ctypes.c_char * len(record)).from_buffer_copy(bytes(record))
+    _check(lib.tmt_ckpt_load_param(buf, ctypes.c_size_t(len(record)), ctypes.c_longlong(master.numel()), _ptr(master), _ptr(m),
+                                   _ptr(v), _ptr(work), _ptr(stream)), lib)
 
 
 def quantize_nvfp4(W, rows, cols, packed, scales, stream=None):

@@ -22,7 +22,7 @@ def test_every_declared_symbol_is_exported(lib):
     for header in sorted(os.listdir(os.path.join(ROOT, "include"))):
         text = open(os.path.join(ROOT, "include", header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names |= set(re.findall(r"\b(tmt_(?:moe|adamw|ln)_[a-z0-9_]+)\s*\(", text))
+        names |= set(re.findall(r"\b(tmt_(?:moe|adamw|ln|ckpt|sampler)_[a-z0-9_]+)\s*\(", text))
     assert len(names) >= 26 and "tmt_adamw_step" in names and "tmt_ln_backward" in names
     for n in sorted(names):
         assert hasattr(lib, n), n
