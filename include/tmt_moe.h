@@ -189,6 +189,16 @@ int tmt_moe_quantize_nvfp4(const void* W_bf16, int rows, int cols, void* packed,
 int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter,
                           const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, void* Y,
                           float beta, int tokens);
+/* The same forward with the LayerNorm in front of the block (layernorm_fwd, tmt-cuda/src/norm.cu:8-50; call site
+ * model.cu:509-514) taken in: X holds the rows BEFORE the normalisation, gamma / beta_ln (dim fp32, device) are its
+ * parameters, eps = 1e-5. For sampler-sized steps (the per-token router, tokens x experts <= 16384, on the packed-weight
+ * route) the router's first kernel normalises each row itself, with the arithmetic of tmt_ln_forward (include/tmt_norm.h),
+ * so a decode step stays at five launches and the result has the bits of tmt_ln_forward followed by
+ * tmt_moe_forward_nvfp4; larger steps run that kernel and then the block. The residual (beta != 0) adds to Y as given:
+ * the reference's residual stream is the un-normalised one (model.cu:513-515). */
+int tmt_moe_forward_nvfp4_ln(tmt_moe* h, const void* X, const float* gamma, const float* beta_ln, const void* Wrouter,
+                             const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, void* Y, float beta, int tokens);
+
 /* Drops everything the handle derived from NVFP4 weights (the bf16 expansion, the pointer table of the small-batch
  * route): the next tmt_moe_forward_nvfp4 builds it again from the descriptors it is given. */
 int tmt_moe_nvfp4_weights_changed(tmt_moe* h);

@@ -56,8 +56,12 @@ struct PeerMap {
 
 // scan_splits > 0 and scanned != NULL: a batch of at most kTokBlock tokens also runs the scan (launch_scan) inside the
 // router's last kernel; *scanned tells whether it did.
+// ln_gamma / ln_beta / xn (all or none): X holds the rows before the LayerNorm in front of the block; the per-token
+// kernel normalises each row itself and writes it to xn. Only where router_takes_layernorm(d) says so.
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
-                          const float* bias, cudaStream_t s, int scan_splits = 0, bool* scanned = nullptr);
+                          const float* bias, cudaStream_t s, int scan_splits = 0, bool* scanned = nullptr,
+                          const float* ln_gamma = nullptr, const float* ln_beta = nullptr, uint16_t* xn = nullptr);
+bool router_takes_layernorm(const RouteDims& d);
 // splits: number of reduction ranges written to split_poff (1..kMaxSplits).
 cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s);
 // Xg[slot] = X[token]; pad rows zeroed; fills slot_of / slotw / tok_of_slot (moe.cu:103-140).

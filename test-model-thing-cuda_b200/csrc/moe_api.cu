@@ -332,7 +332,8 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
     prof_mark(h, kPhRouter);
     bool scanned = false;
-    CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream, h->splits, &scanned));
+    CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream, h->splits, &scanned, h->ln_gamma,
+                     h->ln_beta, h->ln_gamma ? h->xn : nullptr));
     prof_mark(h, kPhScan);
     if (!scanned) CK(launch_scan(h->dims, h->rb, h->splits, h->stream));
     const int plain = (h->dims.T + h->pad - 1) / h->pad * (h->pad / kPad);     // 128-row tiles, whole pairs for the CTA-pair kernel

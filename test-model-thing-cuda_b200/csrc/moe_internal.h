@@ -91,6 +91,10 @@ struct tmt_moe {
     // small-batch NVFP4 route: device table of the packed weights ([4][E] pointers, then [2][E] scales) and what it was built from
     void* q_table = nullptr;
     std::vector<const void*> q_table_key; std::vector<float> q_table_scales;
+    // LayerNorm in front of the block, fused into the per-token router (tmt_moe_forward_nvfp4_ln): the parameters of the
+    // call in progress, the normalised rows, and the statistics of the stand-alone kernel for larger batches
+    const float* ln_gamma = nullptr; const float* ln_beta = nullptr;
+    uint16_t* xn = nullptr; float* ln_stats = nullptr;
     // expert parallelism
     tmt_ep_state* ep = nullptr;
     int* ep_world_counts = nullptr;

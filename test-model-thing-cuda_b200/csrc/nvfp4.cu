@@ -8,6 +8,7 @@
 #include <stdexcept>
 #include <cstdlib>
 
+#include "../../include/tmt_norm.h"
 #include "moe_internal.h"
 #include "nvfp4_decode.h"
 
@@ -166,7 +167,7 @@ void forward_small(tmt_moe* h, const uint16_t* X, const void* Wr, const tmt_nvfp
     route_only(h, X, Wr);
     Fp4RowsArgs up{};
     up.packed = tab; up.scales = tab + E; up.es = es;
-    up.src = X; up.src_ld = D; up.src_div = K;
+    up.src = h->ln_gamma ? h->xn : X; up.src_ld = D; up.src_div = K;      // fused LayerNorm: the router wrote the normalised rows
     up.out = h->Hact; up.out_ld = H;
     up.idx = h->rb.idx; up.gate = h->rb.w; up.n_asg = tokens * K; up.rows = H; up.kdim = D;
     up.status = h->rb.status;
@@ -225,6 +226,34 @@ int tmt_moe_nvfp4_weights_changed(tmt_moe* h) {
     h->q_key.clear(); h->q_scales_host.clear();             // the next large step expands the weights again
     h->q_table_key.clear(); h->q_table_scales.clear();      // the next small step rebuilds its pointer table
     return 0;
+}
+
+int tmt_moe_forward_nvfp4_ln(tmt_moe* h, const void* X, const float* gamma, const float* beta_ln, const void* Wrouter,
+                             const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown, void* Y, float beta, int tokens) {
+    if (!h) { set_error("null handle"); return -1; }
+    try {
+        if (!X || !gamma || !beta_ln) throw std::runtime_error("null argument");
+        if (tokens < 1 || tokens > h->d.tokens) throw std::runtime_error("tokens outside [1, desc.tokens]");
+        if (h->d.dim % 8 || h->d.dim > 8192) throw std::runtime_error("LayerNorm needs dim <= 8192");
+        CKQ(cudaSetDevice(h->d.device));
+        if (!h->xn) {      // allocated on first use, kept for the handle's lifetime
+            void* p = nullptr;
+            CKQ(cudaMalloc(&p, (size_t)h->d.tokens * h->d.dim * 2)); h->allocs.push_back(p); h->xn = static_cast<uint16_t*>(p);
+            CKQ(cudaMalloc(&p, (size_t)h->d.tokens * 2 * sizeof(float))); h->allocs.push_back(p); h->ln_stats = static_cast<float*>(p);
+        }
+        RouteDims dd = h->dims;
+        dd.T = tokens;
+        const bool fused = Wup && Wdown && small_batch_route(h, Wup, Wdown, tokens) && router_takes_layernorm(dd);
+        if (fused) {
+            struct Clear { tmt_moe* h; ~Clear() { h->ln_gamma = nullptr; h->ln_beta = nullptr; } } clear{h};
+            h->ln_gamma = gamma; h->ln_beta = beta_ln;
+            return tmt_moe_forward_nvfp4(h, X, Wrouter, Wup, Wdown, Y, beta, tokens);
+        }
+        // larger batches: the stand-alone LayerNorm kernel, then the block on the normalised rows
+        if (tmt_ln_forward(X, gamma, beta_ln, h->xn, h->ln_stats, h->ln_stats + h->d.tokens, tokens, h->d.dim, h->stream) != 0) return -1;
+        h->launches += 1;
+        return tmt_moe_forward_nvfp4(h, h->xn, Wrouter, Wup, Wdown, Y, beta, tokens);
+    } catch (const std::exception& e) { h->ln_gamma = nullptr; h->ln_beta = nullptr; set_error("%s", e.what()); return -1; }
 }
 
 int tmt_moe_forward_nvfp4(tmt_moe* h, const void* X, const void* Wrouter, const tmt_nvfp4_weight* Wup,

@@ -33,6 +33,9 @@ struct RouterArgs {
     const uint16_t* X; const void* Wr; const float* bias;
     int T, D, E, K;
     RouteBufs b;
+    // fused LayerNorm in front of the router (per-token kernel only): X holds the rows BEFORE the normalisation, the
+    // normalised rows are written to xn (what the expert products read). NULL: X is the block's input as it is.
+    const float* ln_gamma; const float* ln_beta; uint16_t* xn;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -361,8 +364,13 @@ __global__ void __launch_bounds__(256) scan_finish_kernel(const RouteDims d, con
 // Here one block computes the logits of ONE token: 16 groups of 8 lanes, lane s = chain s, group q = experts q, q + 16,
 // ...; the same chains, in the same order, added by the same butterfly, so the logits are bit-identical. The second
 // half then runs per 64-token block on the stored logits (router_finish_kernel).
-template <bool WF32>
+// LN: the LayerNorm in front of the block (tmt-cuda/src/norm.cu:8-50, model.cu:509-510) runs here as well: warp 0
+// normalises the token's row with the arithmetic of the stand-alone forward kernel (lane l owns vectors l, l + 32, ...;
+// sums in index order, butterfly 16..1, IEEE division and square root), leaves it in shared memory for the chains and
+// writes it once for the expert products, so the fused step gives the bits of LayerNorm followed by the router.
+template <bool WF32, bool LN>
 __global__ void __launch_bounds__(128) router_logits_small_kernel(const RouterArgs a) {
+    extern __shared__ __align__(16) uint16_t xs[];       // LN: the normalised row
     const int s = threadIdx.x & 7, grp = threadIdx.x >> 3;
     const long t = blockIdx.x;
     pdl_begin();
@@ -370,6 +378,38 @@ __global__ void __launch_bounds__(128) router_logits_small_kernel(const RouterAr
     const int nvec = a.D >> 3;
     const unsigned full = 0xffffffffu;
     const uint16_t* xrow = a.X + t * a.D;
+    if constexpr (LN) {
+        if (threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            float sum = 0.0f, sq = 0.0f;
+            for (int v = lane; v < nvec; v += 32) {
+                const uint4 r = ldg16(xrow + v * 8);
+                const float f[8] = {bf_lo(r.x), bf_hi(r.x), bf_lo(r.y), bf_hi(r.y), bf_lo(r.z), bf_hi(r.z), bf_lo(r.w), bf_hi(r.w)};
+#pragma unroll
+                for (int q = 0; q < 8; ++q) { sum = __fadd_rn(sum, f[q]); sq = __fmaf_rn(f[q], f[q], sq); }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sum = __fadd_rn(sum, __shfl_xor_sync(full, sum, o));
+                sq = __fadd_rn(sq, __shfl_xor_sync(full, sq, o));
+            }
+            const float fd = (float)a.D;
+            const float m = __fdiv_rn(sum, fd);
+            const float var = __fsub_rn(__fdiv_rn(sq, fd), __fmul_rn(m, m));
+            const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, 1e-5f)));
+            for (int v = lane; v < nvec; v += 32) {
+                const uint4 r = ldg16(xrow + v * 8);
+                const float f[8] = {bf_lo(r.x), bf_hi(r.x), bf_lo(r.y), bf_hi(r.y), bf_lo(r.z), bf_hi(r.z), bf_lo(r.w), bf_hi(r.w)};
+                float o[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) o[q] = __fmaf_rn(__fmul_rn(__fsub_rn(f[q], m), rs), a.ln_gamma[v * 8 + q], a.ln_beta[v * 8 + q]);
+                const uint4 w = make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7]));
+                *reinterpret_cast<uint4*>(xs + v * 8) = w;
+                stg16(a.xn + t * a.D + v * 8, w);
+            }
+        }
+        __syncthreads();
+    }
     for (int e0 = 0; e0 < a.E; e0 += 16) {
         const int e = e0 + grp;
         const bool valid = e < a.E;
@@ -381,7 +421,8 @@ __global__ void __launch_bounds__(128) router_logits_small_kernel(const RouterAr
 #pragma unroll
             for (int u = 0; u < kB; ++u) {
                 const int v = min(v0 + 8 * u, nvec - 8 + s);       // past the end: a valid address, value unused
-                xv[u] = ldg16(xrow + v * 8);
+                if constexpr (LN) xv[u] = *reinterpret_cast<const uint4*>(xs + v * 8);
+                else xv[u] = ldg16(xrow + v * 8);
                 if constexpr (WF32) {
                     const float* wr = reinterpret_cast<const float*>(a.Wr) + (long)er * a.D + v * 8;
                     wa[u] = ldg16(wr); wb[u] = ldg16(wr + 4);
@@ -482,16 +523,31 @@ cudaError_t launch_router_w(const RouterArgs& a, int nb, cudaStream_t s) {
 // the same bits): beyond it, re-reading the router rows per token costs more than the idle SMs of the tiled kernel.
 constexpr long kSmallRouterLogits = 16384;
 
+bool router_takes_layernorm(const RouteDims& d) {
+    bool small = (long)d.T * d.E <= kSmallRouterLogits;
+    if (const char* f = getenv("TMT_MOE_ROUTER_SMALL")) if (*f) small = *f != '0';
+    return small && d.D * 2 <= 48 * 1024;
+}
+
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
-                          const float* bias, cudaStream_t s, int scan_splits, bool* scanned) {
+                          const float* bias, cudaStream_t s, int scan_splits, bool* scanned, const float* ln_gamma,
+                          const float* ln_beta, uint16_t* xn) {
     if (scanned) *scanned = false;
-    RouterArgs a{X, Wr, bias, d.T, d.D, d.E, d.K, b};
+    RouterArgs a{X, Wr, bias, d.T, d.D, d.E, d.K, b, ln_gamma, ln_beta, xn};
     const int nb = (d.T + kTokBlock - 1) / kTokBlock;
     bool small = (long)d.T * d.E <= kSmallRouterLogits;
     if (const char* f = getenv("TMT_MOE_ROUTER_SMALL")) if (*f) small = *f != '0';
+    if (ln_gamma && !(small && router_takes_layernorm(d))) return cudaErrorInvalidValue;     // the caller normalises first
     if (small) {
-        cudaError_t le = d.router_f32 ? launch_pdl(router_logits_small_kernel<true>, dim3(d.T), dim3(128), 0, s, a)
-                                      : launch_pdl(router_logits_small_kernel<false>, dim3(d.T), dim3(128), 0, s, a);
+        cudaError_t le;
+        if (ln_gamma) {
+            const size_t row = (size_t)d.D * 2;
+            le = d.router_f32 ? launch_pdl(router_logits_small_kernel<true, true>, dim3(d.T), dim3(128), row, s, a)
+                              : launch_pdl(router_logits_small_kernel<false, true>, dim3(d.T), dim3(128), row, s, a);
+        } else {
+            le = d.router_f32 ? launch_pdl(router_logits_small_kernel<true, false>, dim3(d.T), dim3(128), 0, s, a)
+                              : launch_pdl(router_logits_small_kernel<false, false>, dim3(d.T), dim3(128), 0, s, a);
+        }
         if (le != cudaSuccess) return le;
         const size_t smem = (size_t)kTokBlock * d.E * sizeof(float);
         if (smem > 40 * 1024) {

@@ -30,6 +30,7 @@ EXPORTS = (
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
     "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes", "tmt_moe_usage",
     "tmt_moe_ep_check_capacity", "tmt_moe_nvfp4_weights_changed",
+    "tmt_moe_forward_nvfp4_ln",
     "tmt_ckpt_hash", "tmt_ckpt_record_bytes", "tmt_ckpt_save_param", "tmt_ckpt_load_param",
     "tmt_sampler_create", "tmt_sampler_destroy", "tmt_sampler_set_weights", "tmt_sampler_x", "tmt_sampler_y",
     "tmt_sampler_stream", "tmt_sampler_step", "tmt_sampler_upload", "tmt_sampler_download", "tmt_sampler_sync",
@@ -229,6 +230,19 @@ class MoE:
             self._nvfp4_desc = hit
         _check(self.lib.tmt_moe_forward_nvfp4(self.h, _ptr(X), _ptr(Wrouter), hit[3], hit[4], _ptr(Y),
                                               ctypes.c_float(beta), t), self.lib)
+
+    def forward_nvfp4_ln(self, X, gamma, beta_ln, Wrouter, Wup, Wdown, Y, beta=0.0, tokens=None):
+        """forward_nvfp4 with the LayerNorm in front of the block taken in (X: rows before the normalisation)."""
+        t = self.tokens if tokens is None else tokens
+
+        def arr(ws):
+            a = (Nvfp4Weight * len(ws))()
+            for i, (p, s, ts, r, c) in enumerate(ws):
+                a[i] = Nvfp4Weight(_ptr(p), _ptr(s), ts, r, c)
+            return a
+        keep = (arr(Wup), arr(Wdown))
+        _check(self.lib.tmt_moe_forward_nvfp4_ln(self.h, _ptr(X), _ptr(gamma), _ptr(beta_ln), _ptr(Wrouter), keep[0], keep[1],
+                                                 _ptr(Y), ctypes.c_float(beta), t), self.lib)
 
     def nvfp4_weights_changed(self):
         """Call after re-quantising into the same buffers: derived copies are rebuilt at the next forward_nvfp4."""

@@ -186,3 +186,52 @@ def test_requantising_in_place_is_followed_by_both_routes(monkeypatch):
         assert moe.device_status() == 0
         assert synth.rel_l2(O.bf16_to_f32(G.host_u16(Y)), want) <= 1e-2, route
         moe.close()
+
+
+@pytest.mark.parametrize("case", [
+    pytest.param(dict(T=64, D=1024, H=2048, E=16, K=2, rf=False, limit="256"), id="sampler_step_fused_into_the_router"),
+    pytest.param(dict(T=33, D=512, H=256, E=8, K=2, rf=True, limit="256"), id="ragged_fp32_router_fused"),
+    pytest.param(dict(T=300, D=256, H=256, E=4, K=2, rf=False, limit="0"), id="larger_batch_stand_alone_kernel"),
+])
+def test_layernorm_taken_into_the_forward_gives_the_same_bits(case, monkeypatch):
+    """tmt_moe_forward_nvfp4_ln on the rows before the LayerNorm = tmt_ln_forward followed by tmt_moe_forward_nvfp4, bit for
+    bit: routing products and output. (The stand-alone kernel is itself bit-identical to its oracle and pinned by the
+    reference's golden outputs; the fused router does the same arithmetic in the same order.)"""
+    import gpu_util as G
+    import tmt_moe_b200 as M
+    monkeypatch.setenv("TMT_MOE_DECODE_MAX_TOKENS", case["limit"])
+    T, D, H, E, K = case["T"], case["D"], case["H"], case["E"], case["K"]
+    data, up_q, down_q, up_dq, down_dq, us, ds, keep = _setup(M, G, T, D, H, E, K, 55)
+    rng = np.random.default_rng(56)
+    raw = O.f32_to_bf16(rng.standard_normal((T, D), dtype=np.float32) * 1.7 + 0.4)
+    gamma = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    beta_ln = (0.1 * rng.standard_normal(D)).astype(np.float32)
+    Wr = G.dev(data["Wr"] if not case["rf"] else O.bf16_to_f32(data["Wr"]))
+    dt = M.F32 if case["rf"] else M.BF16
+    Xraw, Gm, Bt = G.dev(raw), G.dev(gamma), G.dev(beta_ln)
+    # two steps: LayerNorm kernel, then the block
+    Xn = torch.zeros_like(Xraw)
+    mean, rstd = torch.zeros(T, device="cuda"), torch.zeros(T, device="cuda")
+    M.ln_forward(Xraw, Gm, Bt, Xn, mean, rstd)
+    a = M.MoE(T, D, E, K, hidden=H, router_dtype=dt, training=False)
+    Ya = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+    a.forward_nvfp4(Xn, Wr, up_q, down_q, Ya)
+    torch.cuda.synchronize()
+    # one call
+    b = M.MoE(T, D, E, K, hidden=H, router_dtype=dt, training=False)
+    Yb = torch.zeros((T, D), dtype=torch.int16, device="cuda")
+    l0 = b.launch_count
+    for _ in range(2):
+        b.forward_nvfp4_ln(Xraw, Gm, Bt, Wr, up_q, down_q, Yb)
+        torch.cuda.synchronize()
+    assert a.device_status() == 0 and b.device_status() == 0
+    for n in ("logits", "idx", "w", "counts"):
+        np.testing.assert_array_equal(a.read(n), b.read(n), err_msg=n)
+    np.testing.assert_array_equal(G.host_u16(Ya), G.host_u16(Yb))
+    # and against the oracle: LayerNorm oracle, then the block's oracle on the normalised rows
+    xn_ref, _, _ = O.ln_forward(raw, gamma, beta_ln)
+    np.testing.assert_array_equal(G.host_u16(Xn), xn_ref)
+    wr_ref = data["Wr"] if not case["rf"] else O.bf16_to_f32(data["Wr"])
+    ref = O.forward(xn_ref, wr_ref, up_dq, down_dq, K, up_scale=us, down_scale=ds, pad=256)
+    np.testing.assert_array_equal(b.read("idx"), ref["idx"])
+    assert synth.rel_l2(O.bf16_to_f32(G.host_u16(Yb)), O.bf16_to_f32(ref["Y"])) <= 1e-2
