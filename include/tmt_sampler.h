@@ -51,6 +51,12 @@ void tmt_sampler_destroy(tmt_sampler* s);
  * weights changed (new pointers or re-quantised in place). */
 int tmt_sampler_set_weights(tmt_sampler* s, const void* Wrouter, const tmt_nvfp4_weight* Wup, const tmt_nvfp4_weight* Wdown);
 
+/* Optional: the LayerNorm in front of the block (layernorm_fwd, norm.cu:8-50; model.cu:509-514) becomes part of the
+ * step: the X rows of a slot are then the rows BEFORE the normalisation, and the router's first kernel normalises them
+ * (tmt_moe_forward_nvfp4_ln), so the step has no separate LayerNorm launch. gamma / beta: dim fp32 each, device memory,
+ * must stay valid; NULL, NULL switches it off again. Drops the recorded graphs. */
+int tmt_sampler_set_layernorm(tmt_sampler* s, const float* gamma, const float* beta);
+
 /* Device addresses of a slot's rows (streams x dim bf16): the caller's kernels write X and read Y there, ordered on
  * the session's stream. NULL for a slot outside [0, ring). */
 void* tmt_sampler_x(tmt_sampler* s, int slot);

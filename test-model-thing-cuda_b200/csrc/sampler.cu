@@ -26,6 +26,7 @@ struct tmt_sampler {
     uint16_t* Y = nullptr;           // [ring][streams][dim]
     uint16_t* warm = nullptr;        // [streams][dim] output of the warm-up step
     const void* Wr = nullptr;
+    const float* ln_gamma = nullptr; const float* ln_beta = nullptr;     // LayerNorm in front of the block (optional)
     std::vector<tmt_nvfp4_weight> up, down;
     std::vector<cudaGraphExec_t> graphs;     // per slot, nullptr until the slot's first step
     std::vector<float> graph_beta;
@@ -47,6 +48,21 @@ void moe_ok(int rc) {
 }
 
 size_t slot_elems(const tmt_sampler* s) { return (size_t)s->d.streams * s->d.dim; }
+
+// One decode step on the session's stream: with LayerNorm parameters set, X holds the rows before the normalisation.
+int queue_step(tmt_sampler* s, const uint16_t* X, uint16_t* Y, float beta) {
+    if (s->ln_gamma)
+        return tmt_moe_forward_nvfp4_ln(s->moe, X, s->ln_gamma, s->ln_beta, s->Wr, s->up.data(), s->down.data(), Y, beta, s->d.streams);
+    return tmt_moe_forward_nvfp4(s->moe, X, s->Wr, s->up.data(), s->down.data(), Y, beta, s->d.streams);
+}
+
+void warm_up(tmt_sampler* s) {
+    // outside any recording: builds the handle's weight tables (and, for batches above the small-batch limit, the bf16
+    // expansion) and the buffer of normalised rows, which involve allocations and host copies a graph cannot hold
+    moe_ok(queue_step(s, s->X, s->warm, 0.0f));
+    CKS(cudaStreamSynchronize(s->stream));
+    if (tmt_moe_device_status(s->moe) != 0) throw std::runtime_error("sampler: device status after the warm-up step");
+}
 
 void drop_graphs(tmt_sampler* s) {
     for (cudaGraphExec_t& g : s->graphs)
@@ -137,8 +153,7 @@ void record_slot(tmt_sampler* s, int slot, float beta) {
     const size_t n = slot_elems(s);
     cudaGraph_t graph = nullptr;
     CKS(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
-    const int rc = tmt_moe_forward_nvfp4(s->moe, s->X + (size_t)slot * n, s->Wr, s->up.data(), s->down.data(), s->Y + (size_t)slot * n,
-                                         beta, s->d.streams);
+    const int rc = queue_step(s, s->X + (size_t)slot * n, s->Y + (size_t)slot * n, beta);
     const cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
     if (rc != 0 || e != cudaSuccess || !graph) {
         if (graph) cudaGraphDestroy(graph);
@@ -199,11 +214,18 @@ int tmt_sampler_set_weights(tmt_sampler* s, const void* Wrouter, const tmt_nvfp4
         s->up.assign(Wup, Wup + s->d.experts);
         s->down.assign(Wdown, Wdown + s->d.experts);
         moe_ok(tmt_moe_nvfp4_weights_changed(s->moe));
-        // warm-up outside any recording: builds the handle's weight tables (and, for batches above the small-batch
-        // limit, the bf16 expansion), which involves allocations and host copies a graph cannot hold
-        moe_ok(tmt_moe_forward_nvfp4(s->moe, s->X, s->Wr, s->up.data(), s->down.data(), s->warm, 0.0f, s->d.streams));
-        CKS(cudaStreamSynchronize(s->stream));
-        if (tmt_moe_device_status(s->moe) != 0) throw std::runtime_error("sampler: device status after the warm-up step");
+        warm_up(s);
+    })
+}
+
+int tmt_sampler_set_layernorm(tmt_sampler* s, const float* gamma, const float* beta) {
+    if (!s) { set_error("null handle"); return -1; }
+    SGUARD({
+        if ((gamma == nullptr) != (beta == nullptr)) throw std::runtime_error("sampler: gamma and beta go together");
+        CKS(cudaSetDevice(s->d.device));
+        drop_graphs(s);
+        s->ln_gamma = gamma; s->ln_beta = beta;
+        if (s->Wr) warm_up(s);
     })
 }
 

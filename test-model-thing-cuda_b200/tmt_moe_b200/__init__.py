@@ -34,7 +34,7 @@ EXPORTS = (
     "tmt_ckpt_hash", "tmt_ckpt_record_bytes", "tmt_ckpt_save_param", "tmt_ckpt_load_param",
     "tmt_sampler_create", "tmt_sampler_destroy", "tmt_sampler_set_weights", "tmt_sampler_x", "tmt_sampler_y",
     "tmt_sampler_stream", "tmt_sampler_step", "tmt_sampler_upload", "tmt_sampler_download", "tmt_sampler_sync",
-    "tmt_sampler_sample", "tmt_sampler_steps", "tmt_sampler_graphs",
+    "tmt_sampler_sample", "tmt_sampler_steps", "tmt_sampler_graphs", "tmt_sampler_set_layernorm",
 )
 
 
@@ -378,6 +378,11 @@ class Sampler:
             return a
         self._keep = (Wrouter, list(Wup), list(Wdown))
         _check(self.lib.tmt_sampler_set_weights(self.h, _ptr(Wrouter), arr(Wup), arr(Wdown)), self.lib)
+
+    def set_layernorm(self, gamma, beta):
+        """The slots' X rows become the rows before the LayerNorm in front of the block (None, None: off)."""
+        self._ln = (gamma, beta)
+        _check(self.lib.tmt_sampler_set_layernorm(self.h, _ptr(gamma), _ptr(beta)), self.lib)
 
     def x_ptr(self, slot):
         return self.lib.tmt_sampler_x(self.h, slot)

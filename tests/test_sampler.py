@@ -94,6 +94,22 @@ def test_session_steps_equal_direct_calls_on_every_slot():
     # slot 0 holds batch `ring`'s input and output from the second round: beta = 1 doubles it (up to one bf16 rounding)
     ref = 2.0 * O.bf16_to_f32(want[ring])
     assert synth.rel_l2(acc, ref) <= 4e-3
+    # with the LayerNorm in front of the block taken into the step: the slot's X rows are the rows before it
+    gamma = torch.from_numpy((1 + 0.1 * rng.standard_normal(D)).astype(np.float32)).cuda()
+    beta_ln = torch.from_numpy((0.1 * rng.standard_normal(D)).astype(np.float32)).cuda()
+    ses.set_layernorm(gamma, beta_ln)
+    Xn = torch.zeros((S, D), dtype=torch.int16, device="cuda")
+    mean, rstd = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+    M.ln_forward(G.dev(batches[1]), gamma, beta_ln, Xn, mean, rstd)
+    Yd = torch.zeros((S, D), dtype=torch.int16, device="cuda")
+    moe.forward_nvfp4(Xn, Wr, up_q, down_q, Yd)
+    torch.cuda.synchronize()
+    for _ in range(2):
+        ses.upload(1, hx[1])
+        ses.step(1, 0.0)
+        ses.download(1, hy[1])
+    ses.sync()
+    np.testing.assert_array_equal(hy[1].numpy().view(np.uint16), G.host_u16(Yd))
     ses.close()
     with pytest.raises(M.MoeError):
         M.Sampler(S, D, 0, E, K)                                  # reference-mode experts have no NVFP4 path
