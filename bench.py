@@ -746,6 +746,10 @@ def main():
                 clocks=clocks, gpu_launches=launches if not graph_info.get("cuda_graph") else launches0_per_loop * args.steps,
                 roofline=roofline, hbm_kernels=hbm, **({"nvlink_kernels": nvlink} if nvlink else {}),
                 phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})
+    if clocks and clocks.get("sm_mhz"):
+        # the step runs under the power cap, whose clock differs from box to box: ms x median SM MHz (= millions of SM
+        # cycles per step) compares runs taken at different clocks
+        line["mcycles_per_step"] = ms * clocks["sm_mhz"] * 1e-3
     line.update(graph_info)
     if cfg.get("nvfp4"):
         line["dtype"] = "nvfp4 weights, bf16 activations"
