@@ -59,8 +59,6 @@ struct GemmParams {
     const float* row_scale;       // kEpiDown
     const float* expert_scale;    // optional per-expert factor (NVFP4 tensor scale), may be NULL
     const uint16_t* P;            // kEpiDh
-    const CUtensorMap* mapP;      // kEpiDh, optional: tensor map of P (box 32 columns x 128 rows, 64-byte swizzle); with it the
-                                  // CTA-pair kernel fetches the saved pre-activations chunk by chunk with TMA
     float* sw_part; int sw_ld;    // kEpiDh: per-row partial sums, one per kEpiCols columns
     // output tensor maps (device memory): with mapC0 set, the tcgen05 kernels stage every output chunk in
     // shared memory and write it with TMA stores; index = expert * c_stride. kEpiUp: mapC0 = SiLU output,

@@ -5,9 +5,7 @@
 // Four warps form a group (one warp per 32-lane quarter of TMEM). The bf16 epilogues run two groups,
 // each draining 128 of the 256 columns through two 8 KB staging buffers (128 rows x 64 bytes, 64-byte
 // swizzle); the fp32 epilogue runs one group with two 16 KB buffers (128 rows x 128 bytes, 128-byte
-// swizzle). The swizzles are the ones the output tensor maps expect. In the CTA-pair kernel the up-projection
-// (two outputs) has two buffers per output and group, and the dH product has two more per group into which
-// the saved pre-activations arrive by TMA, two chunks ahead of the chunk being computed.
+// swizzle). The swizzles are the ones the output tensor maps expect.
 #pragma once
 #include "gemm.cuh"
 #include "tc_util.cuh"
@@ -23,13 +21,6 @@ struct EpiState {
     int use = 0;
     int quarter, half, lane;
     bool issuer, staged;
-    bool up_double = false;  // kEpiUp with two outputs: each output has two staging buffers of its own (4 x 8 KB per group)
-    // kEpiDh with a tensor map of P: this group's two 8 KB buffers for chunks of saved pre-activations, their "landed"
-    // barriers, the parity each buffer's next wait expects, which buffers have a load in flight (issuer only), and the
-    // tile after the current one (the fetch runs two chunks ahead, across the tile boundary)
-    bool p_tma = false;
-    uint32_t pbuf = 0, pbar[2] = {0, 0}, pph = 0, ppend = 0;
-    bool next_valid = false; int next_row0 = 0, next_tcol0 = 0;
     volatile int* abort_flag;
 };
 
@@ -84,18 +75,9 @@ __device__ __forceinline__ void epi_math32(float (&v)[kChunk], float es, float r
     }
 }
 
-// Issues the TMA load of one 32-column chunk of saved pre-activations (rows row0.., columns col..) into buffer b.
-__device__ __forceinline__ void epi_fetch_p(const GemmParams& p, EpiState& s, int b, int col, int row0) {
-    const uint32_t bar = b ? s.pbar[1] : s.pbar[0];         // no runtime-indexed array: it would live in local memory
-    tc::mbar_expect_tx(bar, kStagingBytes / 2);
-    tc::tma_load_2d(s.pbuf + (uint32_t)b * (kStagingBytes / 2), p.mapP, bar, col, row0);
-    s.ppend |= 1u << b;
-}
-
 // Staged bf16 epilogue: 8 warps in two groups, each group drains 128 of the tile's 256 columns in chunks of 32
 // (64 bytes per row, 64-byte swizzle, one 8 KB TMA store per chunk and output). A group owns two 8 KB buffers:
-// the two outputs of kEpiUp (single-buffered: the single-CTA kernel), or one output double-buffered; with
-// s.up_double four, so that both outputs of kEpiUp are double-buffered. Returns false when a wait ran out.
+// the two outputs of kEpiUp (single-buffered), or one output double-buffered. Returns false when a wait ran out.
 template <int EPI>
 __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s, int expert, int row0, int tcol0, int nkb,
                                                uint32_t tm, bool row_ok, float& sw) {
@@ -106,8 +88,7 @@ __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s,
     const bool two = EPI == kEpiUp && p.mapC1 != nullptr;
     const CUtensorMap* m0 = p.mapC0 + (size_t)expert * p.c_stride;
     const CUtensorMap* m1 = two ? p.mapC1 + (size_t)expert * p.c_stride : nullptr;
-    const bool twin = two && s.up_double;          // both outputs double-buffered: the flow of the single-output epilogues
-    const uint32_t gbuf = s.cbuf + (uint32_t)s.half * (s.up_double ? 2 * kStagingBytes : kStagingBytes);
+    const uint32_t gbuf = s.cbuf + (uint32_t)s.half * kStagingBytes;
     const uint32_t rbase = (uint32_t)r_in_tile * 64u, rsw = (uint32_t)(r_in_tile >> 1) & 3u;
     const float es = p.expert_scale ? p.expert_scale[expert] : 1.0f;
     float rs = 1.0f;
@@ -117,14 +98,7 @@ __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s,
     const uint16_t* prow = nullptr;
     if constexpr (EPI == kEpiDh) {
         prow = p.P + row * p.ldc;
-        if (s.p_tma && s.issuer) {
-            // chunks 0 and 1 of this tile normally arrive from the previous tile's look-ahead; whatever is missing (first
-            // tile, or a previous tile without chunks for this group) is requested here
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-                if (c_first + b * kCols < p.N && !(s.ppend >> b & 1u)) epi_fetch_p(p, s, b, c_first + b * kCols, row0);
-        }
-        if (!s.p_tma && c_first < p.N) {
+        if (c_first < p.N) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) pw[q] = ldg16(prow + c_first + q * 8);
         }
@@ -141,23 +115,8 @@ __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s,
         }
         uint32_t w0[kChunk / 2], w1[kChunk / 2];
         uint4 pnext[4] = {};
-        if constexpr (EPI == kEpiDh) {
-            if (s.p_tma) {                   // this chunk's pre-activations were fetched by TMA two chunks ago
-                const int b = cc & 1;
-                const bool ok = mbar_wait(b ? s.pbar[1] : s.pbar[0], (s.pph >> b) & 1u, s.abort_flag, p.status);
-                s.pph ^= 1u << b;
-                s.ppend &= ~(1u << b);
-                if (!__all_sync(0xffffffffu, ok)) return false;
-                const uint32_t pb = s.pbuf + (uint32_t)b * (kStagingBytes / 2);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t a = pb + rbase + (((uint32_t)q ^ rsw) << 4);
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pw[q].x), "=r"(pw[q].y), "=r"(pw[q].z), "=r"(pw[q].w) : "r"(a) : "memory");
-                }
-            }
-        }
         if constexpr (EPI == kEpiDh) {       // the next chunk's saved pre-activations travel while this chunk is computed
-            if (!s.p_tma && cc + 1 < kEpiCols / kCols && ccol0 + kCols < p.N) {
+            if (cc + 1 < kEpiCols / kCols && ccol0 + kCols < p.N) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) pnext[q] = ldg16(prow + ccol0 + kCols + q * 8);
             }
@@ -168,14 +127,12 @@ __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s,
             for (int i = 0; i < kChunk / 2; ++i) { w0[i] = 0; w1[i] = 0; }
         }
         if constexpr (EPI == kEpiDh) {
-            if (!s.p_tma) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) pw[q] = pnext[q];
-            }
+            for (int q = 0; q < 4; ++q) pw[q] = pnext[q];
         }
-        const uint32_t b0 = gbuf + ((two && !twin) ? 0u : (uint32_t)(s.use & 1) * (kStagingBytes / 2));
-        const uint32_t b1 = twin ? gbuf + kStagingBytes + (uint32_t)(s.use & 1) * (kStagingBytes / 2) : gbuf + kStagingBytes / 2;
-        if (two && !twin) {      // both buffers are reused every chunk: the previous pair of stores must have read them
+        const uint32_t b0 = gbuf + (two ? 0u : (uint32_t)(s.use & 1) * (kStagingBytes / 2));
+        const uint32_t b1 = gbuf + kStagingBytes / 2;
+        if (two) {      // both buffers are reused every chunk: the previous pair of stores must have read them
             if (s.issuer) bulk_wait_read<0>();
             if (!epi_group_sync(s, p.status)) return false;
         }
@@ -187,26 +144,12 @@ __device__ __forceinline__ bool epi_drain_bf16(const GemmParams& p, EpiState& s,
         }
         fence_async_smem();
         // double-buffered: the store of the previous chunk has read its buffer before anyone writes the next chunk there
-        if ((!two || twin) && s.issuer) bulk_wait_read<0>();
+        if (!two && s.issuer) bulk_wait_read<0>();
         if (!epi_group_sync(s, p.status)) return false;
         if (s.issuer && !TMT_DBG(p, 4)) {
             tma_store_2d(m0, b0, ccol0, row0);
             if (two) tma_store_2d(m1, b1, ccol0, row0);
             bulk_commit();
-        }
-        if constexpr (EPI == kEpiDh) {
-            // Every warp of the group has read buffer cc & 1 (they all passed the group barrier above): the chunk two
-            // ahead may land there. Past this tile's last chunk that is a chunk of the next tile.
-            if (s.p_tma && s.issuer) {
-                // chunks this group has in this tile: 0, 2 or 4 (N is a multiple of 64, a chunk is 32 columns)
-                const int nv = c_first >= p.N ? 0 : min(kEpiCols / kCols, (p.N - c_first) / kCols);
-                const int tgt = cc + 2;
-                if (tgt < nv) epi_fetch_p(p, s, cc & 1, c_first + tgt * kCols, row0);
-                else if (s.next_valid) {
-                    const int ncol = s.next_tcol0 + s.half * kEpiCols + (tgt - nv) * kCols;
-                    if (ncol < p.N) epi_fetch_p(p, s, cc & 1, ncol, s.next_row0);
-                }
-            }
         }
         ++s.use;
     }

@@ -28,13 +28,6 @@ namespace {
 using namespace tc;
 
 constexpr int kStages2 = 6;                     // three pairs
-// Pipeline stages per epilogue kind. The up-projection (two outputs per tile) gives two stages to its epilogue: with
-// four staging buffers per warp group each output is double-buffered, and the epilogue, which bounds that launch, no
-// longer waits for a TMA store to finish reading before it may write the next chunk.
-// The dH product gives them to two buffers per warp group for the saved pre-activations its epilogue reads, fetched by
-// TMA two chunks ahead (per-thread 64-byte global loads took their place on the load path before).
-template <int EPI> __host__ __device__ constexpr int stages2() { return (EPI == kEpiUp || EPI == kEpiDh) ? 4 : kStages2; }
-template <int EPI> __host__ __device__ constexpr int staging_bytes2() { return ((EPI == kEpiUp || EPI == kEpiDh) ? 4 : 2) * kStagingBytes; }
 constexpr int kATile2 = kBM * kBK * 2;          // 16 KB: this CTA's 128 rows
 constexpr int kBTile2 = (kBN / 2) * kBK * 2;    // 16 KB: this CTA's 128 of the 256 columns
 constexpr int kStageBytes2 = kATile2 + kBTile2;
@@ -132,8 +125,7 @@ __device__ __forceinline__ bool get_tile2_nkb(const GemmParams& p, int t, int m_
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    constexpr int kSt = stages2<EPI>();
-    __shared__ uint64_t full_bar[kStages2 / 2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2], group_bar[2], p_bar[2][2];
+    __shared__ uint64_t full_bar[kStages2 / 2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2], group_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -145,10 +137,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
 
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < kSt / 2; ++s) mbar_init(smem_u32(&full_bar[s]), 2);    // one leader arrival per stage of the pair
-        for (int s = 0; s < kSt; ++s) mbar_init(smem_u32(&empty_bar[s]), 1);
+        for (int s = 0; s < kStages2 / 2; ++s) mbar_init(smem_u32(&full_bar[s]), 2);    // one leader arrival per stage of the pair
+        for (int s = 0; s < kStages2; ++s) mbar_init(smem_u32(&empty_bar[s]), 1);
         for (int a = 0; a < 2; ++a) mbar_init(smem_u32(&group_bar[a]), 4);
-        for (int a = 0; a < 2; ++a) for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&p_bar[a][b]), 1);
         for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull_bar[a]), 1); mbar_init(smem_u32(&tempty_bar[a]), 2 * epi_warps<EPI>()); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -188,7 +179,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
             __syncwarp();
             const int bcol0 = ti.col0 + rank * (kBN / 2);
             for (int kb = 0; kb < ti.nkb; ++kb) {
-                if ((s & 1) != my) { if (++s == kSt) { s = 0; ph ^= 1; } continue; }     // the other producer's stage
+                if ((s & 1) != my) { if (++s == kStages2) { s = 0; ph ^= 1; } continue; }     // the other producer's stage
                 const uint32_t fb_local = smem_u32(&full_bar[s >> 1]);
                 const uint32_t fb = map_to_cta(fb_local, 0);              // the leader's barrier
                 if (lane == 0) {
@@ -214,7 +205,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                 if (prof && lane == 0) { c_wait += t1 - t0; c_issue += clock64() - t1; }
                 issued |= 1u << (s >> 1);
                 last_parity = (last_parity & ~(1u << (s >> 1))) | (ph << (s >> 1));
-                if (++s == kSt) { s = 0; ph ^= 1; }
+                if (++s == kStages2) { s = 0; ph ^= 1; }
             }
         }
         // An odd number of k blocks leaves the last pair's barrier one arrival short: the leader's odd producer supplies it,
@@ -227,7 +218,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
         }
         if (!ok && leader && lane == 0) {
             // aborting: the leader's barriers count both CTAs' copies; wait (bounded) for what was announced
-            for (int q = 0; q < kSt / 2; ++q) {
+            for (int q = 0; q < kStages2 / 2; ++q) {
                 if (!(issued >> q & 1)) continue;
                 const long long t0 = clock64();
                 while (!mbar_try_wait(smem_u32(&full_bar[q]), (last_parity >> q) & 1) && clock64() - t0 < kWaitCycles) {}
@@ -274,7 +265,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
                     }
                     __syncwarp();
                     if (prof) { c_full += t1 - t0; c_issue += clock64() - t1; }
-                    if (++s == kSt) { s = 0; ph ^= 1; }
+                    if (++s == kStages2) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
                 if (elect_one()) {
@@ -302,14 +293,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
         es.lane = lane;
         es.staged = p.mapC0 != nullptr && !TMT_DBG(p, 8);
         es.issuer = ((warp - 2) & 3) == 0 && lane == 0;
-        es.cbuf = tiles_s + kSt * kStageBytes2;
-        es.up_double = EPI == kEpiUp;
-        if constexpr (EPI == kEpiDh) {
-            es.p_tma = p.mapP != nullptr && es.staged;
-            es.pbuf = es.cbuf + 2 * kStagingBytes + (uint32_t)es.half * kStagingBytes;
-            es.pbar[0] = smem_u32(&p_bar[es.half][0]); es.pbar[1] = smem_u32(&p_bar[es.half][1]);
-            if (es.p_tma && es.issuer) tensormap_acquire(p.mapP);
-        }
+        es.cbuf = tiles_s + kStages2 * kStageBytes2;
         es.gbar = smem_u32(&group_bar[es.half]);
         es.abort_flag = abort_flag;
         const bool prof = p.cyc != nullptr && warp == 2 && lane == 0;
@@ -328,11 +312,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
             const long row = (long)ti.row0 + es.quarter * 32 + lane;
             const bool row_ok = (p.mode == kRowsRagged) ? (row < (long)(p.tile_begin + m_tiles_in_use) * kBM) : (row < p.M);
             const uint32_t tm = tmem_base + ((uint32_t)(es.quarter * 32) << 16) + (uint32_t)(acc * kBN);
-            if constexpr (EPI == kEpiDh) {
-                Tile2 nx;
-                es.next_valid = es.p_tma && get_tile2(p, t + npairs, m_pairs, n_tiles, rank, nx);
-                es.next_row0 = nx.row0; es.next_tcol0 = nx.col0;
-            }
             if (!epi_drain_tile<EPI, kGroups>(p, es, ti.expert, ti.row0, ti.col0, ti.nkb, tm, row_ok)) break;
             tc_fence_before();
             __syncwarp();
@@ -342,14 +321,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
         }
         if (prof) { p.cyc[blockIdx.x * kCycSlots + kCycEpiWaitAcc] = c_wait; p.cyc[blockIdx.x * kCycSlots + kCycEpiWork] = c_work; }
         if (es.staged && es.issuer) bulk_wait_all();
-        if (es.p_tma && es.issuer && es.ppend) {
-            // leaving early (a wait ran out): fetches still in flight must land before this CTA's shared memory goes away
-            for (int b = 0; b < 2; ++b) {
-                if (!(es.ppend >> b & 1u)) continue;
-                const long long t0 = clock64();
-                while (!mbar_try_wait(b ? es.pbar[1] : es.pbar[0], (es.pph >> b) & 1u) && clock64() - t0 < kWaitCycles) {}
-            }
-        }
     }
     tc_fence_before();
     __syncthreads();
@@ -362,7 +333,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>()
 
 template <int EPI>
 cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
-    const size_t smem = (size_t)stages2<EPI>() * kStageBytes2 + staging_bytes2<EPI>() + 1024;
+    const size_t smem = gemm_tcgen05_2cta_smem_bytes();
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gemm_tcgen05_2cta_kernel<EPI><<<grid, block_threads<EPI>(), smem, stream>>>(p);

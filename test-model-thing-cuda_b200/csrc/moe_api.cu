@@ -403,7 +403,6 @@ void expert_backward(tmt_moe* h, const void* const* Wup, const void* const* Wdow
         if (which & 1) {
             GemmParams dh = rows_gemm(h, kDYgK, h->dYg, kDownMN, h->down_ptrs, true, H, D, kEpiDh);
             dh.out0 = h->dP; dh.P = h->P; dh.sw_part = h->sw_part; dh.sw_ld = h->sw_ld;
-            if (h->two_cta) dh.mapP = h->act_maps + kOutP;
             dh.mapC0 = h->act_maps + kOutDP;
             dh.tile_begin = tile_begin; dh.tile_count = tile_count;
             prof_mark(h, kPhGemmDh);
