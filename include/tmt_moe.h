@@ -54,7 +54,10 @@ typedef struct tmt_moe_desc {
     int ep_world;      /* expert-parallel ranks (1 = all experts local)                    */
     int ep_rank;       /* this rank; it owns experts [rank*E/world, (rank+1)*E/world)        */
     float ep_capacity_factor; /* expert-parallel only: rows other ranks may route to this rank's
-                          experts, as a multiple of tokens*topk (0 = 1.5); a step that needs more fails */
+                          experts, as a multiple of tokens*topk (0 = 1.5); a step that needs more fails on every rank:
+                          with -1 from the call where the exchange plan is made on the host (NCCL transport, expert
+                          waves), through tmt_moe_device_status (code 4) where it is made on the device (peer transport:
+                          the step then has no host synchronisation; rows past the capacity are not touched)        */
     int ep_transport;  /* TMT_MOE_EP_PEER: gather / scatter kernels address the owners' buffers over NVLink
                           (CUDA IPC peer memory); TMT_MOE_EP_NCCL: NCCL send / recv exchanges                 */
 } tmt_moe_desc;
@@ -152,8 +155,9 @@ int tmt_moe_usage(tmt_moe* h, double* min_share, double* max_share, long long* d
  * ([launch % *launches][cta < *ctas][slot < *slots] long long) to `out` (may be NULL to query the
  * sizes) and returns the number of GEMM launches so far, -1 when the counters are off. Synchronises. */
 int tmt_moe_debug_gemm_cycles(tmt_moe* h, long long* out, int* launches, int* ctas, int* slots);
-/* Device-side status word: 0 when no kernel reported a bounds violation or a wait that ran
- * out; otherwise the first code recorded. Synchronises. */
+/* Device-side status word: 0 when no kernel reported a problem; otherwise the first code recorded: 1 an index left its
+ * range, 2 a bounded wait ran out, 3 tensor memory could not be allocated, 4 an expert-parallel step routed more rows
+ * to a rank than its capacity. Synchronises. */
 int tmt_moe_device_status(tmt_moe* h);
 
 /* Failure-detection self-test (no counterpart in the reference): launches one block that waits on a

@@ -28,6 +28,7 @@ enum Status : int {
     kErrSlotRange = 1,     // a slot / expert / token index left its range
     kErrWaitTimeout = 2,   // a bounded mbarrier wait ran out
     kErrTmemAlloc = 3,
+    kErrCapacity = 4,      // expert parallel: more rows were routed to a rank than its grouped buffers hold
 };
 
 __device__ __forceinline__ void report(int* status, int code) {

@@ -73,6 +73,10 @@ struct tmt_ep_state {
     std::vector<int> dest_row0_host;
     uint16_t* Xc = nullptr;           // [T_pad][D] X in token order (router weight gradient)
     int* bar_word = nullptr;
+    // Peer transport without expert waves: the exchange plan is computed on the device from the gathered counts, and the
+    // step has no host synchronisation. TMT_MOE_EP_HOST_PLAN=1 keeps the host plan (measurement; the NCCL transport and
+    // expert waves always use it: their message sizes and tile ranges are host values).
+    bool device_plan = false;
 };
 
 namespace tmt {
@@ -219,6 +223,8 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
             if (const char* sm = getenv("TMT_MOE_EP_SMS")) ep->side_sms = std::max(0, std::min(atoi(sm), h->num_sms / 2));
             if (const char* wv = getenv("TMT_MOE_EP_WAVES")) ep->waves = std::max(1, std::min(atoi(wv), (int)tmt_ep_state::kMaxWaves));
             ep->waves = std::min(ep->waves, ep->EL);
+            const char* hp = getenv("TMT_MOE_EP_HOST_PLAN");
+            ep->device_plan = ep->waves < 2 && E <= 256 && ep->G <= 256 && !(hp && atoi(hp) != 0);
             for (int w = 0; w < tmt_ep_state::kMaxWaves; ++w) {
                 CKE(cudaEventCreateWithFlags(&ep->ev_sent[w], cudaEventDisableTiming));
                 CKE(cudaEventCreateWithFlags(&ep->ev_done[w], cudaEventDisableTiming));
@@ -305,8 +311,75 @@ void ep_teardown(tmt_moe* h) {
 
 namespace {
 
+// The exchange plan on the device, one block: what plan_step computes on the host (tmt_moe_ep_plan for every owner,
+// the capacity check, the tile table) from cnt_all[g][e] = rows rank g routes to expert e. tables = [EL+1] padded group
+// starts | [EL] counts | [1] number of 128-row tiles | [max_tiles] tile -> local expert (-1 past the end).
+__global__ void __launch_bounds__(256) ep_plan_kernel(int G, int r, int E, int EL, int pad, int x_cap, int max_tiles,
+                                                      const int* __restrict__ cnt_all, int* __restrict__ tables,
+                                                      int* __restrict__ dest_row0, int* __restrict__ world, int* status) {
+    __shared__ int tot[256], padded[256], before_me[256], opoff[257];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int n = 0, mine = 0;
+        for (int g = 0; g < G; ++g) {
+            const int c = cnt_all[g * E + e];
+            if (g < r) mine += c;            // rows of lower ranks come first inside the owner's group (source order)
+            n += c;
+        }
+        tot[e] = n; before_me[e] = mine;
+        padded[e] = (n + pad - 1) / pad * pad;
+        world[e] = n;
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {                   // one thread per owner: padded starts of its EL groups, capacity check
+        const int g = threadIdx.x;
+        long long p = 0;
+        for (int le = 0; le < EL; ++le) { opoff[g * EL + le] = (int)p; p += padded[g * EL + le]; }
+        if (p > x_cap) report(status, kErrCapacity);
+        if (g == r) opoff[256] = (int)(p > x_cap ? x_cap / pad * pad : p);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) dest_row0[e] = opoff[e] + before_me[e];
+    const int rows = opoff[256];
+    for (int le = threadIdx.x; le < EL; le += blockDim.x) {
+        tables[le] = min(opoff[r * EL + le], rows);
+        tables[EL + 1 + le] = tot[r * EL + le];
+    }
+    if (threadIdx.x == 0) { tables[EL] = rows; tables[2 * EL + 1] = rows / kPad; }
+    int* te = tables + 2 * EL + 2;
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) {
+        const int row = i * kPad;
+        int le = -1;
+        if (row < rows)
+            for (int q = 0; q < EL; ++q)
+                if (row >= opoff[r * EL + q] && row < opoff[r * EL + q] + padded[r * EL + q]) le = q;
+        te[i] = le;
+    }
+}
+
+// Pad rows of the expert-side groups read as zero (they feed the weight-gradient GEMMs): block = one local expert,
+// rows from the device tables.
+__global__ void __launch_bounds__(256) ep_zero_pads_kernel(const int* __restrict__ tables, int EL, uint16_t* __restrict__ buf, int width,
+                                                           int x_cap) {
+    const int le = blockIdx.x;
+    const long r0 = (long)tables[le] + tables[EL + 1 + le], r1 = min(tables[le + 1], x_cap);
+    const long n = (r1 - r0) * (width / 8);
+    uint4* dst = reinterpret_cast<uint4*>(buf + r0 * width);
+    for (long i = threadIdx.x; i < n; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+}
+
+void plan_step_device(tmt_moe* h) {
+    tmt_ep_state* ep = h->ep;
+    const int E = h->d.experts;
+    NC(ep, ep->AllGather(h->rb.counts, ep->cnt_all_dev, E, ncclInt32, ep->comm, h->stream));
+    ep_plan_kernel<<<1, 256, 0, h->stream>>>(ep->G, ep->r, E, ep->EL, h->pad, ep->x_cap, ep->x_max_tiles, ep->cnt_all_dev, ep->x_tables,
+                                             ep->dest_row0, h->ep_world_counts, h->rb.status);
+    CKE(cudaGetLastError());
+    h->launches += 2;
+}
+
 // Counts of every rank -> host, exchange plan, expert-side tables -> device. One stream sync.
 void plan_step(tmt_moe* h) {
+    if (h->ep->device_plan) { plan_step_device(h); return; }
     tmt_ep_state* ep = h->ep;
     const int E = h->d.experts, G = ep->G, EL = ep->EL;
     NC(ep, ep->AllGather(h->rb.counts, ep->cnt_all_dev, E, ncclInt32, ep->comm, h->stream));
@@ -350,6 +423,12 @@ void plan_step(tmt_moe* h) {
 // Pad rows of the expert-side groups must read as zero (they feed the weight-gradient GEMMs).
 void zero_pads(tmt_moe* h, uint16_t* buf, int width) {
     tmt_ep_state* ep = h->ep;
+    if (ep->device_plan) {
+        ep_zero_pads_kernel<<<ep->EL, 256, 0, h->stream>>>(ep->x_tables, ep->EL, buf, width, ep->x_cap);
+        CKE(cudaGetLastError());
+        h->launches += 1;
+        return;
+    }
     for (int le = 0; le < ep->EL; ++le) {
         const size_t r0 = (size_t)ep->x_poff[le] + ep->x_counts[le], r1 = ep->x_poff[le + 1];
         if (r1 > r0) CKE(cudaMemsetAsync(buf + r0 * width, 0, (r1 - r0) * width * 2, h->stream));
@@ -391,6 +470,7 @@ void rank_barrier(tmt_moe* h, cudaStream_t stream = nullptr) {
 PeerMap peer_map(tmt_moe* h, uint16_t** table, bool beside_gemm = false) {
     PeerMap pm;
     pm.base = table; pm.dest_row0 = h->ep->dest_row0; pm.experts_per_rank = h->ep->EL;
+    pm.row_limit = h->ep->x_cap; pm.status = h->rb.status;
     if (beside_gemm && h->ep->side_sms > 0) pm.pad_smem = 4096;
     return pm;
 }

@@ -49,6 +49,10 @@ struct PeerMap {
     // Only assignments whose expert's index inside its owner rank lies in [wave_lo, wave_hi) move rows (the expert-
     // parallel step sends the experts in waves so that a wave's transfer runs under the previous wave's GEMMs).
     int wave_lo = 0, wave_hi = 1 << 30;
+    // Rows of an owner's grouped buffer; a row at or past it is not touched (the step's capacity check failed: with the
+    // exchange plan computed on the device the host learns of it from the status word, after the kernels have run).
+    int row_limit = 0;
+    int* status = nullptr;
     // Extra dynamic shared memory per block (unused by the kernel): with a few KB a block no longer fits beside a
     // resident GEMM CTA, so a kernel launched next to a GEMM stays on the SMs that GEMM left free.
     int pad_smem = 0;

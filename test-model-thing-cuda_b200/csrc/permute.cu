@@ -23,7 +23,9 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // Address of grouped row `slot` (token-side numbering) of expert e: local, or in the owner's buffer.
 __device__ __forceinline__ uint16_t* group_row(const PeerMap& pm, const uint16_t* local, const int* poff, int e, int slot, int D) {
     if (pm.base == nullptr) return const_cast<uint16_t*>(local) + (long)slot * D;
-    return pm.base[e / pm.experts_per_rank] + (long)(pm.dest_row0[e] + slot - poff[e]) * D;
+    const int row = pm.dest_row0[e] + slot - poff[e];
+    if (pm.row_limit > 0 && (row < 0 || row >= pm.row_limit)) { report(pm.status, kErrCapacity); return nullptr; }
+    return pm.base[e / pm.experts_per_rank] + (long)row * D;
 }
 __device__ __forceinline__ bool in_wave(const PeerMap& pm, int e) {
     const int le = e % pm.experts_per_rank;
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
         const int e = b.idx[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
         else if (!in_wave(pm, e)) slot = -1;
-        else { wj = b.slotw[slot]; row = group_row(pm, Yg, b.poff, e, slot, d.D); }
+        else { wj = b.slotw[slot]; row = group_row(pm, Yg, b.poff, e, slot, d.D); if (row == nullptr) slot = -1; }
     }
     int slots[kMaxK]; float ws[kMaxK]; const uint16_t* rows[kMaxK];
 #pragma unroll
@@ -179,7 +181,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
         const int e = b.idx[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
         else if (!in_wave(pm, e)) slot = -1;
-        else { wj = b.slotw[slot]; row = group_row(pm, dYg, b.poff, e, slot, d.D); }
+        else { wj = b.slotw[slot]; row = group_row(pm, dYg, b.poff, e, slot, d.D); if (row == nullptr) slot = -1; }
     }
     int slots[kMaxK]; float ws[kMaxK]; float sdot[kMaxK]; uint16_t* rows[kMaxK];
 #pragma unroll
