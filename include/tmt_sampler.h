@@ -70,7 +70,12 @@ void* tmt_sampler_stream(tmt_sampler* s);
 int tmt_sampler_step(tmt_sampler* s, int slot, float beta);
 
 /* Host convenience for callers whose rows start in host memory: asynchronous copies of a slot's X rows from, and Y
- * rows to, (pinned) host memory on the session's stream, and a wait for everything queued so far. */
+ * rows to, (pinned) host memory, and a wait for everything queued so far. The copies run on two streams of the
+ * session's own and are ordered against the slot's steps by events (an upload waits until the slot's last step has read
+ * its rows, a step waits for the slot's upload and for the download of its previous result, a download waits for the
+ * slot's last step), so with several ring slots the copies of neighbouring decode steps overlap a step's kernels. A
+ * caller that reads Y or writes X with kernels of its own on the session's stream, after a download or before an
+ * upload of the same slot, orders those itself (tmt_sampler_sync, or events on tmt_sampler_stream). */
 int tmt_sampler_upload(tmt_sampler* s, int slot, const void* X_host);
 int tmt_sampler_download(tmt_sampler* s, int slot, void* Y_host);
 int tmt_sampler_sync(tmt_sampler* s);

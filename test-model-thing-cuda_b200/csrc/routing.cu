@@ -148,21 +148,27 @@ __device__ __forceinline__ void route_block_finish(const RouterArgs& a, float* l
 
 // Block = 64 tokens x (TE * ESLABS) experts per expert pass; 4 * ESLABS warps. Warp = one slab of 16
 // tokens x TE experts; lane = (chain s = lane & 7, token group g = lane >> 3); a thread keeps
-// kTT x TE accumulators of its chain. X (bf16) and the router rows (fp32 split into two 16-byte
-// planes, or bf16) are staged in shared memory by cp.async, double buffered, kDC columns at a time,
-// so that the 8 chains of a group read 128 contiguous bytes.
+// kTT x TE accumulators of its chain, as kTT x TE/2 PAIRS of neighbouring experts: the products run on the packed
+// fp32 FMA of sm_100 (fma.rn.f32x2: two chains per issued instruction; each half is one round-to-nearest FMA of its
+// own chain, so the logits keep the stated bits). X (bf16) is staged in shared memory by cp.async; the router rows
+// travel through registers (loaded one chunk ahead) and are stored as fp32, two experts interleaved element by element
+// in four 16-byte planes [plane][pair][vector], so that one 16-byte load returns {w_e[d], w_e+1[d], w_e[d+1], w_e+1[d+1]}
+// and the 8 chains of a group read 128 contiguous bytes. Both double buffered, kDC columns at a time.
 template <int TE, int ESLABS, bool WF32>
 __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a) {
+    static_assert(TE % 2 == 0, "experts are processed in pairs");
     constexpr int EP = TE * ESLABS;                 // experts per pass
+    constexpr int NP = EP / 2, TP = TE / 2;         // expert pairs per pass / per thread
     constexpr int NTHR = 128 * ESLABS;
     constexpr int XS_BYTES = kTokBlock * kDC * 2;
-    constexpr int WS_BYTES = EP * kDC * (WF32 ? 4 : 2);
+    constexpr int WS_BYTES = EP * kDC * 4;
+    constexpr int WITEMS = (EP * (kDC / 8) + NTHR - 1) / NTHR;      // (expert row, 8-column vector) items a thread stages per chunk
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* stage[2] = {smem, smem + XS_BYTES + WS_BYTES};
     float* lg = reinterpret_cast<float*>(smem + 2 * (XS_BYTES + WS_BYTES));     // [kTokBlock][E]
     __shared__ int sidx[kTokBlock * 8];
     __shared__ float zs[kTokBlock];
-    const int E = a.E, K = a.K, D = a.D;
+    const int E = a.E, D = a.D;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int s = lane & 7, g = lane >> 3;
     const int tslab = warp & 3, eslab = warp >> 2;
@@ -172,42 +178,72 @@ __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a
     const unsigned full = 0xffffffffu;
 
     for (int ep0 = 0; ep0 < E; ep0 += EP) {
-        auto load_chunk = [&](int k, uint8_t* buf) {
-            const int v0 = k * (kDC / 8);
-            // X: 64 rows x 16 vectors of 16 bytes
-            for (int q = threadIdx.x; q < kTokBlock * (kDC / 8); q += NTHR) {
-                const int row = q >> 4, v = q & 15;
-                const long t = tok0 + row;
-                const bool ok = t < a.T && v0 + v < nvec;
-                cp_async16(buf + (row * (kDC / 8) + v) * 16, a.X + (ok ? t * D + (long)(v0 + v) * 8 : 0), ok);
-            }
-            uint8_t* wb = buf + XS_BYTES;
-            if constexpr (WF32) {
-                // fp32 rows: vector v = two 16-byte halves, stored in two planes [half][expert][vector]
-                for (int q = threadIdx.x; q < EP * (kDC / 4); q += NTHR) {
-                    const int row = q >> 5, piece = q & 31, v = piece >> 1, half = piece & 1;
-                    const bool ok = ep0 + row < E && v0 + v < nvec;
-                    const float* src = reinterpret_cast<const float*>(a.Wr) + (ok ? (long)(ep0 + row) * D + (long)(v0 + v) * 8 + half * 4 : 0);
-                    cp_async16(wb + ((half * EP + row) * (kDC / 8) + v) * 16, src, ok);
-                }
-            } else {
-                for (int q = threadIdx.x; q < EP * (kDC / 8); q += NTHR) {
-                    const int row = q >> 4, v = q & 15;
-                    const bool ok = ep0 + row < E && v0 + v < nvec;
-                    const uint16_t* src = reinterpret_cast<const uint16_t*>(a.Wr) + (ok ? (long)(ep0 + row) * D + (long)(v0 + v) * 8 : 0);
-                    cp_async16(wb + (row * (kDC / 8) + v) * 16, src, ok);
-                }
+        // X: 64 rows x 16 vectors of 16 bytes by cp.async. A thread copies the same vector column of every (NTHR / 16)-th
+        // row, so its source and destination advance by constants (no per-piece index arithmetic).
+        auto load_x = [&](int k, uint8_t* buf) {
+            constexpr int kRowStep = NTHR / 16, kPieces = kTokBlock / kRowStep;
+            const int xv = threadIdx.x & 15, xr = threadIdx.x >> 4;
+            const bool col_ok = k * (kDC / 8) + xv < nvec;
+            const uint16_t* src = a.X + (tok0 + xr) * D + (long)(k * (kDC / 8) + xv) * 8;
+            uint8_t* dst = buf + (xr * (kDC / 8) + xv) * 16;
+#pragma unroll
+            for (int j = 0; j < kPieces; ++j) {
+                const bool ok = col_ok && tok0 + xr + j * kRowStep < a.T;
+                cp_async16(dst + j * kRowStep * (kDC / 8) * 16, ok ? src + (long)j * kRowStep * D : a.X, ok);
             }
             cp_async_commit();
         };
-        float acc[kTT][TE];
+        // router rows: item = (expert row of the pass, vector of 8 columns) -> 8 fp32 values in registers
+        float wreg[WITEMS][8];
+        auto load_w = [&](int k) {
+            const int v0 = k * (kDC / 8);
+#pragma unroll
+            for (int it = 0; it < WITEMS; ++it) {
+                const int q = threadIdx.x + it * NTHR;
+                const int row = q >> 4, v = q & 15;
+                const bool ok = q < EP * (kDC / 8) && ep0 + row < E && v0 + v < nvec;
+                if (ok) {
+                    if constexpr (WF32) {
+                        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.Wr) + (long)(ep0 + row) * D + (long)(v0 + v) * 8);
+                        const float4 w0 = __ldg(src), w1 = __ldg(src + 1);
+                        wreg[it][0] = w0.x; wreg[it][1] = w0.y; wreg[it][2] = w0.z; wreg[it][3] = w0.w;
+                        wreg[it][4] = w1.x; wreg[it][5] = w1.y; wreg[it][6] = w1.z; wreg[it][7] = w1.w;
+                    } else {
+                        const uint4 w = ldg16(reinterpret_cast<const uint16_t*>(a.Wr) + (long)(ep0 + row) * D + (long)(v0 + v) * 8);
+                        wreg[it][0] = bf_lo(w.x); wreg[it][1] = bf_hi(w.x); wreg[it][2] = bf_lo(w.y); wreg[it][3] = bf_hi(w.y);
+                        wreg[it][4] = bf_lo(w.z); wreg[it][5] = bf_hi(w.z); wreg[it][6] = bf_lo(w.w); wreg[it][7] = bf_hi(w.w);
+                    }
+                } else {
+#pragma unroll
+                    for (int q8 = 0; q8 < 8; ++q8) wreg[it][q8] = 0.0f;
+                }
+            }
+        };
+        // element (row, column 8v + q) -> plane q / 2, pair row / 2, vector v, float (q % 2) * 2 + row % 2
+        auto store_w = [&](uint8_t* buf) {
+            float* wsm = reinterpret_cast<float*>(buf + XS_BYTES);
+#pragma unroll
+            for (int it = 0; it < WITEMS; ++it) {
+                const int q = threadIdx.x + it * NTHR;
+                if (q < EP * (kDC / 8)) {
+                    const int row = q >> 4, v = q & 15;
+                    float* dst = wsm + ((row >> 1) * (kDC / 8) + v) * 4 + (row & 1);
+#pragma unroll
+                    for (int q8 = 0; q8 < 8; ++q8) dst[(q8 >> 1) * (NP * (kDC / 8) * 4) + (q8 & 1) * 2] = wreg[it][q8];
+                }
+            }
+        };
+        float2 acc[kTT][TP];
 #pragma unroll
         for (int i = 0; i < kTT; ++i)
 #pragma unroll
-            for (int e = 0; e < TE; ++e) acc[i][e] = 0.0f;
-        load_chunk(0, stage[0]);
+            for (int e = 0; e < TP; ++e) acc[i][e] = make_float2(0.0f, 0.0f);
+        load_x(0, stage[0]);
+        load_w(0);
+        store_w(stage[0]);
         for (int k = 0; k < nchunks; ++k) {
-            if (k + 1 < nchunks) { load_chunk(k + 1, stage[(k + 1) & 1]); cp_async_wait<1>(); }
+            const bool more = k + 1 < nchunks;
+            if (more) { load_x(k + 1, stage[(k + 1) & 1]); load_w(k + 1); cp_async_wait<1>(); }
             else cp_async_wait<0>();
             __syncthreads();
             const uint32_t xb = (uint32_t)__cvta_generic_to_shared(stage[k & 1]);
@@ -216,37 +252,44 @@ __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a
             for (int c = 0; c < 2; ++c) {
                 const int v = c * 8 + s;                         // this chain's vector inside the chunk
                 if (k * (kDC / 8) + c * 8 < nvec) {              // uniform: nvec is a multiple of 8
-                    float x[kTT][8];
                     const uint32_t xa = xb + (uint32_t)(((tslab * 16 + g * kTT) * (kDC / 8) + v) * 16);
-                    const uint32_t wa = wb + (uint32_t)(((eslab * TE) * (kDC / 8) + v) * 16);
-                    auto unpack = [&](const uint4 xv, float (&f)[8]) {
-                        f[0] = bf_lo(xv.x); f[1] = bf_hi(xv.x); f[2] = bf_lo(xv.y); f[3] = bf_hi(xv.y);
-                        f[4] = bf_lo(xv.z); f[5] = bf_hi(xv.z); f[6] = bf_lo(xv.w); f[7] = bf_hi(xv.w);
-                    };
+                    const uint32_t wa = wb + (uint32_t)(((eslab * TP) * (kDC / 8) + v) * 16);
                     static_assert(kTT == 4, "token rows are unrolled by hand");
-                    unpack(lds16<0 * (kDC / 8) * 16>(xa), x[0]);
-                    unpack(lds16<1 * (kDC / 8) * 16>(xa), x[1]);
-                    unpack(lds16<2 * (kDC / 8) * 16>(xa), x[2]);
-                    unpack(lds16<3 * (kDC / 8) * 16>(xa), x[3]);
-                    auto expert = [&](auto E_) {
-                        constexpr int e = decltype(E_)::value;
-                        float w[8];
-                        if constexpr (WF32) {
-                            const uint4 w0 = lds16<e * (kDC / 8) * 16>(wa);
-                            const uint4 w1 = lds16<(EP + e) * (kDC / 8) * 16>(wa);
-                            w[0] = __uint_as_float(w0.x); w[1] = __uint_as_float(w0.y); w[2] = __uint_as_float(w0.z); w[3] = __uint_as_float(w0.w);
-                            w[4] = __uint_as_float(w1.x); w[5] = __uint_as_float(w1.y); w[6] = __uint_as_float(w1.z); w[7] = __uint_as_float(w1.w);
-                        } else {
-                            unpack(lds16<e * (kDC / 8) * 16>(wa), w);
+                    uint4 xp[kTT];
+                    xp[0] = lds16<0 * (kDC / 8) * 16>(xa);
+                    xp[1] = lds16<1 * (kDC / 8) * 16>(xa);
+                    xp[2] = lds16<2 * (kDC / 8) * 16>(xa);
+                    xp[3] = lds16<3 * (kDC / 8) * 16>(xa);
+                    // the 8 columns of the vector in two halves of 4, in column order: the chain of (token, expert) stays sequential
+                    auto half = [&](auto H_) {
+                        constexpr int hq = decltype(H_)::value;
+                        float2 xd[kTT][4];                       // x broadcast to both halves of the packed operand
+#pragma unroll
+                        for (int i = 0; i < kTT; ++i) {
+                            const uint32_t w0 = hq == 0 ? xp[i].x : xp[i].z, w1 = hq == 0 ? xp[i].y : xp[i].w;
+                            const float f0 = bf_lo(w0), f1 = bf_hi(w0), f2 = bf_lo(w1), f3 = bf_hi(w1);
+                            xd[i][0] = make_float2(f0, f0); xd[i][1] = make_float2(f1, f1);
+                            xd[i][2] = make_float2(f2, f2); xd[i][3] = make_float2(f3, f3);
                         }
+                        auto pair = [&](auto P_) {
+                            constexpr int pp = decltype(P_)::value;
+                            const uint4 wlo = lds16<((2 * hq) * NP + pp) * (kDC / 8) * 16>(wa);        // columns 4hq, 4hq+1
+                            const uint4 whi = lds16<((2 * hq + 1) * NP + pp) * (kDC / 8) * 16>(wa);    // columns 4hq+2, 4hq+3
+                            const float2 w[4] = {make_float2(__uint_as_float(wlo.x), __uint_as_float(wlo.y)),
+                                                 make_float2(__uint_as_float(wlo.z), __uint_as_float(wlo.w)),
+                                                 make_float2(__uint_as_float(whi.x), __uint_as_float(whi.y)),
+                                                 make_float2(__uint_as_float(whi.z), __uint_as_float(whi.w))};
 #pragma unroll
-                        for (int i = 0; i < kTT; ++i)
+                            for (int i = 0; i < kTT; ++i)
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) acc[i][e] = __fmaf_rn(x[i][q], w[q], acc[i][e]);
+                                for (int q = 0; q < 4; ++q) acc[i][pp] = __ffma2_rn(xd[i][q], w[q], acc[i][pp]);
+                        };
+                        static_for<TP>(pair);
                     };
-                    static_for<TE>(expert);
+                    static_for<2>(half);
                 }
             }
+            if (more) store_w(stage[(k + 1) & 1]);               // that buffer was last read in iteration k - 1
             __syncthreads();
         }
         // chain tree ((c0+c1)+(c2+c3))+((c4+c5)+(c6+c7)), then lane s keeps every 8th value
@@ -254,7 +297,7 @@ __global__ void __launch_bounds__(128 * ESLABS) router_kernel(const RouterArgs a
         for (int i = 0; i < kTT; ++i)
 #pragma unroll
             for (int e = 0; e < TE; ++e) {
-                float v = acc[i][e];
+                float v = (e & 1) ? acc[i][e >> 1].y : acc[i][e >> 1].x;
                 v = __fadd_rn(v, __shfl_xor_sync(full, v, 1));
                 v = __fadd_rn(v, __shfl_xor_sync(full, v, 2));
                 v = __fadd_rn(v, __shfl_xor_sync(full, v, 4));
@@ -496,7 +539,7 @@ __global__ void __launch_bounds__(kFinishThreads) router_finish_kernel(const Rou
 template <int TE, int ESLABS, bool WF32>
 cudaError_t launch_router_t(const RouterArgs& a, int nb, cudaStream_t s) {
     constexpr int EP = TE * ESLABS;
-    const size_t smem = 2 * ((size_t)kTokBlock * kDC * 2 + (size_t)EP * kDC * (WF32 ? 4 : 2)) + (size_t)kTokBlock * a.E * sizeof(float);
+    const size_t smem = 2 * ((size_t)kTokBlock * kDC * 2 + (size_t)EP * kDC * 4) + (size_t)kTokBlock * a.E * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(router_kernel<TE, ESLABS, WF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;

@@ -30,6 +30,11 @@ struct tmt_sampler {
     std::vector<tmt_nvfp4_weight> up, down;
     std::vector<cudaGraphExec_t> graphs;     // per slot, nullptr until the slot's first step
     std::vector<float> graph_beta;
+    // host rows: uploads and downloads run on streams of their own, ordered against the steps by per-slot events, so the
+    // copies of neighbouring decode steps overlap a step's kernels
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_step, ev_out;   // upload landed / step done / download done, per slot
+    std::vector<unsigned char> pend_in, pend_out, stepped;
     long long steps = 0;
     int recorded = 0;
 };
@@ -145,6 +150,15 @@ tmt_sampler* create_impl(const tmt_sampler_desc& d) {
     CKS(cudaStreamSynchronize(s->stream));
     s->graphs.assign(d.ring, nullptr);
     s->graph_beta.assign(d.ring, 0.0f);
+    CKS(cudaStreamCreateWithFlags(&s->in_stream, cudaStreamNonBlocking));
+    CKS(cudaStreamCreateWithFlags(&s->out_stream, cudaStreamNonBlocking));
+    s->ev_in.assign(d.ring, nullptr); s->ev_step.assign(d.ring, nullptr); s->ev_out.assign(d.ring, nullptr);
+    for (int i = 0; i < d.ring; ++i) {
+        CKS(cudaEventCreateWithFlags(&s->ev_in[i], cudaEventDisableTiming));
+        CKS(cudaEventCreateWithFlags(&s->ev_step[i], cudaEventDisableTiming));
+        CKS(cudaEventCreateWithFlags(&s->ev_out[i], cudaEventDisableTiming));
+    }
+    s->pend_in.assign(d.ring, 0); s->pend_out.assign(d.ring, 0); s->stepped.assign(d.ring, 0);
     return hold.release();
 }
 
@@ -195,7 +209,12 @@ int tmt_sampler_create(const tmt_sampler_desc* desc, tmt_sampler** out) {
 void tmt_sampler_destroy(tmt_sampler* s) {
     if (!s) return;
     cudaSetDevice(s->d.device);
-    if (s->stream) cudaStreamSynchronize(s->stream);
+    for (cudaStream_t st : {s->in_stream, s->stream, s->out_stream})
+        if (st) cudaStreamSynchronize(st);
+    for (auto* v : {&s->ev_in, &s->ev_step, &s->ev_out})
+        for (cudaEvent_t e : *v) if (e) cudaEventDestroy(e);
+    if (s->in_stream) cudaStreamDestroy(s->in_stream);
+    if (s->out_stream) cudaStreamDestroy(s->out_stream);
     drop_graphs(s);
     if (s->moe) tmt_moe_destroy(s->moe);
     for (void* p : {(void*)s->X, (void*)s->Y, (void*)s->warm})
@@ -240,7 +259,11 @@ int tmt_sampler_step(tmt_sampler* s, int slot, float beta) {
         if (!s->Wr) throw std::runtime_error("sampler: tmt_sampler_set_weights has not been called");
         CKS(cudaSetDevice(s->d.device));
         if (!s->graphs[slot] || s->graph_beta[slot] != beta) record_slot(s, slot, beta);
+        if (s->pend_in[slot]) { CKS(cudaStreamWaitEvent(s->stream, s->ev_in[slot], 0)); s->pend_in[slot] = 0; }      // the rows have landed
+        if (s->pend_out[slot]) { CKS(cudaStreamWaitEvent(s->stream, s->ev_out[slot], 0)); s->pend_out[slot] = 0; }   // the old result has left
         CKS(cudaGraphLaunch(s->graphs[slot], s->stream));
+        CKS(cudaEventRecord(s->ev_step[slot], s->stream));
+        s->stepped[slot] = 1;
         s->steps += 1;
     })
 }
@@ -250,7 +273,10 @@ int tmt_sampler_upload(tmt_sampler* s, int slot, const void* X_host) {
     SGUARD({
         check_slot(s, slot);
         CKS(cudaSetDevice(s->d.device));
-        CKS(cudaMemcpyAsync(s->X + (size_t)slot * slot_elems(s), X_host, slot_elems(s) * 2, cudaMemcpyHostToDevice, s->stream));
+        if (s->stepped[slot]) CKS(cudaStreamWaitEvent(s->in_stream, s->ev_step[slot], 0));      // the slot's last step has read its rows
+        CKS(cudaMemcpyAsync(s->X + (size_t)slot * slot_elems(s), X_host, slot_elems(s) * 2, cudaMemcpyHostToDevice, s->in_stream));
+        CKS(cudaEventRecord(s->ev_in[slot], s->in_stream));
+        s->pend_in[slot] = 1;
     })
 }
 
@@ -259,7 +285,10 @@ int tmt_sampler_download(tmt_sampler* s, int slot, void* Y_host) {
     SGUARD({
         check_slot(s, slot);
         CKS(cudaSetDevice(s->d.device));
-        CKS(cudaMemcpyAsync(Y_host, s->Y + (size_t)slot * slot_elems(s), slot_elems(s) * 2, cudaMemcpyDeviceToHost, s->stream));
+        if (s->stepped[slot]) CKS(cudaStreamWaitEvent(s->out_stream, s->ev_step[slot], 0));     // the slot's last step has written them
+        CKS(cudaMemcpyAsync(Y_host, s->Y + (size_t)slot * slot_elems(s), slot_elems(s) * 2, cudaMemcpyDeviceToHost, s->out_stream));
+        CKS(cudaEventRecord(s->ev_out[slot], s->out_stream));
+        s->pend_out[slot] = 1;
     })
 }
 
@@ -267,7 +296,9 @@ int tmt_sampler_sync(tmt_sampler* s) {
     if (!s) { set_error("null handle"); return -1; }
     SGUARD({
         CKS(cudaSetDevice(s->d.device));
+        CKS(cudaStreamSynchronize(s->in_stream));
         CKS(cudaStreamSynchronize(s->stream));
+        CKS(cudaStreamSynchronize(s->out_stream));
         const int st = tmt_moe_device_status(s->moe);
         if (st != 0) throw std::runtime_error("sampler: device status " + std::to_string(st));
     })
