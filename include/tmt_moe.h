@@ -225,6 +225,14 @@ long long tmt_moe_ep_plan(int G, int r, int E, int pad, const int* cnt_all, int*
  * that overflows (its row count in *rows_out, may be NULL); -2 on bad arguments. Same input on every rank, hence
  * the same verdict: a step that overflows one rank fails on all ranks together, with both transports. */
 int tmt_moe_ep_check_capacity(int G, int E, int pad, const int* cnt_all, long long x_cap, long long* rows_out);
+/* The same plan computed by the library's device kernel (what a peer-transport step without expert waves runs after its
+ * all-gather), on host-given counts and on the current device, without a communicator: lets one GPU check the kernel
+ * against the two functions above for any rank count. tables_host: [EL+1] padded group starts of rank r's experts |
+ * [EL] their row counts | [1] number of 128-row tiles | [x_cap / 128] tile -> local expert (-1 past the end);
+ * dest_row0_host[E]: where rank r's rows start inside the owner's group of each expert; world_host[E]: rows per expert
+ * over all ranks; *status_host: 0, or 4 when some rank's rows exceed x_cap. HOST pointers. */
+int tmt_moe_ep_plan_device(int G, int r, int E, int pad, int x_cap, const int* cnt_all_host, int* tables_host,
+                           int* dest_row0_host, int* world_host, int* status_host);
 
 /* ---- entry point that allocates nothing (no counterpart in the reference) ---------------
  * dWrouter[e, d] = sum_t bf16(dlogits[t, e]) * X[t, d], the router_dw phase of

@@ -671,3 +671,33 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
 const float* ep_stat(tmt_moe* h) { return h->ep ? h->ep->stat_global : h->rb.stat; }
 
 }  // namespace tmt
+
+// The device-side plan kernel run alone on the current device, on counts given by the caller: what an expert-parallel
+// step of rank r computes after its all-gather, without any communicator. Exported so that one GPU can check the
+// kernel against the host plan (tmt_moe_ep_plan / tmt_moe_ep_check_capacity) for any number of ranks.
+extern "C" int tmt_moe_ep_plan_device(int G, int r, int E, int pad, int x_cap, const int* cnt_all_host, int* tables_host,
+                                      int* dest_row0_host, int* world_host, int* status_host) {
+    using namespace tmt;
+    try {
+        if (G < 1 || G > 256 || r < 0 || r >= G || E < 1 || E > 256 || E % G || pad < 1 || pad % kPad || x_cap < pad || !cnt_all_host ||
+            !tables_host || !dest_row0_host || !world_host || !status_host)
+            throw std::runtime_error("ep_plan_device: bad arguments");
+        const int EL = E / G, max_tiles = x_cap / kPad;
+        const size_t nt = (size_t)2 * EL + 2 + max_tiles;
+        int *cnt = nullptr, *tab = nullptr, *dst = nullptr, *wor = nullptr, *st = nullptr;
+        CKE(cudaMalloc(&cnt, (size_t)G * E * 4)); CKE(cudaMalloc(&tab, nt * 4)); CKE(cudaMalloc(&dst, E * 4));
+        CKE(cudaMalloc(&wor, E * 4)); CKE(cudaMalloc(&st, 4));
+        CKE(cudaMemcpy(cnt, cnt_all_host, (size_t)G * E * 4, cudaMemcpyHostToDevice));
+        CKE(cudaMemset(st, 0, 4));
+        ep_plan_kernel<<<1, 256>>>(G, r, E, EL, pad, x_cap, max_tiles, cnt, tab, dst, wor, st);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e == cudaSuccess) e = cudaMemcpy(tables_host, tab, nt * 4, cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy(dest_row0_host, dst, E * 4, cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy(world_host, wor, E * 4, cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy(status_host, st, 4, cudaMemcpyDeviceToHost);
+        for (int* q : {cnt, tab, dst, wor, st}) cudaFree(q);
+        CKE(e);
+        return 0;
+    } catch (const std::exception& ex) { set_error("%s", ex.what()); return -1; }
+}

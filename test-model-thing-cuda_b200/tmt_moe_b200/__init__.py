@@ -30,7 +30,7 @@ EXPORTS = (
     "tmt_adamw_create", "tmt_adamw_destroy", "tmt_adamw_step",
     "tmt_ln_forward", "tmt_ln_backward", "tmt_ln_backward_scratch_bytes", "tmt_moe_usage",
     "tmt_moe_ep_check_capacity", "tmt_moe_nvfp4_weights_changed",
-    "tmt_moe_forward_nvfp4_ln",
+    "tmt_moe_forward_nvfp4_ln", "tmt_moe_ep_plan_device",
     "tmt_ckpt_hash", "tmt_ckpt_record_bytes", "tmt_ckpt_save_param", "tmt_ckpt_load_param",
     "tmt_sampler_create", "tmt_sampler_destroy", "tmt_sampler_set_weights", "tmt_sampler_x", "tmt_sampler_y",
     "tmt_sampler_stream", "tmt_sampler_step", "tmt_sampler_upload", "tmt_sampler_download", "tmt_sampler_sync",

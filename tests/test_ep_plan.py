@@ -213,3 +213,59 @@ def test_exchange_plan_two_cpu_ranks(world):
         p.join(timeout=60)
     for rank, msg in res:
         assert msg == "ok", "rank %d: %s" % (rank, msg)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("G,E,pad", [(8, 64, 256), (2, 8, 128), (4, 64, 256), (8, 8, 128), (3, 6, 128)])
+def test_device_plan_kernel_equals_the_host_plan(G, E, pad):
+    """The plan kernel of the peer transport (no host synchronisation in a step) against tmt_moe_ep_plan for every rank,
+    on one GPU, including the 8-rank layout of the benchmarked configuration; then an overflow: status 4 on every
+    rank, tables clamped to the capacity."""
+    sys.path[:0] = [os.path.join(ROOT, "test-model-thing-cuda_b200")]
+    import tmt_moe_b200 as M
+    lib = M.load()
+    rng = np.random.default_rng(G * 1000 + E)
+    EL = E // G
+    cnt_all = rng.integers(0, 900, size=(G, E)).astype(np.int32)
+    cnt_all[:, rng.integers(0, E)] = 0                      # an expert nobody routes to
+    cnt_all[rng.integers(0, G), :] += 3
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    totals = []
+    for r in range(G):
+        tok_poff = np.zeros(E + 1, np.int32); x_counts = np.zeros(EL, np.int32)
+        x_poff = np.zeros(EL + 1, np.int32); src_off = np.zeros(G * EL, np.int32)
+        rows = lib.tmt_moe_ep_plan(G, r, E, pad, p(cnt_all), p(tok_poff), p(x_counts), p(x_poff), p(src_off))
+        totals.append(rows)
+    x_cap = int(max(totals)) + 2 * pad
+    for r in range(G):
+        tok_poff = np.zeros(E + 1, np.int32); x_counts = np.zeros(EL, np.int32)
+        x_poff = np.zeros(EL + 1, np.int32); src_off = np.zeros(G * EL, np.int32)
+        rows = lib.tmt_moe_ep_plan(G, r, E, pad, p(cnt_all), p(tok_poff), p(x_counts), p(x_poff), p(src_off))
+        tables = np.full(2 * EL + 2 + x_cap // 128, 7, np.int32)
+        dest = np.zeros(E, np.int32); world = np.zeros(E, np.int32); status = np.zeros(1, np.int32)
+        rc = lib.tmt_moe_ep_plan_device(G, r, E, pad, x_cap, p(cnt_all), p(tables), p(dest), p(world), p(status))
+        assert rc == 0, lib.tmt_moe_last_error().decode()
+        assert status[0] == 0
+        np.testing.assert_array_equal(tables[:EL + 1], x_poff)
+        np.testing.assert_array_equal(tables[EL + 1:2 * EL + 1], x_counts)
+        assert tables[2 * EL + 1] == rows // 128
+        te = tables[2 * EL + 2:]
+        want_te = np.full(x_cap // 128, -1, np.int32)
+        for le in range(EL):
+            want_te[x_poff[le] // 128:x_poff[le + 1] // 128] = le
+        np.testing.assert_array_equal(te, want_te)
+        np.testing.assert_array_equal(world, cnt_all.sum(0))
+        # where this rank's rows start inside each owner's group: the owner's plan
+        for g in range(G):
+            o_tok = np.zeros(E + 1, np.int32); o_cnt = np.zeros(EL, np.int32)
+            o_poff = np.zeros(EL + 1, np.int32); o_src = np.zeros(G * EL, np.int32)
+            lib.tmt_moe_ep_plan(G, g, E, pad, p(cnt_all), p(o_tok), p(o_cnt), p(o_poff), p(o_src))
+            np.testing.assert_array_equal(dest[g * EL:(g + 1) * EL], o_poff[:EL] + o_src.reshape(G, EL)[r])
+    # a capacity below the fullest rank: every rank reports it, and no table points past the capacity
+    small = (int(max(totals)) // pad - 1) * pad
+    for r in range(G):
+        tables = np.zeros(2 * EL + 2 + small // 128, np.int32)
+        dest = np.zeros(E, np.int32); world = np.zeros(E, np.int32); status = np.zeros(1, np.int32)
+        assert lib.tmt_moe_ep_plan_device(G, r, E, pad, small, p(cnt_all), p(tables), p(dest), p(world), p(status)) == 0
+        assert status[0] == 4
+        assert tables[:EL + 1].max() <= small and tables[2 * EL + 1] <= small // 128
