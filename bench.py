@@ -647,14 +647,27 @@ def main():
                "session_graphs": ses.graphs}
         ses.close()
     elif not args.no_e2e:
-        hX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
-        hX.copy_(d["X"])
-        hdY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
-        hdY.copy_(d["dY"])
-        hY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
-        hdX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
-        hstat = torch.empty(E + 1, dtype=torch.float32).pin_memory()
+        # pinned host buffers first; every rank must have them before any rank enters the host steps (they contain
+        # collectives under expert parallelism), so the outcome is agreed on before going on
+        pinned_ok, pinned_err = 1, ""
+        try:
+            hX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+            hX.copy_(d["X"])
+            hdY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+            hdY.copy_(d["dY"])
+            hY = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+            hdX = torch.empty((T, D), dtype=torch.bfloat16).pin_memory()
+            hstat = torch.empty(E + 1, dtype=torch.float32).pin_memory()
+        except Exception as exc:             # noqa: BLE001
+            pinned_ok, pinned_err = 0, str(exc)[:200]
+        if dist is not None:
+            flag = torch.tensor([pinned_ok], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            pinned_ok = int(flag.item())
         nbytes = T * D * 2
+    if world >= 1 and not args.no_e2e and not cfg.get("nvfp4") and not pinned_ok:
+        e2e = {"value": None, "unit": "tokens/s", "error": "pinned host buffers could not be allocated on every rank: " + pinned_err}
+    elif not args.no_e2e and not cfg.get("nvfp4"):
 
         def host_step():
             # queued without waiting: the next step's uploads run under this step's GEMMs, downloads under the next compute
