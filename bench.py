@@ -424,8 +424,9 @@ def main():
                     help="measurement only: print (stderr) where the TMA, MMA and epilogue threads of the last GEMM launches spent their cycles")
     ap.add_argument("--gemm", default="2cta", choices=["2cta", "1cta"],
                     help="grouped GEMM kernel: CTA pairs on 256x256 tiles (default) or one CTA per 128x256 tile")
-    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: rows move by peer loads/stores inside the gather/scatter kernels, or by NCCL send/recv")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl", "dma"],
+                    help="N > 1: rows move by peer loads/stores inside the gather/scatter kernels, by NCCL send/recv, or as "
+                         "peer-to-peer copies of the copy engines in expert waves under the GEMMs")
     args = ap.parse_args()
     if args.config == "adamw5":
         return bench_adamw(args)
@@ -493,7 +494,7 @@ def main():
                 training=cfg["backward"], device=local_rank, host_io=(not args.no_e2e and not cfg.get("nvfp4")),
                 gemm_impl=M.GEMM_TCGEN05_2CTA if args.gemm == "2cta" else M.GEMM_TCGEN05,
                 stream=stream, ep_world=world, ep_rank=rank,
-                ep_transport=M.EP_PEER if args.ep_transport == "peer" else M.EP_NCCL)
+                ep_transport={"peer": M.EP_PEER, "nccl": M.EP_NCCL, "dma": M.EP_DMA}[args.ep_transport])
     if cfg.get("zipf"):
         from tmt_moe_b200 import synth
         moe.set_router_bias(synth.zipf_bias(E, 2.0))
@@ -729,7 +730,7 @@ def main():
     # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)
     bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12 + (T * D * 2 if cfg["backward"] else 0)), "combine": (A * D * 2 + T * D * 2),
                 "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
-    waves = int(os.environ.get("TMT_MOE_EP_WAVES", "1") or 1)
+    waves = int(os.environ.get("TMT_MOE_EP_WAVES", "4" if args.ep_transport == "dma" else "1") or 1)
     for n, nb in bytes_of.items():
         if world > 1:
             break

@@ -34,7 +34,7 @@ enum { TMT_MOE_BF16 = 0, TMT_MOE_F32 = 1 };
  * tiles, expert groups padded to 256 rows. TCGEN05 = one CTA per 128x256 tile (groups padded to 128 rows). SIMT = slow
  * independent kernel the tests cross-check the tensor-core products with; nothing switches to it at run time. */
 enum { TMT_MOE_GEMM_AUTO = 0, TMT_MOE_GEMM_SIMT = 1, TMT_MOE_GEMM_TCGEN05_2CTA = 2, TMT_MOE_GEMM_TCGEN05 = 3 };
-enum { TMT_MOE_EP_PEER = 0, TMT_MOE_EP_NCCL = 1 };
+enum { TMT_MOE_EP_PEER = 0, TMT_MOE_EP_NCCL = 1, TMT_MOE_EP_DMA = 2 };
 
 /* Replaces the (N,E,K,D) arguments of moe_keep_alloc / moe_ws_alloc (moe.cu:330-362) and
  * the config knobs experts=, topk= (tmt-cuda/src/config.h:12). */
@@ -59,7 +59,9 @@ typedef struct tmt_moe_desc {
                           waves), through tmt_moe_device_status (code 4) where it is made on the device (peer transport:
                           the step then has no host synchronisation; rows past the capacity are not touched)        */
     int ep_transport;  /* TMT_MOE_EP_PEER: gather / scatter kernels address the owners' buffers over NVLink
-                          (CUDA IPC peer memory); TMT_MOE_EP_NCCL: NCCL send / recv exchanges                 */
+                          (CUDA IPC peer memory); TMT_MOE_EP_NCCL: NCCL send / recv exchanges; TMT_MOE_EP_DMA: rows are
+                          grouped locally and cross NVLink as peer-to-peer copies of the copy engines over the same
+                          mappings, on a second stream, in expert waves (TMT_MOE_EP_WAVES) under the GEMMs          */
 } tmt_moe_desc;
 
 /* moe_keep_alloc + moe_ws_alloc (moe.cu:330-362): every buffer is allocated here, none later. */

@@ -67,6 +67,8 @@ struct tmt_ep_state {
     float* stat_global = nullptr;     // E+1
     // peer transport: owners' buffers as seen from this process, [G] pointers each, on the device
     bool peer = false;
+    bool dma = false;                 // TMT_MOE_EP_DMA: rows cross NVLink as peer-to-peer copies of the copy engines
+    std::vector<uint16_t*> peer_tab_host;   // [4][G] the same addresses on the host (sources / destinations of those copies)
     uint16_t** peer_Xg = nullptr; uint16_t** peer_Yg = nullptr; uint16_t** peer_dYg = nullptr; uint16_t** peer_dXg = nullptr;
     std::vector<void*> opened;        // cudaIpcOpenMemHandle results to close
     int* dest_row0 = nullptr;         // [E] this rank's first row inside the owner's group of expert e
@@ -218,13 +220,17 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         const int E = h->d.experts, D = h->d.dim;
         const size_t cap = h->dims.cap;
         ep->peer = h->d.ep_transport == TMT_MOE_EP_PEER;
-        if (ep->peer) {
+        ep->dma = h->d.ep_transport == TMT_MOE_EP_DMA;
+        if (h->d.ep_transport < 0 || h->d.ep_transport > TMT_MOE_EP_DMA) throw std::runtime_error("unknown ep_transport");
+        const bool maps = ep->peer || ep->dma;         // both address the owners' buffers through CUDA IPC mappings
+        if (maps) {
             if (const char* ov = getenv("TMT_MOE_EP_OVERLAP")) ep->overlap = atoi(ov) != 0;
             if (const char* sm = getenv("TMT_MOE_EP_SMS")) ep->side_sms = std::max(0, std::min(atoi(sm), h->num_sms / 2));
+            if (ep->dma) ep->waves = tmt_ep_state::kMaxWaves;     // copy-engine transfers overlap the GEMMs cleanly: waves by default
             if (const char* wv = getenv("TMT_MOE_EP_WAVES")) ep->waves = std::max(1, std::min(atoi(wv), (int)tmt_ep_state::kMaxWaves));
             ep->waves = std::min(ep->waves, ep->EL);
             const char* hp = getenv("TMT_MOE_EP_HOST_PLAN");
-            ep->device_plan = ep->waves < 2 && E <= 256 && ep->G <= 256 && !(hp && atoi(hp) != 0);
+            ep->device_plan = ep->peer && ep->waves < 2 && E <= 256 && ep->G <= 256 && !(hp && atoi(hp) != 0);
             for (int w = 0; w < tmt_ep_state::kMaxWaves; ++w) {
                 CKE(cudaEventCreateWithFlags(&ep->ev_sent[w], cudaEventDisableTiming));
                 CKE(cudaEventCreateWithFlags(&ep->ev_done[w], cudaEventDisableTiming));
@@ -236,10 +242,12 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         ep->Yr = ep_alloc<uint16_t>(h, cap * D);
         ep->bar_word = ep_alloc<int>(h, 1);
         CKE(cudaMemsetAsync(ep->bar_word, 0, sizeof(int), h->stream));
-        if (ep->peer) {
-            const size_t tpad = (size_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
-            ep->Xc = ep_alloc<uint16_t>(h, tpad * D);
-            CKE(cudaMemsetAsync(ep->Xc, 0, tpad * D * 2, h->stream));
+        if (maps) {
+            if (ep->peer) {
+                const size_t tpad = (size_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
+                ep->Xc = ep_alloc<uint16_t>(h, tpad * D);
+                CKE(cudaMemsetAsync(ep->Xc, 0, tpad * D * 2, h->stream));
+            }
             ep->dest_row0 = ep_alloc<int>(h, E);
             ep->dest_row0_host.assign(E, 0);
             // exchange CUDA IPC handles of the four buffers peers write to or read from
@@ -267,7 +275,9 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
             CKE(cudaMemcpyAsync(dev_tab, tab.data(), tab.size() * sizeof(uint16_t*), cudaMemcpyHostToDevice, h->stream));
             CKE(cudaStreamSynchronize(h->stream));
             ep->peer_Xg = dev_tab; ep->peer_Yg = dev_tab + ep->G; ep->peer_dYg = dev_tab + 2 * ep->G; ep->peer_dXg = dev_tab + 3 * ep->G;
-        } else {
+            ep->peer_tab_host = tab;
+        }
+        if (!ep->peer) {
             ep->Xs = ep_alloc<uint16_t>(h, cap * D);
             if (h->d.training) {
                 ep->dYs = ep_alloc<uint16_t>(h, cap * D);
@@ -404,7 +414,7 @@ void plan_step(tmt_moe* h) {
     for (int le = 0; le < EL; ++le)
         for (int i = ep->x_poff[le] / kPad; i < ep->x_poff[le + 1] / kPad; ++i) te[i] = le;
     CKE(cudaMemcpyAsync(ep->x_tables, t, ep->x_tables_host.size() * sizeof(int), cudaMemcpyHostToDevice, h->stream));
-    if (ep->peer) {
+    if (ep->peer || ep->dma) {
         // where this rank's rows start inside the owner's group: the owner's plan, computed here as well
         std::vector<int> o_tok(E + 1), o_cnt(EL), o_poff(EL + 1), o_src((size_t)G * EL);
         for (int g = 0; g < G; ++g) {
@@ -457,6 +467,28 @@ void exchange(tmt_moe* h, bool to_experts, const uint16_t* src, uint16_t* dst, i
             }
         }
     NC(ep, ep->GroupEnd());
+    h->launches += 1;
+}
+
+// The DMA transport's row movement: one peer-to-peer copy (copy engine, no SM) per (owner, expert) segment of this rank's
+// token-side groups, for the local experts [le_lo, le_hi) of every owner. push: local rows -> the owner's group (buffer
+// `which` of the mapped tables); otherwise the owner's rows -> the local buffer. Owners are visited starting after this
+// rank, so that at any moment the ranks target different owners.
+void dma_rows(tmt_moe* h, bool push, int which, uint16_t* local, int le_lo, int le_hi, int width, cudaStream_t stream) {
+    tmt_ep_state* ep = h->ep;
+    const int E = h->d.experts, G = ep->G, EL = ep->EL, r = ep->r;
+    for (int i = 0; i < G; ++i) {
+        const int g = (r + 1 + i) % G;
+        uint16_t* owner = ep->peer_tab_host[(size_t)which * G + g];
+        for (int le = le_lo; le < le_hi; ++le) {
+            const int e = g * EL + le;
+            const size_t n = (size_t)ep->cnt_all[(size_t)r * E + e];
+            if (!n) continue;
+            uint16_t* mine = local + (size_t)ep->tok_poff[e] * width;
+            uint16_t* theirs = owner + (size_t)ep->dest_row0_host[e] * width;
+            CKE(cudaMemcpyAsync(push ? theirs : mine, push ? mine : theirs, n * width * 2, cudaMemcpyDeviceToDevice, stream));
+        }
+    }
     h->launches += 1;
 }
 
@@ -560,6 +592,42 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
             CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
             h->launches += 1;
         }
+    } else if (ep->dma) {
+        // Rows are grouped locally (token-side layout), cross NVLink as copy-engine copies on the second stream, wave by
+        // wave, and are summed locally at the end. The copies occupy no SM, so a wave's transfer really runs under the
+        // previous wave's GEMMs (the SM-based row kernels of the peer transport find no room beside an up / down CTA).
+        route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
+        plan_step(h);
+        zero_pads(h, h->Xg, D);
+        const int W = ep->waves, EL = ep->EL;
+        CKE(cudaEventRecord(ep->ev_fork, h->stream));
+        CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+        prof_mark(h, kPhExchange);
+        for (int w = 0; w < W; ++w) {
+            dma_rows(h, true, 0, ep->Xs, (int)((long)EL * w / W), (int)((long)EL * (w + 1) / W), D, ep->side);
+            rank_barrier(h, ep->side);          // every rank's rows of this wave have landed
+            CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
+        }
+        {
+            struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
+            h->sm_limit = h->num_sms - 2;       // room for the barriers' kernels beside the persistent GEMM CTAs
+            for (int w = 0; w < W; ++w) {
+                const int lo = (int)((long)EL * w / W), hi = (int)((long)EL * (w + 1) / W);
+                CKE(cudaStreamWaitEvent(h->stream, ep->ev_sent[w], 0));
+                expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false, ep->x_poff[lo] / kPad, (ep->x_poff[hi] - ep->x_poff[lo]) / kPad);
+                CKE(cudaEventRecord(ep->ev_done[w], h->stream));
+            }
+        }
+        for (int w = 0; w < W; ++w) {
+            CKE(cudaStreamWaitEvent(ep->side, ep->ev_done[w], 0));
+            rank_barrier(h, ep->side);          // every rank's outputs of this wave are complete
+            dma_rows(h, false, 1, ep->Yr, (int)((long)EL * w / W), (int)((long)EL * (w + 1) / W), D, ep->side);
+        }
+        CKE(cudaEventRecord(ep->ev_join, ep->side));
+        CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
+        prof_mark(h, kPhCombine);
+        CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
+        h->launches += 1;
     } else {
         route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
         plan_step(h);
@@ -651,6 +719,41 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
             prof_mark(h, kPhScatter);
             CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
         }
+    } else if (ep->dma) {
+        CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
+        h->launches += 1;
+        if (h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], h->stream));
+        zero_pads(h, h->dYg, D);
+        const int W = ep->waves, EL = ep->EL;
+        CKE(cudaEventRecord(ep->ev_fork, h->stream));
+        CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
+        prof_mark(h, kPhExchange);
+        for (int w = 0; w < W; ++w) {
+            dma_rows(h, true, 2, ep->dYs, (int)((long)EL * w / W), (int)((long)EL * (w + 1) / W), D, ep->side);
+            rank_barrier(h, ep->side);          // every rank's gradient rows of this wave have landed
+            CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
+        }
+        {
+            struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
+            h->sm_limit = h->num_sms - 2;
+            for (int w = 0; w < W; ++w) {
+                const int lo = (int)((long)EL * w / W), hi = (int)((long)EL * (w + 1) / W);
+                CKE(cudaStreamWaitEvent(h->stream, ep->ev_sent[w], 0));
+                expert_backward(h, Wup, Wdown, dWup, dWdown, 1, ep->x_poff[lo] / kPad, (ep->x_poff[hi] - ep->x_poff[lo]) / kPad);
+                CKE(cudaEventRecord(ep->ev_done[w], h->stream));
+            }
+            // the input-gradient rows travel back (second stream) while the weight gradients are computed here
+            for (int w = 0; w < W; ++w) {
+                CKE(cudaStreamWaitEvent(ep->side, ep->ev_done[w], 0));
+                rank_barrier(h, ep->side);      // every rank's dXg rows of this wave are complete
+                dma_rows(h, false, 3, ep->dXr, (int)((long)EL * w / W), (int)((long)EL * (w + 1) / W), D, ep->side);
+            }
+            CKE(cudaEventRecord(ep->ev_join, ep->side));
+            expert_backward(h, Wup, Wdown, dWup, dWdown, 2);
+        }
+        CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
+        router_backward(h, Wr, nullptr, ep->Xs, true, ep->dXr, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+                        (long)h->d.tokens * ep->G);
     } else {
         CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
         h->launches += 1;

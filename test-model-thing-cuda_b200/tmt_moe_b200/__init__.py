@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libtmt_moe_b200.so")
 
 BF16, F32 = 0, 1
 GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05_2CTA, GEMM_TCGEN05 = 0, 1, 2, 3
-EP_PEER, EP_NCCL = 0, 1
+EP_PEER, EP_NCCL, EP_DMA = 0, 1, 2
 
 EXPORTS = (
     "tmt_moe_create", "tmt_moe_destroy", "tmt_moe_last_error", "tmt_moe_set_router_bias",

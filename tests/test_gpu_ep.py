@@ -100,7 +100,9 @@ C5_WIDTHS = (1024, 2048, 2048, 64, 4)      # the benchmarked configuration's wid
     pytest.param(0, 2, 1, SMALL, id="peer-cta_pairs"), pytest.param(1, 2, 1, SMALL, id="nccl-cta_pairs"),
     pytest.param(0, 2, 2, SMALL, id="peer-cta_pairs-two_expert_waves"),
     pytest.param(0, 2, 4, SMALL, id="peer-cta_pairs-four_expert_waves"),
-    pytest.param(0, 0, 1, C5_WIDTHS, id="peer-config5_widths"), pytest.param(1, 0, 1, C5_WIDTHS, id="nccl-config5_widths")])
+    pytest.param(0, 0, 1, C5_WIDTHS, id="peer-config5_widths"), pytest.param(1, 0, 1, C5_WIDTHS, id="nccl-config5_widths"),
+    pytest.param(2, 2, 1, SMALL, id="dma-cta_pairs-one_wave"), pytest.param(2, 2, 4, SMALL, id="dma-cta_pairs-four_expert_waves"),
+    pytest.param(2, 3, 2, SMALL, id="dma-two_expert_waves"), pytest.param(2, 0, 4, C5_WIDTHS, id="dma-config5_widths")])
 def test_expert_parallel_two_gpus(transport, gemm_impl, waves, shape):
     world = 2
     ctx = mp.get_context("spawn")
