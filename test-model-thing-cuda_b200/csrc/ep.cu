@@ -69,6 +69,9 @@ struct tmt_ep_state {
     bool peer = false;
     bool dma = false;                 // TMT_MOE_EP_DMA: rows cross NVLink as peer-to-peer copies of the copy engines
     std::vector<uint16_t*> peer_tab_host;   // [4][G] the same addresses on the host (sources / destinations of those copies)
+    std::vector<cudaStream_t> copy_streams; // DMA transport: one stream per owner, so that several copy engines and links work at once
+    std::vector<cudaEvent_t> copy_done;
+    cudaEvent_t copy_go = nullptr;
     uint16_t** peer_Xg = nullptr; uint16_t** peer_Yg = nullptr; uint16_t** peer_dYg = nullptr; uint16_t** peer_dXg = nullptr;
     std::vector<void*> opened;        // cudaIpcOpenMemHandle results to close
     int* dest_row0 = nullptr;         // [E] this rank's first row inside the owner's group of expert e
@@ -276,6 +279,20 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
             CKE(cudaStreamSynchronize(h->stream));
             ep->peer_Xg = dev_tab; ep->peer_Yg = dev_tab + ep->G; ep->peer_dYg = dev_tab + 2 * ep->G; ep->peer_dXg = dev_tab + 3 * ep->G;
             ep->peer_tab_host = tab;
+            if (ep->dma) {
+                ep->copy_streams.assign(ep->G, nullptr);
+                ep->copy_done.assign(ep->G, nullptr);
+                for (int g = 0; g < ep->G; ++g) {
+                    CKE(cudaStreamCreateWithFlags(&ep->copy_streams[g], cudaStreamNonBlocking));
+                    CKE(cudaEventCreateWithFlags(&ep->copy_done[g], cudaEventDisableTiming));
+                }
+                CKE(cudaEventCreateWithFlags(&ep->copy_go, cudaEventDisableTiming));
+                // X in token order for the router weight gradient, kept by the local dispatch kernel as on one GPU
+                const size_t tpad = (size_t)(h->d.tokens + h->pad - 1) / h->pad * h->pad;
+                ep->Xc = ep_alloc<uint16_t>(h, tpad * D);
+                CKE(cudaMemsetAsync(ep->Xc, 0, tpad * D * 2, h->stream));
+                if (h->d.training) h->Xc = ep->Xc;
+            }
         }
         if (!ep->peer) {
             ep->Xs = ep_alloc<uint16_t>(h, cap * D);
@@ -297,7 +314,8 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         ep->stat_global = ep_alloc<float>(h, E + 1);
         h->ep_world_counts = ep_alloc<int>(h, E);
         h->ep = ep.release();
-        build_ep_maps(h, h->ep->peer ? h->ep->Xc : h->ep->Xs, h->ep->peer);
+        const bool tok_order = h->ep->peer || (h->ep->dma && h->d.training);
+        build_ep_maps(h, tok_order ? h->ep->Xc : h->ep->Xs, tok_order);
         return 0;
     } catch (const std::exception& e) { set_error("%s", e.what()); return -1; }
 }
@@ -309,6 +327,9 @@ namespace tmt {
 void ep_teardown(tmt_moe* h) {
     if (!h->ep) return;
     for (void* p : h->ep->opened) cudaIpcCloseMemHandle(p);
+    for (cudaStream_t st : h->ep->copy_streams) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+    for (cudaEvent_t e : h->ep->copy_done) if (e) cudaEventDestroy(e);
+    if (h->ep->copy_go) cudaEventDestroy(h->ep->copy_go);
     if (h->ep->side) cudaStreamDestroy(h->ep->side);
     if (h->ep->ev_fork) cudaEventDestroy(h->ep->ev_fork);
     if (h->ep->ev_join) cudaEventDestroy(h->ep->ev_join);
@@ -477,8 +498,12 @@ void exchange(tmt_moe* h, bool to_experts, const uint16_t* src, uint16_t* dst, i
 void dma_rows(tmt_moe* h, bool push, int which, uint16_t* local, int le_lo, int le_hi, int width, cudaStream_t stream) {
     tmt_ep_state* ep = h->ep;
     const int E = h->d.experts, G = ep->G, EL = ep->EL, r = ep->r;
+    // every owner's copies run on a stream of their own (fork from `stream`, join back into it)
+    CKE(cudaEventRecord(ep->copy_go, stream));
     for (int i = 0; i < G; ++i) {
         const int g = (r + 1 + i) % G;
+        cudaStream_t cs = ep->copy_streams[g];
+        CKE(cudaStreamWaitEvent(cs, ep->copy_go, 0));
         uint16_t* owner = ep->peer_tab_host[(size_t)which * G + g];
         for (int le = le_lo; le < le_hi; ++le) {
             const int e = g * EL + le;
@@ -486,8 +511,10 @@ void dma_rows(tmt_moe* h, bool push, int which, uint16_t* local, int le_lo, int 
             if (!n) continue;
             uint16_t* mine = local + (size_t)ep->tok_poff[e] * width;
             uint16_t* theirs = owner + (size_t)ep->dest_row0_host[e] * width;
-            CKE(cudaMemcpyAsync(push ? theirs : mine, push ? mine : theirs, n * width * 2, cudaMemcpyDeviceToDevice, stream));
+            CKE(cudaMemcpyAsync(push ? theirs : mine, push ? mine : theirs, n * width * 2, cudaMemcpyDeviceToDevice, cs));
         }
+        CKE(cudaEventRecord(ep->copy_done[g], cs));
+        CKE(cudaStreamWaitEvent(stream, ep->copy_done[g], 0));
     }
     h->launches += 1;
 }
@@ -752,7 +779,7 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
             expert_backward(h, Wup, Wdown, dWup, dWdown, 2);
         }
         CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
-        router_backward(h, Wr, nullptr, ep->Xs, true, ep->dXr, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
+        router_backward(h, Wr, nullptr, ep->Xc, true, ep->dXr, dWr, static_cast<uint16_t*>(dX), aux, zcoef, h->ep_world_counts,
                         (long)h->d.tokens * ep->G);
     } else {
         CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, ep->dYs, h->s_j, /*mode=*/2, h->stream));
