@@ -127,6 +127,8 @@ int tmt_moe_host_wait(tmt_moe* h);
  *   "logits" "probs" (tokens*E f32)  "idx" "slot_of" (tokens*K i32)  "w" (tokens*K f32)
  *   "counts" (E i32)  "poff" (E+1 i32, 128-row padded group starts)  "lse" (tokens f32)
  *   "dlogits" (tokens*E f32, after backward)  "s_j" (tokens*K f32, after backward)
+ *   "ep_waves" (1 i32: expert waves an expert-parallel step of this handle runs in, 1 = one exchange per pass;
+ *   known after tmt_moe_ep_init)
  * Returns the number of bytes written, or -1. */
 long long tmt_moe_read(tmt_moe* h, const char* name, void* dst_host, size_t dst_bytes);
 

@@ -60,5 +60,12 @@ __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f,
 
 __device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void stg16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+// 16-byte read-only load that allocates no L1 line: for kernels that share an SM with a CTA whose shared memory leaves the
+// L1 a few KB, where lines for rows that are read once would only be fought over.
+__device__ __forceinline__ uint4 ldg16_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 }  // namespace tmt

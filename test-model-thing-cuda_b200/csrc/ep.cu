@@ -40,9 +40,12 @@ struct tmt_ep_state {
     static constexpr int kMaxWaves = 4;
     cudaEvent_t ev_sent[kMaxWaves] = {}, ev_done[kMaxWaves] = {};     // a wave's rows have landed / its GEMMs are done
     bool overlap = true;              // TMT_MOE_EP_OVERLAP=0 switches the second stream off (measurement)
-    int waves = 1;                    // TMT_MOE_EP_WAVES: expert waves of the forward pass. Measured at 2 GPUs: 2 waves make the
-                                      // step 1.0-1.5 ms SLOWER (GEMMs beside the row kernels lose more than the transfers
-                                      // hide, with shared or with dedicated SMs), so the default is no waves.
+    int waves = 1;                    // TMT_MOE_EP_WAVES: expert waves of both passes. Peer transport: four from four ranks up (measured
+                                      // at 4 GPUs: 2-4 % faster than one exchange per pass), none at two ranks, where half of the
+                                      // rows never leave the GPU and the waves cost 1-3 ms more than they hide.
+    int fetch_waves = -1;             // TMT_MOE_EP_FETCH: how many of the forward waves' output rows are fetched under later GEMMs
+                                      // (the final combine reads the others from their owners itself); -1: all
+    bool thin = true;                 // TMT_MOE_EP_THIN=0: the waves after the first use the full-size row kernels again (measurement)
     int side_sms = 0;                 // TMT_MOE_EP_SMS: > 0 keeps that many SMs for the side stream's row kernels instead of
                                       // letting their blocks share SMs with the GEMM CTAs
     int G = 1, r = 0, EL = 0;
@@ -228,8 +231,11 @@ int tmt_moe_ep_init(tmt_moe* h, const void* id128) {
         const bool maps = ep->peer || ep->dma;         // both address the owners' buffers through CUDA IPC mappings
         if (maps) {
             if (const char* ov = getenv("TMT_MOE_EP_OVERLAP")) ep->overlap = atoi(ov) != 0;
+            if (const char* th = getenv("TMT_MOE_EP_THIN")) ep->thin = atoi(th) != 0;
+            if (const char* fw = getenv("TMT_MOE_EP_FETCH")) ep->fetch_waves = atoi(fw);
             if (const char* sm = getenv("TMT_MOE_EP_SMS")) ep->side_sms = std::max(0, std::min(atoi(sm), h->num_sms / 2));
             if (ep->dma) ep->waves = tmt_ep_state::kMaxWaves;     // copy-engine transfers overlap the GEMMs cleanly: waves by default
+            if (ep->peer && ep->G >= 4 && h->two_cta) ep->waves = tmt_ep_state::kMaxWaves;   // the later waves' row kernels fit beside the CTA-pair GEMM only
             if (const char* wv = getenv("TMT_MOE_EP_WAVES")) ep->waves = std::max(1, std::min(atoi(wv), (int)tmt_ep_state::kMaxWaves));
             ep->waves = std::min(ep->waves, ep->EL);
             const char* hp = getenv("TMT_MOE_EP_HOST_PLAN");
@@ -590,33 +596,59 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
                 return pm;
             };
             prof_mark(h, kPhDispatch);
-            for (int w = 0; w < W; ++w) {
-                CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, ep->side, wave_map(ep->peer_Xg, w),
-                                    (h->d.training && w == 0) ? ep->Xc : nullptr));
+            // The first wave fixes every assignment's slot and has the machine to itself; the later ones only move rows,
+            // beside the GEMM CTAs of the waves before (launch_wave_rows).
+            auto send = [&](int w) {
+                if (w == 0 || !ep->thin)
+                    CKE(launch_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(X), h->Xg, ep->side, wave_map(ep->peer_Xg, w),
+                                        (h->d.training && w == 0) ? ep->Xc : nullptr));
+                else
+                    CKE(launch_wave_rows(h->dims, h->rb, 0, static_cast<const uint16_t*>(X), nullptr, nullptr, h->num_sms, ep->side,
+                                         wave_map(ep->peer_Xg, w)));
                 if (w == W - 1 && h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvXFree], ep->side));   // last read of X
                 rank_barrier(h, ep->side);      // every rank's rows of this wave have landed
                 CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
                 h->launches += 1;
-            }
+            };
+            // Order on the second stream: the sends run two waves ahead of the GEMMs, a finished wave's fetch comes before
+            // the send after next (W = 4: send 0, 1, 2, fetch 0, send 3, fetch 1, 2, 3).
+            int sent = 0;
+            for (; sent < std::min(W, 3); ++sent) send(sent);
+            const int F = ep->fetch_waves < 0 ? W : std::min(ep->fetch_waves, W);      // waves fetched on the second stream
             struct Limit { tmt_moe* h; ~Limit() { h->sm_limit = 0; } } limit{h};
-            h->sm_limit = gemm_sms_beside_rows(h);
             for (int w = 0; w < W; ++w) {
                 const int lo = (int)((long)EL * w / W), hi = (int)((long)EL * (w + 1) / W);
                 CKE(cudaStreamWaitEvent(h->stream, ep->ev_sent[w], 0));
+                h->sm_limit = gemm_sms_beside_rows(h);
                 expert_forward(h, Wup, Wdown, /*gate_in_epilogue=*/false, ep->x_poff[lo] / kPad, (ep->x_poff[hi] - ep->x_poff[lo]) / kPad);
-                CKE(cudaEventRecord(ep->ev_done[w], h->stream));
-            }
-            h->sm_limit = 0;
-            for (int w = 0; w < W; ++w) {
-                CKE(cudaStreamWaitEvent(ep->side, ep->ev_done[w], 0));
-                rank_barrier(h, ep->side);      // every rank's outputs of this wave are complete
-                CKE(launch_combine(h->dims, h->rb, h->Yg, nullptr, 0.0f, /*mode=*/3, ep->side, wave_map(ep->peer_Yg, w), ep->Yr));
-                h->launches += 1;
+                h->sm_limit = 0;
+                if (w < F) {
+                    CKE(cudaEventRecord(ep->ev_done[w], h->stream));
+                    CKE(cudaStreamWaitEvent(ep->side, ep->ev_done[w], 0));
+                    rank_barrier(h, ep->side);      // every rank's outputs of this wave are complete
+                    // a fetch that has GEMMs left to hide under runs beside them; the last wave's has none: full-size kernel
+                    if (w == W - 1 || !ep->thin)
+                        CKE(launch_combine(h->dims, h->rb, h->Yg, nullptr, 0.0f, /*mode=*/3, ep->side, wave_map(ep->peer_Yg, w), ep->Yr));
+                    else
+                        CKE(launch_wave_rows(h->dims, h->rb, 2, nullptr, ep->Yr, nullptr, h->num_sms, ep->side, wave_map(ep->peer_Yg, w)));
+                    h->launches += 1;
+                }
+                if (sent < W) send(sent++);
             }
             CKE(cudaEventRecord(ep->ev_join, ep->side));
             CKE(cudaStreamWaitEvent(h->stream, ep->ev_join, 0));
-            prof_mark(h, kPhCombine);           // every row is in Yr (token-side slots): a local weighted sum remains
-            CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
+            if (F == W) {
+                prof_mark(h, kPhCombine);       // every row is in Yr (token-side slots): a local weighted sum remains
+                CKE(launch_combine(h->dims, h->rb, ep->Yr, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream));
+            } else {
+                prof_mark(h, kPhExchange);
+                rank_barrier(h);                // every rank's outputs of the waves not fetched yet are complete
+                prof_mark(h, kPhCombine);       // the fetched waves' rows from Yr, the others straight from their owners
+                PeerMap pm = peer_map(h, ep->peer_Yg);
+                pm.fetched = ep->Yr; pm.fetched_hi = (int)((long)EL * F / W);
+                CKE(launch_combine(h->dims, h->rb, h->Yg, static_cast<uint16_t*>(Y), beta, /*mode=*/2, h->stream, pm,
+                                   h->d.training ? ep->Yr : nullptr));
+            }
             h->launches += 1;
         }
     } else if (ep->dma) {
@@ -700,7 +732,10 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
             for (int w = 0; w < ep->waves; ++w) {
                 PeerMap pm = peer_map(h, ep->peer_dYg, true);
                 pm.wave_lo = (int)((long)ep->EL * w / ep->waves); pm.wave_hi = (int)((long)ep->EL * (w + 1) / ep->waves);
-                CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, h->dYg, h->s_j, /*mode=*/2, ep->side, pm));
+                if (w == 0 || !ep->thin)
+                    CKE(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), ep->Yr, h->dYg, h->s_j, /*mode=*/2, ep->side, pm));
+                else
+                    CKE(launch_wave_rows(h->dims, h->rb, 1, static_cast<const uint16_t*>(dY), ep->Yr, h->s_j, h->num_sms, ep->side, pm));
                 if (w == ep->waves - 1 && h->host_hooks) CKE(cudaEventRecord(h->host_ev[tmt_moe::kEvDyFree], ep->side));
                 rank_barrier(h, ep->side);      // every rank's gradient rows of this wave have landed
                 CKE(cudaEventRecord(ep->ev_sent[w], ep->side));
@@ -799,6 +834,7 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
 }
 
 const float* ep_stat(tmt_moe* h) { return h->ep ? h->ep->stat_global : h->rb.stat; }
+int ep_waves(tmt_moe* h) { return h->ep ? h->ep->waves : 1; }
 
 }  // namespace tmt
 

@@ -122,8 +122,19 @@ __device__ __forceinline__ bool get_tile2_nkb(const GemmParams& p, int t, int m_
     return true;
 }
 
+// Register cap: 128 per thread. An SM's register file is four partitions of 16384, one per warp scheduler, and a
+// block's warps are dealt round over them: the 11 warps of an up / dH CTA put three into a partition. At the 152 / 168
+// registers the compiler takes when left alone those three warps fill a partition (14592 / 16128), and no warp of another
+// kernel fits beside the CTA, although a sixth of the file is free in total. At 128 they leave 4096 per partition: two
+// more warps of 64 registers, which is what the expert-parallel step's row kernels for the later waves are shaped to
+// (wave_rows_kernel, 256 threads x 64 registers, no shared memory). The cap costs nothing measurable: no spills, and
+// the full-size step alone takes the same time with and without it (alternating runs on one GPU).
+#ifndef TMT_GEMM_MAXNREG
+#define TMT_GEMM_MAXNREG 128
+#endif
+#define TMT_GEMM_BOUNDS __maxnreg__(TMT_GEMM_MAXNREG)
 template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(block_threads<EPI>(), 1) gemm_tcgen05_2cta_kernel(const GemmParams p) {
+__global__ void __cluster_dims__(2, 1, 1) TMT_GEMM_BOUNDS gemm_tcgen05_2cta_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kStages2 / 2], empty_bar[kStages2], tfull_bar[2], tempty_bar[2], group_bar[2];
     __shared__ uint32_t tmem_base_s;

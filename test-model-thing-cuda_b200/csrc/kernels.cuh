@@ -53,6 +53,10 @@ struct PeerMap {
     // exchange plan computed on the device the host learns of it from the status word, after the kernels have run).
     int row_limit = 0;
     int* status = nullptr;
+    // launch_combine only: the rows of assignments whose expert's index inside its owner lies below fetched_hi were
+    // brought over earlier (mode 3) and are read from `fetched` at their token-side slots, not from the owner.
+    const uint16_t* fetched = nullptr;
+    int fetched_hi = 0;
     // Extra dynamic shared memory per block (unused by the kernel): with a few KB a block no longer fits beside a
     // resident GEMM CTA, so a kernel launched next to a GEMM stays on the SMs that GEMM left free.
     int pad_smem = 0;
@@ -84,6 +88,12 @@ cudaError_t launch_combine(const RouteDims& d, const RouteBufs& b, const uint16_
 // mode 2: as mode 0 and s_j = <dY, Yg[slot]>                                     (expert parallel)
 cudaError_t launch_grad_dispatch(const RouteDims& d, const RouteBufs& b, const uint16_t* dY, const uint16_t* Yg,
                                  uint16_t* dYg, float* s_j, int mode, cudaStream_t s, PeerMap pm = PeerMap());
+// One expert wave's row moves beside a resident tensor-core CTA (128-thread blocks, no shared memory, `blocks` = one per
+// SM). op 0: owner's Xg row = X[token] (src = X); op 1: owner's dYg row = bf16(w * dY[token]) and s_j = <dY[token],
+// kept[slot]> (src = dY); op 2: kept[slot] = owner's Yg row. pm names the owners' buffers and the wave; the slots must
+// have been fixed by launch_dispatch before.
+cudaError_t launch_wave_rows(const RouteDims& d, const RouteBufs& b, int op, const uint16_t* src, uint16_t* kept, float* s_j,
+                             int blocks, cudaStream_t s, PeerMap pm);
 // moe.cu:200-234. sw_part (may be NULL): per-row partial sums of w * dL/dw from the dH GEMM.
 // counts / n_norm: per-expert counts and token count the aux and z terms are normalised by
 // (the local ones on one GPU, the totals over all ranks under expert parallelism).

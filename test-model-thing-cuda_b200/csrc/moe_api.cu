@@ -341,7 +341,7 @@ void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
         CK(cudaMemcpyAsync(h->plain_num, &plain, sizeof(int), cudaMemcpyHostToDevice, h->stream));
         h->plain_num_host = plain;
     }
-    h->launches += 2;
+    h->launches += scanned ? 1 : 3;      // the router's kernel, and the scan's two when it ran on its own
 }
 
 // Grouped expert products over the rows in h->Xg: Yg = expert(Xg). With gate_in_epilogue the
@@ -907,6 +907,7 @@ long long tmt_moe_read(tmt_moe* h, const char* name, void* dst, size_t dst_bytes
         else if (s == "Yg") { src = h->Yg; n = (size_t)h->gcap * h->d.dim * 2; }
         else if (s == "dYg") { src = h->d.training ? h->dYg : nullptr; n = (size_t)h->gcap * h->d.dim * 2; }
         else if (s == "dXg") { src = h->dXg; n = (size_t)h->gcap * h->d.dim * 2; }
+        else if (s == "ep_waves") { int w = ep_waves(h); if (dst_bytes < 4) throw std::runtime_error("destination too small"); memcpy(dst, &w, 4); return 4; }
         else if (s == "gcap") { n = 4; int gc = (int)h->gcap; if (dst_bytes < 4) throw std::runtime_error("destination too small"); memcpy(dst, &gc, 4); return 4; }
         else if (s == "P") { src = h->P; n = (size_t)h->gcap * h->d.hidden * 2; }
         else if (s == "Hact") { src = h->Hact; n = (size_t)h->gcap * h->d.hidden * 2; }

@@ -118,6 +118,7 @@ void ep_backward(tmt_moe* h, const void* dY, const void* Wr, const void* const* 
                  float* dWr, float* const* dWup, float* const* dWdown, void* dX, float aux, float zcoef);
 void ep_teardown(tmt_moe* h);
 const float* ep_stat(tmt_moe* h);
+int ep_waves(tmt_moe* h);           // expert waves of an expert-parallel step (1: one exchange per pass)
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr);
 void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t* grouped);
 // tile_count >= 0: only the 128-row tiles [tile_begin, tile_begin + tile_count) of the grouped buffers.

@@ -105,6 +105,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
         const int e = b.idx[t * d.K + lane];
         if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
         else if (!in_wave(pm, e)) slot = -1;
+        else if (pm.fetched != nullptr && e % pm.experts_per_rank < pm.fetched_hi) {
+            wj = b.slotw[slot]; row = const_cast<uint16_t*>(pm.fetched) + (long)slot * d.D;
+        }
         else { wj = b.slotw[slot]; row = group_row(pm, Yg, b.poff, e, slot, d.D); if (row == nullptr) slot = -1; }
     }
     int slots[kMaxK]; float ws[kMaxK]; const uint16_t* rows[kMaxK];
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) combine_kernel(const Rout
             if (j < d.K && slots[j] >= 0) {
                 float y[8];
                 const uint4 raw = ldg16(rows[j] + v * 8);
-                if (y_keep) stg16(y_keep + (long)slots[j] * d.D + v * 8, raw);
+                if (y_keep && rows[j] != y_keep + (long)slots[j] * d.D) stg16(y_keep + (long)slots[j] * d.D + v * 8, raw);
                 unpack8(raw, y);
                 if constexpr (MODE == 1) {
 #pragma unroll
@@ -229,6 +232,82 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) grad_dispatch_kernel(cons
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 if (lane == 0 && slots[j] >= 0) s_j[t * d.K + j] = s;
+            }
+        }
+    }
+}
+
+// The row moves of one expert wave (expert-parallel step), shaped to run BESIDE a resident tensor-core CTA of the
+// CTA-pair kernel. Such a CTA leaves 1.9 KB of the SM's shared memory, i.e. room for ONE more block (every block
+// reserves 1 KB) that uses none of its own, and, with its registers capped at 128, 4096 registers in each of the four
+// scheduler partitions: two warps of 64. So: one block per SM, 256 threads, at most 64 registers, each warp walking
+// the tokens with a grid stride and keeping a whole 4 KB row in flight. The slots were fixed by the first wave's
+// dispatch (slot_of, slotw), so only rows move here. A warp reads the bookkeeping of 32 / K tokens at once (one
+// assignment per lane), so the dependent index loads are paid once per handful of rows, not once per row.
+//   OP 0: owner's Xg[row]  = X[token]                                         (dispatch_kernel's copy)
+//   OP 1: owner's dYg[row] = bf16(w * dY[token]); s_j = <dY[token], kept[slot]>  (grad_dispatch_kernel, mode 2, same sum order)
+//   OP 2: kept[slot]       = owner's Yg[row]                                  (combine_kernel, mode 3)
+template <int OP>
+__global__ void __launch_bounds__(256, 4) wave_rows_kernel(const RouteDims d, const RouteBufs b,
+                                                                                          const uint16_t* __restrict__ src,
+                                                                                          uint16_t* __restrict__ kept,
+                                                                                          float* __restrict__ s_j, const PeerMap pm) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = d.D >> 3;
+    const int per = 32 / d.K;                                   // tokens a warp looks at together
+    const long nchunk = (d.T + per - 1) / per;
+    const long nwarp = (long)gridDim.x * (blockDim.x >> 5);
+    const int tl = lane / d.K;                                  // this lane's token within the chunk; its assignment is lane % K
+    for (long c = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < nchunk; c += nwarp) {
+        const long t = c * per + tl;
+        int slot = -1; float wj = 0.0f; uint16_t* row = nullptr;
+        if (tl < per && t < d.T) {
+            const long a = c * per * d.K + lane;                // = t * K + lane % K
+            const int e = b.idx[a];
+            if (e >= 0 && e < d.E && in_wave(pm, e)) {
+                slot = b.slot_of[a];
+                if (slot < 0 || slot >= d.cap) { report(b.status, kErrSlotRange); slot = -1; }
+                else {
+                    wj = b.slotw[slot];
+                    row = group_row(pm, nullptr, b.poff, e, slot, d.D);
+                    if (row == nullptr) slot = -1;
+                }
+            }
+        }
+        unsigned todo = __ballot_sync(0xffffffffu, slot >= 0);
+        while (todo) {
+            const int j = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const int sl = __shfl_sync(0xffffffffu, slot, j);
+            uint16_t* r = shfl_ptr(row, j);
+            const long tj = c * per + j / d.K;
+            if constexpr (OP == 0) {
+                const uint16_t* x = src + tj * d.D;
+#pragma unroll 8
+                for (int v = lane; v < nvec; v += 32) stg16(r + v * 8, ldg16_stream(x + v * 8));
+            } else if constexpr (OP == 2) {
+                uint16_t* k = kept + (long)sl * d.D;
+#pragma unroll 8
+                for (int v = lane; v < nvec; v += 32) stg16(k + v * 8, ldg16_stream(r + v * 8));
+            } else {
+                const float w = __shfl_sync(0xffffffffu, wj, j);
+                const uint16_t* g_row = src + tj * d.D;
+                const uint16_t* y_row = kept + (long)sl * d.D;
+                float sdot = 0.0f;
+#pragma unroll 4
+                for (int v = lane; v < nvec; v += 32) {
+                    float g[8], y[8], o[8];
+                    unpack8(ldg16_stream(g_row + v * 8), g);
+                    unpack8(ldg16_stream(y_row + v * 8), y);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sdot += g[i] * y[i];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] = w * g[i];
+                    stg16(r + v * 8, pack8(o));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+                if (lane == 0) s_j[c * per * d.K + j] = sdot;
             }
         }
     }
@@ -481,6 +560,18 @@ cudaError_t launch_router_bwd(const RouteDims& d, const RouteBufs& b, const floa
                               uint16_t* dl_t, int kw, uint16_t* dl_g, int mw, cudaStream_t s) {
     router_bwd_kernel<<<(d.T + 31) / 32, 256, 0, s>>>(d, b, sw_part, sw_ld, s_j, dlogits, aux, zcoef, counts, n_norm,
                                                       dl_t, kw, dl_g, mw);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wave_rows(const RouteDims& d, const RouteBufs& b, int op, const uint16_t* src, uint16_t* kept, float* s_j,
+                             int blocks, cudaStream_t s, PeerMap pm) {
+    if (d.K < 1 || d.K > kMaxK || (d.D & 7) != 0 || pm.base == nullptr || blocks < 1) return cudaErrorInvalidValue;
+    switch (op) {
+        case 0: wave_rows_kernel<0><<<blocks, 256, 0, s>>>(d, b, src, kept, s_j, pm); break;
+        case 1: wave_rows_kernel<1><<<blocks, 256, 0, s>>>(d, b, src, kept, s_j, pm); break;
+        case 2: wave_rows_kernel<2><<<blocks, 256, 0, s>>>(d, b, src, kept, s_j, pm); break;
+        default: return cudaErrorInvalidValue;
+    }
     return cudaGetLastError();
 }
 

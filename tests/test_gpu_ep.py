@@ -17,7 +17,10 @@ pytestmark = pytest.mark.gpu
 def _worker(rank, world, port, q, transport, gemm_impl=3, waves=1, shape=(900, 256, 384, 8, 2)):
     try:
         sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200"), os.path.join(ROOT, "tests")]
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TMT_MOE_EP_WAVES=str(waves))
+        # waves > 10: tens = expert waves, units = how many of them the second stream fetches (the rest: final combine)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TMT_MOE_EP_WAVES=str(waves // 10 if waves > 10 else waves))
+        if waves > 10:
+            os.environ["TMT_MOE_EP_FETCH"] = str(waves % 10)
         import torch.distributed as dist
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -101,6 +104,9 @@ C5_WIDTHS = (1024, 2048, 2048, 64, 4)      # the benchmarked configuration's wid
     pytest.param(0, 2, 2, SMALL, id="peer-cta_pairs-two_expert_waves"),
     pytest.param(0, 2, 4, SMALL, id="peer-cta_pairs-four_expert_waves"),
     pytest.param(0, 0, 1, C5_WIDTHS, id="peer-config5_widths"), pytest.param(1, 0, 1, C5_WIDTHS, id="nccl-config5_widths"),
+    pytest.param(0, 0, 4, C5_WIDTHS, id="peer-config5_widths-four_expert_waves"),
+    pytest.param(0, 0, 42, C5_WIDTHS, id="peer-config5_widths-four_expert_waves-two_fetched"),
+    pytest.param(0, 2, 40, SMALL, id="peer-cta_pairs-four_expert_waves-none_fetched"),
     pytest.param(2, 2, 1, SMALL, id="dma-cta_pairs-one_wave"), pytest.param(2, 2, 4, SMALL, id="dma-cta_pairs-four_expert_waves"),
     pytest.param(2, 3, 2, SMALL, id="dma-two_expert_waves"), pytest.param(2, 0, 4, C5_WIDTHS, id="dma-config5_widths")])
 def test_expert_parallel_two_gpus(transport, gemm_impl, waves, shape):
