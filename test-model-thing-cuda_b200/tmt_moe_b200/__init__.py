@@ -264,10 +264,10 @@ class MoE:
     @property
     def ep_waves(self):
         """Expert waves an expert-parallel step runs in (1: one exchange per pass); known after ep_init."""
-        w = np.zeros(1, np.int32)
-        if self.lib.tmt_moe_read(self.h, b"ep_waves", _ptr(w), ctypes.c_size_t(4)) != 4:
+        w = ctypes.c_int(0)
+        if self.lib.tmt_moe_read(self.h, b"ep_waves", ctypes.byref(w), ctypes.c_size_t(4)) != 4:
             _check(-1, self.lib)
-        return int(w[0])
+        return int(w.value)
 
     def set_profile(self, on):
         _check(self.lib.tmt_moe_set_profile(self.h, int(on)), self.lib)
