@@ -480,7 +480,9 @@ def main():
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a rank that failed leaves the others in a collective: give up after five minutes, not after the default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()                        # nvidia-smi needs about a second before its first sample
@@ -699,92 +701,95 @@ def main():
             dist.destroy_process_group()
         return
 
-    pk, pk_kind = peaks()
-    A = T * K
-    gemm_names = [n for n in phases if n.startswith("gemm_")]
-    gemm_ms = sum(phases[n][0] for n in gemm_names) / args.steps
-    gemm_launches = sum(phases[n][1] for n in gemm_names) // args.steps
-    flops = (12.0 if cfg["backward"] else 4.0) * A * D * H          # all ranks' tokens processed by... this rank's share
-    achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
-    roofline = {"bound": "tensor", "kernel": "%s (%d launches per step)" % (
-                    "gemm_tcgen05_2cta_kernel" if args.gemm == "2cta" else "gemm_tcgen05_kernel", gemm_launches),
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                # dram read + write per launch, averaged over the six launches: ncu capture at 32768 tokens scaled to
-                # the full token count (activations x 4, weights fixed)
-                "traffic": 6.1e9 if (args.config == "c5" and not args.tokens and world == 1) else None,
-                "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
-                "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}
-    if cfg.get("nvfp4"):
-        # weight-byte roofline: every expert hit in a decode step streams its packed weights once
-        # (0.5 B per value + one scale byte per 16 values), 2*D*H values per expert; with 128 assignments over
-        # 16 experts all experts are hit (P(miss) < 1e-3), plus the 64 input and output rows
-        per_decode = E * 2.0 * D * H * (0.5 + 1.0 / 16) + 2 * T * D * 2
-        gbs = per_decode * cfg["decode_steps"] / (ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "decode step (router, fp4_rows_kernel up and down on the packed weights, combine)", "achieved": gbs,
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
-                    "peak_kind": pk_kind + " copy bandwidth; algorithmic bytes are the packed weights of every expert hit, once per decode "
-                                 "step (36 MB: they stay in the 126 MB L2 between decode steps, so this bounds the kernels' load path, not DRAM)",
-                    "bytes_per_decode_step": per_decode}
-    hbm = {}
-    # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)
-    bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12 + (T * D * 2 if cfg["backward"] else 0)), "combine": (A * D * 2 + T * D * 2),
-                "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
-    waves = moe.ep_waves if world > 1 else 1
-    for n, nb in bytes_of.items():
-        if world > 1:
-            break
-        if n in phases and phases[n][0] > 0:
-            gbs = nb / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
-            hbm[n] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-                      "bytes_per_launch": nb}
-    nvlink = {}
-    if world > 1 and args.ep_transport == "peer":
-        # Expert parallel: the row kernels move (world-1)/world of their grouped rows over NVLink and are bound by it, not
-        # by HBM: rows leaving (dispatch, gradient dispatch) or entering (combine, scatter) this GPU per launch, against the
-        # measured peer-copy bandwidth of this pool (770 GB/s per direction). Only kernels that run alone on the main stream
-        # have a phase time: the scatter always runs on the second stream under the weight-gradient GEMMs, and with expert
-        # waves so do the other three.
-        out_bytes = A * D * 2 * (world - 1) / world
-        for n in ("dispatch", "combine", "grad_dispatch"):
-            if waves < 2 and n in phases and phases[n][0] > 0:
-                gbs = out_bytes / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
-                nvlink[n] = {"achieved": gbs, "peak": 770.0, "unit": "GB/s", "frac": gbs / 770.0, "bytes_over_nvlink": out_bytes,
-                             "exposed_ms": phases[n][0] / phases[n][1]}
-        nvlink["note"] = ("scatter runs on the second stream under the weight-gradient GEMMs" +
-                          ("; with %d expert waves dispatch, combine and gradient dispatch run there too (no phase time)" % waves if waves > 1 else ""))
-    line = dict(base, value=value, ms_per_step=ms,
-                config={"workload": workload, "tokens_per_gpu": T,
-                        "parallelism": ("ep%d/%s%s" % (world, args.ep_transport, "/waves%d" % waves if waves > 1 else "")) if world > 1 else "single",
-                        "l2": "L2 flushed between steps" if flush else "working set larger than L2 (no flush needed)"},
-                clocks=clocks, gpu_launches=launches if not graph_info.get("cuda_graph") else launches0_per_loop * args.steps,
-                roofline=roofline, hbm_kernels=hbm, **({"nvlink_kernels": nvlink} if nvlink else {}),
-                phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})
-    if clocks and clocks.get("sm_mhz"):
-        # the step runs under the power cap, whose clock differs from box to box: ms x median SM MHz (= millions of SM
-        # cycles per step) compares runs taken at different clocks
-        line["mcycles_per_step"] = ms * clocks["sm_mhz"] * 1e-3
-    line.update(graph_info)
-    if cfg.get("nvfp4"):
-        line["dtype"] = "nvfp4 weights, bf16 activations"
-        line["config"]["decode_steps_per_step"] = cfg["decode_steps"]
-    if e2e is not None:
-        line["e2e"] = e2e
-    if world == 1 and not args.no_cpu_baseline:
-        from tmt_moe_b200 import synth
-        sample = 2048 if cfg.get("nvfp4") else cpu_sample_tokens(cfg)
-        host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
-        if cfg.get("zipf"):
-            host["bias"] = synth.zipf_bias(E, 2.0)
-        tps, threads, sec = run_cpu(cfg, host, sample, 1, 0)
-        what = ("%d decode steps of %d rows as one batch, bf16 weights (same arithmetic as the dequantised ones)" % (sample // T, T)
-                if cfg.get("nvfp4") else "first %d tokens of the workload" % sample)
-        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                "sample": "%s, all %d experts, one pass (%.1f s)" % (what, E, sec)}
-    print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    # the other ranks wait in their barrier for this report: reach ours whatever happens while the line is put together
+    try:
+        pk, pk_kind = peaks()
+        A = T * K
+        gemm_names = [n for n in phases if n.startswith("gemm_")]
+        gemm_ms = sum(phases[n][0] for n in gemm_names) / args.steps
+        gemm_launches = sum(phases[n][1] for n in gemm_names) // args.steps
+        flops = (12.0 if cfg["backward"] else 4.0) * A * D * H          # all ranks' tokens processed by... this rank's share
+        achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
+        roofline = {"bound": "tensor", "kernel": "%s (%d launches per step)" % (
+                        "gemm_tcgen05_2cta_kernel" if args.gemm == "2cta" else "gemm_tcgen05_kernel", gemm_launches),
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    # dram read + write per launch, averaged over the six launches: ncu capture at 32768 tokens scaled to
+                    # the full token count (activations x 4, weights fixed)
+                    "traffic": 6.1e9 if (args.config == "c5" and not args.tokens and world == 1) else None,
+                    "peak_kind": "%s, sustained (kernel timed inside a long step); burst %.1f" % (pk_kind, pk["bf16_tflops"]),
+                    "flops_per_step": flops, "ms_per_step_in_kernel": gemm_ms}
+        if cfg.get("nvfp4"):
+            # weight-byte roofline: every expert hit in a decode step streams its packed weights once
+            # (0.5 B per value + one scale byte per 16 values), 2*D*H values per expert; with 128 assignments over
+            # 16 experts all experts are hit (P(miss) < 1e-3), plus the 64 input and output rows
+            per_decode = E * 2.0 * D * H * (0.5 + 1.0 / 16) + 2 * T * D * 2
+            gbs = per_decode * cfg["decode_steps"] / (ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": "decode step (router, fp4_rows_kernel up and down on the packed weights, combine)", "achieved": gbs,
+                        "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                        "peak_kind": pk_kind + " copy bandwidth; algorithmic bytes are the packed weights of every expert hit, once per decode "
+                                     "step (36 MB: they stay in the 126 MB L2 between decode steps, so this bounds the kernels' load path, not DRAM)",
+                        "bytes_per_decode_step": per_decode}
+        hbm = {}
+        # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)
+        bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12 + (T * D * 2 if cfg["backward"] else 0)), "combine": (A * D * 2 + T * D * 2),
+                    "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
+        waves = moe.ep_waves if world > 1 else 1
+        for n, nb in bytes_of.items():
+            if world > 1:
+                break
+            if n in phases and phases[n][0] > 0:
+                gbs = nb / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
+                hbm[n] = {"achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                          "bytes_per_launch": nb}
+        nvlink = {}
+        if world > 1 and args.ep_transport == "peer":
+            # Expert parallel: the row kernels move (world-1)/world of their grouped rows over NVLink and are bound by it, not
+            # by HBM: rows leaving (dispatch, gradient dispatch) or entering (combine, scatter) this GPU per launch, against the
+            # measured peer-copy bandwidth of this pool (770 GB/s per direction). Only kernels that run alone on the main stream
+            # have a phase time: the scatter always runs on the second stream under the weight-gradient GEMMs, and with expert
+            # waves so do the other three.
+            out_bytes = A * D * 2 * (world - 1) / world
+            for n in ("dispatch", "combine", "grad_dispatch"):
+                if waves < 2 and n in phases and phases[n][0] > 0:
+                    gbs = out_bytes / (phases[n][0] / phases[n][1] * 1e-3) / 1e9
+                    nvlink[n] = {"achieved": gbs, "peak": 770.0, "unit": "GB/s", "frac": gbs / 770.0, "bytes_over_nvlink": out_bytes,
+                                 "exposed_ms": phases[n][0] / phases[n][1]}
+            nvlink["note"] = ("scatter runs on the second stream under the weight-gradient GEMMs" +
+                              ("; with %d expert waves dispatch, combine and gradient dispatch run there too (no phase time)" % waves if waves > 1 else ""))
+        line = dict(base, value=value, ms_per_step=ms,
+                    config={"workload": workload, "tokens_per_gpu": T,
+                            "parallelism": ("ep%d/%s%s" % (world, args.ep_transport, "/waves%d" % waves if waves > 1 else "")) if world > 1 else "single",
+                            "l2": "L2 flushed between steps" if flush else "working set larger than L2 (no flush needed)"},
+                    clocks=clocks, gpu_launches=launches if not graph_info.get("cuda_graph") else launches0_per_loop * args.steps,
+                    roofline=roofline, hbm_kernels=hbm, **({"nvlink_kernels": nvlink} if nvlink else {}),
+                    phases_ms_per_step={n: v[0] / args.steps for n, v in phases.items()})
+        if clocks and clocks.get("sm_mhz"):
+            # the step runs under the power cap, whose clock differs from box to box: ms x median SM MHz (= millions of SM
+            # cycles per step) compares runs taken at different clocks
+            line["mcycles_per_step"] = ms * clocks["sm_mhz"] * 1e-3
+        line.update(graph_info)
+        if cfg.get("nvfp4"):
+            line["dtype"] = "nvfp4 weights, bf16 activations"
+            line["config"]["decode_steps_per_step"] = cfg["decode_steps"]
+        if e2e is not None:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu_baseline:
+            from tmt_moe_b200 import synth
+            sample = 2048 if cfg.get("nvfp4") else cpu_sample_tokens(cfg)
+            host = synth.make(sample, D, H, E, K, cfg["router_f32"], seed=1234, need_dy=True)
+            if cfg.get("zipf"):
+                host["bias"] = synth.zipf_bias(E, 2.0)
+            tps, threads, sec = run_cpu(cfg, host, sample, 1, 0)
+            what = ("%d decode steps of %d rows as one batch, bf16 weights (same arithmetic as the dequantised ones)" % (sample // T, T)
+                    if cfg.get("nvfp4") else "first %d tokens of the workload" % sample)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": "%s, all %d experts, one pass (%.1f s)" % (what, E, sec)}
+        print(json.dumps(line), flush=True)
+    finally:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

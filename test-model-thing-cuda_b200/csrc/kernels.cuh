@@ -66,9 +66,11 @@ struct PeerMap {
 // router's last kernel; *scanned tells whether it did.
 // ln_gamma / ln_beta / xn (all or none): X holds the rows before the LayerNorm in front of the block; the per-token
 // kernel normalises each row itself and writes it to xn. Only where router_takes_layernorm(d) says so.
+// kernels (may be NULL): receives the number of kernels launched (1 tiled, 2 per-token).
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
                           const float* bias, cudaStream_t s, int scan_splits = 0, bool* scanned = nullptr,
-                          const float* ln_gamma = nullptr, const float* ln_beta = nullptr, uint16_t* xn = nullptr);
+                          const float* ln_gamma = nullptr, const float* ln_beta = nullptr, uint16_t* xn = nullptr,
+                          int* kernels = nullptr);
 bool router_takes_layernorm(const RouteDims& d);
 // splits: number of reduction ranges written to split_poff (1..kMaxSplits).
 cudaError_t launch_scan(const RouteDims& d, const RouteBufs& b, int splits, cudaStream_t s);

@@ -332,8 +332,9 @@ void route_and_dispatch(tmt_moe* h, const uint16_t* X, const void* Wr, uint16_t*
 void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
     prof_mark(h, kPhRouter);
     bool scanned = false;
+    int router_kernels = 1;
     CK(launch_router(h->dims, h->rb, X, Wr, h->has_bias ? h->bias : nullptr, h->stream, h->splits, &scanned, h->ln_gamma,
-                     h->ln_beta, h->ln_gamma ? h->xn : nullptr));
+                     h->ln_beta, h->ln_gamma ? h->xn : nullptr, &router_kernels));
     prof_mark(h, kPhScan);
     if (!scanned) CK(launch_scan(h->dims, h->rb, h->splits, h->stream));
     const int plain = (h->dims.T + h->pad - 1) / h->pad * (h->pad / kPad);     // 128-row tiles, whole pairs for the CTA-pair kernel
@@ -341,7 +342,7 @@ void route_only(tmt_moe* h, const uint16_t* X, const void* Wr) {
         CK(cudaMemcpyAsync(h->plain_num, &plain, sizeof(int), cudaMemcpyHostToDevice, h->stream));
         h->plain_num_host = plain;
     }
-    h->launches += scanned ? 1 : 3;      // the router's kernel, and the scan's two when it ran on its own
+    h->launches += router_kernels + (scanned ? 0 : 2);      // the router's one or two kernels, and the scan's two when it ran on its own
 }
 
 // Grouped expert products over the rows in h->Xg: Yg = expert(Xg). With gate_in_epilogue the

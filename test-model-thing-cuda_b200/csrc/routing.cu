@@ -574,14 +574,16 @@ bool router_takes_layernorm(const RouteDims& d) {
 
 cudaError_t launch_router(const RouteDims& d, const RouteBufs& b, const uint16_t* X, const void* Wr,
                           const float* bias, cudaStream_t s, int scan_splits, bool* scanned, const float* ln_gamma,
-                          const float* ln_beta, uint16_t* xn) {
+                          const float* ln_beta, uint16_t* xn, int* kernels) {
     if (scanned) *scanned = false;
+    if (kernels) *kernels = 1;
     RouterArgs a{X, Wr, bias, d.T, d.D, d.E, d.K, b, ln_gamma, ln_beta, xn};
     const int nb = (d.T + kTokBlock - 1) / kTokBlock;
     bool small = (long)d.T * d.E <= kSmallRouterLogits;
     if (const char* f = getenv("TMT_MOE_ROUTER_SMALL")) if (*f) small = *f != '0';
     if (ln_gamma && !(small && router_takes_layernorm(d))) return cudaErrorInvalidValue;     // the caller normalises first
     if (small) {
+        if (kernels) *kernels = 2;
         cudaError_t le;
         if (ln_gamma) {
             const size_t row = (size_t)d.D * 2;
