@@ -583,10 +583,11 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
             h->launches += 1;
         } else {
             // Expert waves: wave w = the local experts [w*EL/W, (w+1)*EL/W) of EVERY rank. The side stream sends wave after
-            // wave (dispatch + rank barrier) and later fetches the finished waves' output rows; the main stream runs a
-            // wave's two GEMMs as soon as its rows have landed everywhere. So the transfer of wave w+1 runs under the GEMMs
-            // of wave w, and the fetch of wave w under the GEMMs of wave w+1. The GEMM launches leave two SMs free for the
-            // barriers' kernels; the row kernels fit beside the resident GEMM CTAs.
+            // wave (row kernel + rank barrier) and fetches the finished waves' output rows; the main stream runs a wave's
+            // two GEMMs as soon as its rows have landed everywhere. So the transfer of wave w+1 runs under the GEMMs of
+            // wave w, and the fetch of wave w under the GEMMs of the waves after it. The GEMM launches leave two SMs free
+            // for the barriers' kernels; the later waves' row kernels (launch_wave_rows) are shaped to fit beside the
+            // resident CTAs of the CTA-pair GEMM, the full-size ones do not.
             const int W = ep->waves, EL = ep->EL;
             CKE(cudaEventRecord(ep->ev_fork, h->stream));
             CKE(cudaStreamWaitEvent(ep->side, ep->ev_fork, 0));
@@ -654,7 +655,7 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
     } else if (ep->dma) {
         // Rows are grouped locally (token-side layout), cross NVLink as copy-engine copies on the second stream, wave by
         // wave, and are summed locally at the end. The copies occupy no SM, so a wave's transfer really runs under the
-        // previous wave's GEMMs (the SM-based row kernels of the peer transport find no room beside an up / down CTA).
+        // previous wave's GEMMs whatever GEMM kernel runs there.
         route_and_dispatch(h, static_cast<const uint16_t*>(X), Wr, ep->Xs);
         plan_step(h);
         zero_pads(h, h->Xg, D);
