@@ -561,7 +561,7 @@ void ep_forward(tmt_moe* h, const void* X, const void* Wr, const void* const* Wu
     use_expert_layout(h);
     h->dims.T = tokens;
     h->last_tokens = tokens;
-    const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
+    const int D = h->d.dim, E = h->d.experts;
     if (ep->peer) {
         route_only(h, static_cast<const uint16_t*>(X), Wr);
         plan_step(h);                       // all-gather of counts: also separates this step from the previous one

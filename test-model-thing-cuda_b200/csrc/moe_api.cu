@@ -449,7 +449,7 @@ void backward_impl(tmt_moe* h, const void* dY, const void* Wr, const void* const
     if (!dY || !Wr || !Wup || !dWr || !dWup || !dX || (h->d.hidden > 0 && (!Wdown || !dWdown)))
         throw std::runtime_error("null argument");
     CK(cudaSetDevice(h->d.device));
-    const int D = h->d.dim, H = h->d.hidden, E = h->d.experts;
+    const int H = h->d.hidden;
     prof_mark(h, kPhGradDispatch);
     CK(launch_grad_dispatch(h->dims, h->rb, static_cast<const uint16_t*>(dY), h->Yg, h->dYg, h->s_j, H == 0 ? 1 : 0, h->stream));
     h->launches += 1;
