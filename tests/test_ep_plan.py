@@ -269,3 +269,54 @@ def test_device_plan_kernel_equals_the_host_plan(G, E, pad):
         assert lib.tmt_moe_ep_plan_device(G, r, E, pad, small, p(cnt_all), p(tables), p(dest), p(world), p(status)) == 0
         assert status[0] == 4
         assert tables[:EL + 1].max() <= small and tables[2 * EL + 1] <= small // 128
+
+
+@pytest.mark.parametrize("G,E,pad,W", [(8, 64, 256, 4), (4, 64, 256, 4), (2, 64, 256, 4), (2, 8, 128, 4), (8, 16, 128, 4), (3, 6, 128, 2)])
+def test_plan_invariants_for_expert_waves(G, E, pad, W):
+    """Host plan arithmetic at the rank counts no CPU process group runs here, and what the expert waves take from it:
+    on every owner the sources' rows of an expert are contiguous, disjoint and in rank order inside the expert's padded
+    group; every source finds its rows where the owner expects them; the waves' tile ranges (the tile_begin / tile_count
+    a wave's GEMM launches get) are whole `pad`-row units and split the owner's tiles without gap or overlap."""
+    sys.path[:0] = [os.path.join(ROOT, "test-model-thing-cuda_b200")]
+    import tmt_moe_b200 as M
+    lib = M.load()
+    rng = np.random.default_rng(17 * G + E + W)
+    EL = E // G
+    W = min(W, EL)
+    cnt_all = rng.integers(0, 700, size=(G, E)).astype(np.int32)
+    cnt_all[:, rng.integers(0, E)] = 0                      # an expert nobody routes to
+    cnt_all[rng.integers(0, G), rng.integers(0, E)] += 5000  # and a hot one
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    plans = []
+    for r in range(G):
+        tok_poff = np.zeros(E + 1, np.int32); x_counts = np.zeros(EL, np.int32)
+        x_poff = np.zeros(EL + 1, np.int32); src_off = np.zeros(G * EL, np.int32)
+        rows = lib.tmt_moe_ep_plan(G, r, E, pad, p(cnt_all), p(tok_poff), p(x_counts), p(x_poff), p(src_off))
+        assert rows == x_poff[EL]
+        plans.append((tok_poff, x_counts, x_poff, src_off.reshape(G, EL)))
+    for o, (tok_poff, x_counts, x_poff, src_off) in enumerate(plans):
+        assert x_poff[0] == 0 and np.all(x_poff % pad == 0)
+        # token side of rank o: its own assignments per expert, padded groups
+        np.testing.assert_array_equal(np.diff(tok_poff), (cnt_all[o] + pad - 1) // pad * pad)
+        for le in range(EL):
+            e = o * EL + le
+            assert x_counts[le] == cnt_all[:, e].sum()
+            assert x_poff[le + 1] - x_poff[le] == (x_counts[le] + pad - 1) // pad * pad
+            # sources in rank order, back to back, from the start of the group
+            want = np.concatenate([[0], np.cumsum(cnt_all[:-1, e])])
+            np.testing.assert_array_equal(src_off[:, le], want)
+        # the waves' GEMM tile ranges on this owner
+        covered = 0
+        for w in range(W):
+            lo, hi = EL * w // W, EL * (w + 1) // W
+            assert hi > lo
+            begin, count = x_poff[lo] // 128, (x_poff[hi] - x_poff[lo]) // 128
+            assert begin == covered and begin % (pad // 128) == 0 and count % (pad // 128) == 0
+            covered += count
+        assert covered == x_poff[EL] // 128
+    # every rank's view of the same thing: capacity verdicts agree with the plans
+    worst = max(int(pl[2][EL]) for pl in plans)
+    rows_out = ctypes.c_longlong(0)
+    assert lib.tmt_moe_ep_check_capacity(G, E, pad, p(cnt_all), ctypes.c_longlong(worst), ctypes.byref(rows_out)) == -1
+    bad = lib.tmt_moe_ep_check_capacity(G, E, pad, p(cnt_all), ctypes.c_longlong(worst - pad), ctypes.byref(rows_out))
+    assert bad == min(r for r, pl in enumerate(plans) if pl[2][EL] > worst - pad) and rows_out.value == plans[bad][2][EL]
