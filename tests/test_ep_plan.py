@@ -320,3 +320,72 @@ def test_plan_invariants_for_expert_waves(G, E, pad, W):
     assert lib.tmt_moe_ep_check_capacity(G, E, pad, p(cnt_all), ctypes.c_longlong(worst), ctypes.byref(rows_out)) == -1
     bad = lib.tmt_moe_ep_check_capacity(G, E, pad, p(cnt_all), ctypes.c_longlong(worst - pad), ctypes.byref(rows_out))
     assert bad == min(r for r, pl in enumerate(plans) if pl[2][EL] > worst - pad) and rows_out.value == plans[bad][2][EL]
+
+
+@pytest.mark.parametrize("G,E,K,pad,W,F", [(8, 64, 4, 256, 4, 4), (8, 64, 4, 256, 4, 2), (4, 64, 4, 256, 4, 0), (2, 8, 2, 128, 2, 2)])
+def test_peer_addressing_in_expert_waves(G, E, K, pad, W, F):
+    """The peer transport's addressing, restated with numpy for rank counts no GPU test here runs: a token-side slot of
+    rank r and expert e lives in the owner's buffer at row dest_row0_r[e] + slot - poff_r[e] (group_row in
+    csrc/permute.cu), dest_row0 taken from the OWNER's plan; an assignment moves in the wave its expert's index inside
+    the owner falls into (in_wave). Sent wave by wave from all ranks, every data row of every owner is written exactly
+    once, each expert group holds its sources' rows in rank order and slot order, and what comes back (F waves fetched
+    into the token-side copy, the others read by the final combine) is each assignment's own row."""
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "test-model-thing-cuda_b200")]
+    import tmt_moe_b200 as M
+    from oracle import oracle as O
+    lib = M.load()
+    rng = np.random.default_rng(5 * G + E + W + F)
+    EL, T = E // G, 160
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    idx = [np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32) for _ in range(G)]
+    lay = [dict(zip(("counts", "off", "poff", "slot_of"), O.layout(i, E, pad))) for i in idx]    # every rank's token side
+    cnt_all = np.stack([l["counts"] for l in lay]).astype(np.int32)
+    plans = []
+    for o in range(G):
+        tok_poff = np.zeros(E + 1, np.int32); x_counts = np.zeros(EL, np.int32)
+        x_poff = np.zeros(EL + 1, np.int32); src_off = np.zeros(G * EL, np.int32)
+        rows = lib.tmt_moe_ep_plan(G, o, E, pad, p(cnt_all), p(tok_poff), p(x_counts), p(x_poff), p(src_off))
+        plans.append((int(rows), x_counts, x_poff, src_off.reshape(G, EL)))
+        np.testing.assert_array_equal(tok_poff, lay[o]["poff"])
+    dest_row0 = [np.array([plans[e // EL][2][e % EL] + plans[e // EL][3][r, e % EL] for e in range(E)]) for r in range(G)]
+    ident = lambda r, t: r * 100000 + t + 1                    # a row's content: who sent it
+    Xg = [np.zeros(pl[0], np.int64) for pl in plans]
+    waves_of = lambda e: [w for w in range(W) if EL * w // W <= e % EL < EL * (w + 1) // W]
+    for w in range(W):                                         # dispatch, wave after wave
+        for r in range(G):
+            for t in range(T):
+                for j in range(K):
+                    e = int(idx[r][t, j])
+                    if waves_of(e) != [w]:
+                        continue
+                    row = dest_row0[r][e] + lay[r]["slot_of"][t, j] - lay[r]["poff"][e]
+                    assert 0 <= row < plans[e // EL][0] and Xg[e // EL][row] == 0
+                    Xg[e // EL][row] = ident(r, t)
+    for o, (rows, x_counts, x_poff, src_off) in enumerate(plans):
+        assert np.count_nonzero(Xg[o]) == x_counts.sum()
+        for le in range(EL):
+            e = o * EL + le
+            want = []
+            for s in range(G):                                 # sources in rank order, each in its own slot order
+                tj = np.argwhere(idx[s] == e)
+                tj = tj[np.argsort(lay[s]["slot_of"][tj[:, 0], tj[:, 1]])]
+                want += [ident(s, int(t)) for t, _ in tj]
+            np.testing.assert_array_equal(Xg[o][x_poff[le]:x_poff[le] + x_counts[le]], np.array(want, np.int64))
+            assert not Xg[o][x_poff[le] + x_counts[le]:x_poff[le + 1]].any()        # pad rows untouched
+    Yg = [x * 3 for x in Xg]                                   # the experts' outputs, row for row
+    fetched_hi = EL * F // W
+    for r in range(G):
+        Yr = np.zeros(int(lay[r]["poff"][E]), np.int64)
+        for w in range(F):                                     # fetched on the second stream
+            for t in range(T):
+                for j in range(K):
+                    e = int(idx[r][t, j])
+                    if waves_of(e) == [w]:
+                        slot = lay[r]["slot_of"][t, j]
+                        Yr[slot] = Yg[e // EL][dest_row0[r][e] + slot - lay[r]["poff"][e]]
+        for t in range(T):                                     # final combine: fetched rows locally, the others from their owners
+            for j in range(K):
+                e = int(idx[r][t, j])
+                slot = lay[r]["slot_of"][t, j]
+                got = Yr[slot] if e % EL < fetched_hi else Yg[e // EL][dest_row0[r][e] + slot - lay[r]["poff"][e]]
+                assert got == 3 * ident(r, t)
