@@ -389,3 +389,29 @@ def test_peer_addressing_in_expert_waves(G, E, K, pad, W, F):
                 slot = lay[r]["slot_of"][t, j]
                 got = Yr[slot] if e % EL < fetched_hi else Yg[e // EL][dest_row0[r][e] + slot - lay[r]["poff"][e]]
                 assert got == 3 * ident(r, t)
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_wave_row_kernel_visits_every_assignment_once(K):
+    """The index arithmetic of wave_rows_kernel (csrc/permute.cu) restated: a warp takes 32 / K tokens at a time, lane l
+    looks at assignment l of the chunk; for every top-k (also those that do not divide 32) and token counts that do not
+    fill the last chunk, each assignment of each token is looked at exactly once, by the lane that the row loop later
+    names, and the s_j index of lane j is that assignment's."""
+    for T in (1, 31, 32, 33, 257):
+        per = 32 // K
+        nchunk = (T + per - 1) // per
+        blocks, warps = 3, 8
+        nwarp = blocks * warps
+        seen = np.zeros(T * K, np.int32)
+        for gw in range(nwarp):                               # blockIdx.x * warps + warp
+            for c in range(gw, nchunk, nwarp):
+                for lane in range(32):
+                    tl = lane // K
+                    t = c * per + tl
+                    if tl < per and t < T:
+                        a = c * per * K + lane
+                        assert a == t * K + lane % K
+                        seen[a] += 1
+                        # the row loop names this assignment by its lane j: token c * per + j / K, s_j index c * per * K + j
+                        assert c * per + lane // K == t and c * per * K + lane == a
+        assert (seen == 1).all()
