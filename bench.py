@@ -734,7 +734,10 @@ def main():
         # dispatch also keeps X in token order for the router weight gradient when the handle trains (one more T*D*2 written)
         bytes_of = {"dispatch": (T * D * 2 + A * D * 2 + A * 12 + (T * D * 2 if cfg["backward"] else 0)), "combine": (A * D * 2 + T * D * 2),
                     "grad_dispatch": (T * D * 2 + A * D * 2), "scatter": (A * D * 2 + 2 * T * D * 2)}
-        waves = moe.ep_waves if world > 1 else 1
+        try:                                    # a label of the report only: never worth losing the line for
+            waves = moe.ep_waves if world > 1 else 1
+        except Exception:
+            waves = int(os.environ.get("TMT_MOE_EP_WAVES", "1") or 1)
         for n, nb in bytes_of.items():
             if world > 1:
                 break
