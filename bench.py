@@ -760,6 +760,9 @@ def main():
                                  "exposed_ms": phases[n][0] / phases[n][1]}
             nvlink["note"] = ("scatter runs on the second stream under the weight-gradient GEMMs" +
                               ("; with %d expert waves dispatch, combine and gradient dispatch run there too (no phase time)" % waves if waves > 1 else ""))
+        if waves > 1:
+            roofline["note"] = ("expert waves: the GEMM phases' events also bracket the main stream's waits for the waves' rows and the "
+                                "row kernels running beside the CTAs, so this fraction is a lower bound of the kernels' own")
         line = dict(base, value=value, ms_per_step=ms,
                     config={"workload": workload, "tokens_per_gpu": T,
                             "parallelism": ("ep%d/%s%s" % (world, args.ep_transport, "/waves%d" % waves if waves > 1 else "")) if world > 1 else "single",
